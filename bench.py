@@ -1,0 +1,297 @@
+#!/usr/bin/env python
+"""Benchmark of the DP-Linear backward hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl native|reference] [--workload NAME]
+
+A step is one DP backward of one Linear layer on one batch of synthetic input:
+    dW = (1/B) sum_b clip(G_b^T X_b) + N(0, (sigma/sqrt(B))^2)      (fdp_linear_wgrad)
+    dX = G W                                                        (fdp_linear_dgrad)
+and, on N > 1 GPUs (one process per GPU, the batch sharded, B samples per rank), an NCCL all-reduce
+of the clipped sums.  The metric is algorithmic TFLOP/s: 4*B*T*in*out per rank and step.
+Rank 0 prints one JSON line.  `--impl reference` times the CPU port of the reference's
+pure-PyTorch per-sample path on the host cores instead (rank 0 only).
+"""
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B per GPU, T, in, out, dtype, g_scale)
+    "linear_bf16_b32_t1024_4096x4096": (32, 1024, 4096, 4096, "bf16", 1e-3),
+    "conv1d_bf16_b16_t1024_1024x3072": (16, 1024, 1024, 3072, "bf16", 1e-3),
+    "linear_fp32_b4_t128_768x768": (4, 128, 768, 768, "f32", 1e-2),
+    "small_bf16_b4_t256_512x512": (4, 256, 512, 512, "bf16", 1e-3),
+}
+DEFAULT_WORKLOAD = "linear_bf16_b32_t1024_4096x4096"
+METRIC, UNIT = "dp_linear_bwd_tflops", "TFLOP/s"
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(bf16=p["bf16_tflops"], bf16_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]),
+                    hbm=p["hbm_gbs"], source="measured")
+    return dict(bf16=1590.0, bf16_sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+def flops_bwd(B, T, n_in, n_out):
+    return 4.0 * B * T * n_in * n_out
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                       "-lms", "100", "-i", str(gpu_index)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.p = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.p is None:
+            return out
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except Exception:
+            self.p.kill()
+        self.f.flush()
+        self.f.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.f.read().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.f.name)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def cpu_port_rate(T, n_in, n_out, dtype_name, budget_s, sample_b=2, steps=None, warmup=1):
+    """TFLOP/s of the reference's per-sample path (CPU port in oracle/) on a bounded sample."""
+    import torch
+    from oracle import dp_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    dt = torch.bfloat16 if dtype_name == "bf16" else torch.float32
+    X, G, W = O.make_linear_inputs(sample_b, T, n_in, n_out, 1e-3, seed=0, dtype=dt)
+    for _ in range(warmup):
+        O.torch_port_linear_backward(G, X, W, 1.0, 1.0, 1.0, False)
+    times = []
+    t_start = time.perf_counter()
+    while True:
+        t0 = time.perf_counter()
+        O.torch_port_linear_backward(G, X, W, 1.0, 1.0, 1.0, False)
+        times.append(time.perf_counter() - t0)
+        if steps is not None:
+            if len(times) >= steps:
+                break
+        elif time.perf_counter() - t_start > budget_s and len(times) >= 3:
+            break
+    med = statistics.median(times)
+    return dict(value=flops_bwd(sample_b, T, n_in, n_out) / med / 1e12, unit=UNIT, cores=cores, kind="port",
+                sample=f"{sample_b} of the workload's samples per step (T={T}, {n_in}->{n_out}, {dtype_name}), "
+                       f"median of {len(times)} steps, torch CPU ops as the reference issues them",
+                ms_per_step=med * 1e3, steps=len(times))
+
+
+def run_reference(args, wl):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    B, T, n_in, n_out, dtn, _ = wl
+    base = cpu_port_rate(T, n_in, n_out, dtn, budget_s=0, steps=max(1, args.steps), warmup=max(1, args.warmup))
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtn, "data": "synthetic",
+            "config": {"workload": args.workload, "where": "host CPU cores", "sample": base["sample"]},
+            "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def run_native(args, wl):
+    import torch
+    import torch.distributed as dist
+    import flashdp4review_b200 as fdp
+    from flashdp4review_b200 import _lib
+    from flashdp4review_b200.core import ops
+    from oracle import dp_oracle as O  # input recipe + the cpu_baseline leg only
+
+    B, T, n_in, n_out, dtn, g_scale = wl
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus and world > 1:
+        args.gpus = world
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    lib = _lib.load()
+    _lib.check(lib.fdp_check_device(local_rank), "fdp_check_device")
+    fdp.manual_seed(1234)
+    fdp.set_data_parallel(rank, world)
+    dt = torch.bfloat16 if dtn == "bf16" else torch.float32
+
+    # synthetic inputs: X~N(0,1), G~N(0,g_scale^2), W~N(0,0.02^2); a different seed per rank (its shard)
+    Xh, Gh, Wh = O.make_linear_inputs(B, T, n_in, n_out, g_scale, seed=rank, dtype=dt)
+    Xh, Gh = Xh.pin_memory(), Gh.pin_memory()
+    X, G, W = Xh.to(dev), Gh.to(dev), Wh.to(dev)
+    step_no = [0]
+
+    def step(Xd, Gd):
+        step_no[0] += 1
+        noise = ops.NoiseSpec(std=ops.noise_std(1.0, B * world), seed=1234, param_id=1, step=step_no[0],
+                              rank=rank, world=world)
+        dW = ops.dp_linear_weight_grad(Xd, Gd, 1.0, 1.0, batch_divisor=B * world, noise=noise,
+                                       out_dtype=torch.float32, norm_algo=args.norm_algo)
+        work = dist.all_reduce(dW, op=dist.ReduceOp.SUM, async_op=True) if world > 1 else None
+        dX = ops.linear_input_grad(Gd, W, "out_in")
+        if work is not None:
+            work.wait()
+        return dW, dX
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(args.warmup, 3)):
+        step(X, G)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    launches0 = lib.fdp_launch_count()
+    total_ms = timed(lambda: step(X, G), args.steps)
+    launches = lib.fdp_launch_count() - launches0
+    clocks = sampler.stop() if sampler else None
+    ms_per_step = total_ms / args.steps
+    value = world * flops_bwd(B, T, n_in, n_out) / (ms_per_step * 1e-3) / 1e12
+
+    # end to end: host (pinned) inputs in, gradient back to the host, every step
+    dW_host = torch.empty(n_out, n_in, dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        X.copy_(Xh, non_blocking=True)
+        G.copy_(Gh, non_blocking=True)
+        dW, dX = step(X, G)
+        dW_host.copy_(dW, non_blocking=True)
+
+    e2e_steps = max(2, min(args.steps, 10))
+    e2e_step()
+    e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
+    e2e_value = world * flops_bwd(B, T, n_in, n_out) / (e2e_ms * 1e-3) / 1e12
+    h2d = Xh.numel() * Xh.element_size() + Gh.numel() * Gh.element_size()
+    d2h = dW_host.numel() * 4
+
+    # dominant kernel (clipped-sum GEMM) timed alone with CUDA events recorded inside the call
+    pk = peaks()
+    roof = None
+    phases = None
+    if rank == 0:
+        lib.fdp_profile_enable(1)
+        acc = [[], [], [], []]
+        for _ in range(5):
+            step(X, G)
+            ms = (ctypes.c_float * 4)()
+            if lib.fdp_profile_read(ms, 4) == 4:
+                for i in range(4):
+                    acc[i].append(ms[i])
+        lib.fdp_profile_enable(0)
+        if acc[3]:
+            phases = {n: statistics.mean(v) for n, v in zip(("norm_pass_ms", "clip_factors_ms", "prescale_ms",
+                                                             "clipped_gemm_ms"), acc)}
+            gemm_flops = 2.0 * B * T * n_in * n_out
+            achieved = gemm_flops / (phases["clipped_gemm_ms"] * 1e-3) / 1e12
+            roof = {"kernel": "clipped-sum GEMM (tcgen05)" if dtn != "f32" else "clipped-sum GEMM (fp32 FMA)",
+                    "bound": "tensor", "achieved": achieved, "peak": pk["bf16_sustained"], "unit": "TFLOP/s",
+                    "frac": achieved / pk["bf16_sustained"], "frac_of_burst_peak": achieved / pk["bf16"],
+                    "peak_source": pk["source"] + " (sustained cuBLAS bf16; kernel timed inside the step loop)",
+                    "traffic": None, "phases_ms": phases,
+                    "wgrad_path_tflops": gemm_flops / (sum(phases.values()) * 1e-3) / 1e12}
+    barrier()
+
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cpu = cpu_port_rate(T, n_in, n_out, dtn, budget_s=args.cpu_budget)
+        cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+
+    if rank == 0:
+        line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": dtn, "data": "synthetic",
+                "config": {"workload": args.workload, "B_per_gpu": B, "T": T, "in": n_in, "out": n_out,
+                           "C": 1.0, "noise_multiplier": 1.0, "bias": False, "grad_dtype": "f32",
+                           "flops_per_step_per_gpu": flops_bwd(B, T, n_in, n_out),
+                           "l2": "inputs (X, G: %.0f MB) larger than the 126 MB L2" % (h2d / 1e6),
+                           "parallelism": f"dp{world}" + (" + NCCL all-reduce of dW" if world > 1 else "")},
+                "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "ms_per_step": e2e_ms, "steps": e2e_steps},
+                "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "cpu_baseline": cpu}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--norm-algo", default="auto", choices=["auto", "direct", "gram"])
+    ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work for cpu_baseline")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    wl = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, wl)
+    else:
+        run_native(args, wl)
+
+
+if __name__ == "__main__":
+    main()

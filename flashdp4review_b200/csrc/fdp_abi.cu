@@ -1,0 +1,334 @@
+// extern "C" entry points: argument checks, workspace carving, kernel selection.
+// No allocation, no host synchronisation (except fdp_device_status), no exceptions.
+#include <atomic>
+#include <mutex>
+
+#include "fdp_kernels.h"
+
+using namespace fdp;
+
+namespace fdp {
+static std::atomic<unsigned long long> g_launches{0};
+void note_launch(int n) { g_launches.fetch_add(static_cast<unsigned long long>(n), std::memory_order_relaxed); }
+}  // namespace fdp
+
+namespace {
+
+bool valid_dtype(int dt) { return dt == FDP_F32 || dt == FDP_BF16 || dt == FDP_F16; }
+
+// compute capability per device, looked up once
+int device_cc_major(int dev) {
+  static std::mutex mu;
+  static int cache[64];
+  static bool have[64];
+  if (dev < 0 || dev >= 64) return -1;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!have[dev]) {
+    int major = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) {
+      cudaGetLastError();
+      return -1;
+    }
+    cache[dev] = major;
+    have[dev] = true;
+  }
+  return cache[dev];
+}
+
+int current_device_ok() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return FDP_ERR_LAUNCH; }
+  return device_cc_major(dev) == 10 ? FDP_OK : FDP_ERR_ARCH;
+}
+
+int check_params(const fdp_dp_params* p) {
+  if (p == nullptr) return FDP_ERR_ARG;
+  if (!(p->noise_std >= 0.f)) return FDP_ERR_ARG;
+  if (p->noise_world > 1 && (p->noise_rank < 0 || p->noise_rank >= p->noise_world)) return FDP_ERR_ARG;
+  return FDP_OK;
+}
+
+// workspace of fdp_linear_wgrad: [status word | norms | factors | partials | tensor-core extra]
+struct WgradWs {
+  int* status; float* norms; float* factors; float* partials; void* tc_extra;
+  size_t bytes; int nparts; TcPlan tc;
+};
+WgradWs wgrad_ws(void* base, int B, int T, int n_in, int n_out, int dt, int norm_algo) {
+  WgradWs w;
+  w.tc = tc_plan(B, T, n_in, n_out, dt, norm_algo);
+  w.nparts = w.tc.ok ? w.tc.nparts : simt_norm_tiles(n_in, n_out);
+  Carver c(base);
+  w.status = c.take<int>(64);
+  w.norms = c.take<float>(B);
+  w.factors = c.take<float>(B);
+  w.partials = c.take<float>(static_cast<size_t>(B) * w.nparts);
+  w.tc_extra = c.take<char>(w.tc.ok ? w.tc.ws_bytes : 0);
+  w.bytes = c.off;
+  return w;
+}
+
+// Optional phase timing of fdp_linear_wgrad: CUDA events recorded on the caller's stream between
+// the phases (norm pass | clip factors | c_b pre-scale | clipped-sum GEMM).  Off by default.
+struct PhaseProfile {
+  std::mutex mu;
+  bool on = false;
+  bool have_events = false;
+  bool recorded = false;
+  cudaEvent_t ev[5];
+} g_prof;
+
+void prof_mark(int i, cudaStream_t s) {
+  if (!g_prof.on) return;
+  std::lock_guard<std::mutex> lk(g_prof.mu);
+  if (g_prof.on && g_prof.have_events) {
+    cudaEventRecord(g_prof.ev[i], s);
+    if (i == 4) g_prof.recorded = true;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+unsigned long long fdp_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int fdp_profile_enable(int on) {
+  std::lock_guard<std::mutex> lk(g_prof.mu);
+  if (on && !g_prof.have_events) {
+    for (int i = 0; i < 5; ++i)
+      if (cudaEventCreate(&g_prof.ev[i]) != cudaSuccess) { cudaGetLastError(); return FDP_ERR_LAUNCH; }
+    g_prof.have_events = true;
+  }
+  g_prof.on = on != 0;
+  g_prof.recorded = false;
+  return FDP_OK;
+}
+
+int fdp_profile_read(float* ms, int capacity) {
+  std::lock_guard<std::mutex> lk(g_prof.mu);
+  if (ms == nullptr || capacity < 4) return FDP_ERR_ARG;
+  if (!g_prof.have_events || !g_prof.recorded) return FDP_ERR_ARG;
+  if (cudaEventSynchronize(g_prof.ev[4]) != cudaSuccess) { cudaGetLastError(); return FDP_ERR_LAUNCH; }
+  for (int i = 0; i < 4; ++i)
+    if (cudaEventElapsedTime(&ms[i], g_prof.ev[i], g_prof.ev[i + 1]) != cudaSuccess) { cudaGetLastError(); return FDP_ERR_LAUNCH; }
+  return 4;
+}
+
+int fdp_abi_version(void) { return FDP_ABI_VERSION; }
+
+const char* fdp_status_string(int status) {
+  switch (status) {
+    case FDP_OK: return "ok";
+    case FDP_ERR_ARG: return "invalid argument";
+    case FDP_ERR_DTYPE: return "unsupported dtype";
+    case FDP_ERR_SHAPE: return "unsupported shape";
+    case FDP_ERR_ALIGN: return "pointer not 16-byte aligned";
+    case FDP_ERR_WORKSPACE: return "workspace missing or too small";
+    case FDP_ERR_ARCH: return "device is not sm_100 (B200)";
+    case FDP_ERR_LAUNCH: return "CUDA launch/runtime error";
+    case FDP_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    default: return "unknown status";
+  }
+}
+
+int fdp_check_device(int device) { return device_cc_major(device) == 10 ? FDP_OK : FDP_ERR_ARCH; }
+
+int fdp_device_status(const void* workspace, fdp_stream_t stream) {
+  if (workspace == nullptr) return FDP_ERR_ARG;
+  int h = 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  FDP_CUDA_OK(cudaMemcpyAsync(&h, workspace, sizeof(int), cudaMemcpyDeviceToHost, s));
+  FDP_CUDA_OK(cudaStreamSynchronize(s));
+  return h == 0 ? FDP_OK : FDP_ERR_TIMEOUT;
+}
+
+// ---- weight gradient ------------------------------------------------------------------------------
+size_t fdp_linear_wgrad_workspace_bytes(int B, int T, int n_in, int n_out, int in_dtype,
+                                        int norm_algo) {
+  if (B <= 0 || T <= 0 || n_in <= 0 || n_out <= 0 || !valid_dtype(in_dtype)) return 0;
+  return wgrad_ws(nullptr, B, T, n_in, n_out, in_dtype, norm_algo).bytes;
+}
+
+int fdp_linear_wgrad(const void* G, const void* X, void* dW, float* norms_out, float* factors_out,
+                     int B, int T, int n_in, int n_out, int in_dtype, int out_dtype, int layout,
+                     int norm_algo, const fdp_dp_params* p, void* workspace, size_t workspace_bytes,
+                     fdp_stream_t stream) {
+  if (G == nullptr || X == nullptr || dW == nullptr) return FDP_ERR_ARG;
+  if (B <= 0 || T <= 0 || n_in <= 0 || n_out <= 0) return FDP_ERR_ARG;
+  if (layout != FDP_OUT_IN && layout != FDP_IN_OUT) return FDP_ERR_ARG;
+  if (norm_algo < FDP_NORM_AUTO || norm_algo > FDP_NORM_GRAM) return FDP_ERR_ARG;
+  if (!valid_dtype(in_dtype) || !valid_dtype(out_dtype)) return FDP_ERR_DTYPE;
+  if (static_cast<long long>(B) * T >= (1ll << 31) / 2) return FDP_ERR_SHAPE;
+  int st = check_params(p);
+  if (st != FDP_OK) return st;
+  if (!aligned16(G) || !aligned16(X) || !aligned16(dW)) return FDP_ERR_ALIGN;
+  if ((st = current_device_ok()) != FDP_OK) return st;
+  if (workspace == nullptr) return FDP_ERR_WORKSPACE;
+  WgradWs w = wgrad_ws(workspace, B, T, n_in, n_out, in_dtype, norm_algo);
+  if (workspace_bytes < w.bytes || !aligned16(workspace)) return FDP_ERR_WORKSPACE;
+
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int div = p->batch_divisor > 0 ? p->batch_divisor : B;
+  const float inv_div = 1.0f / static_cast<float>(div);
+  const NoiseKey nk = make_noise_key(p, p->param_id);
+  FDP_CUDA_OK(cudaMemsetAsync(w.status, 0, sizeof(int), s));
+
+  prof_mark(0, s);
+  if (w.tc.ok) {
+    if ((st = tc_norms(G, X, w.partials, w.status, B, T, n_in, n_out, in_dtype, w.tc, s)) != FDP_OK) return st;
+  } else {
+    simt_norm_direct(G, X, w.partials, B, T, n_in, n_out, in_dtype, s);
+  }
+  prof_mark(1, s);
+  clip_factors(w.partials, w.nparts, B, p->C, p->clamp_value, w.norms, w.factors, norms_out, factors_out, s);
+  prof_mark(2, s);
+  if (w.tc.ok) {
+    if ((st = tc_prescale(G, w.factors, w.tc_extra, B, T, n_out, in_dtype, s)) != FDP_OK) return st;
+    prof_mark(3, s);
+    if ((st = tc_clipped_wgrad(w.tc_extra, X, dW, w.status, B, T, n_in, n_out, in_dtype, out_dtype, layout,
+                               inv_div, nk, s)) != FDP_OK) return st;
+  } else {
+    prof_mark(3, s);
+    simt_clipped_wgrad(G, X, w.factors, dW, B, T, n_in, n_out, in_dtype, out_dtype, layout, inv_div, nk, s);
+  }
+  prof_mark(4, s);
+  FDP_LAUNCH_OK();
+  return FDP_OK;
+}
+
+// ---- bias gradient ----------------------------------------------------------------------------------
+size_t fdp_bias_grad_workspace_bytes(int B, int T, int n_out, int in_dtype) {
+  if (B <= 0 || T <= 0 || n_out <= 0 || !valid_dtype(in_dtype)) return 0;
+  const GstatsPlan pl = gstats_plan(T, n_out, in_dtype);
+  Carver c(nullptr);
+  c.take<float>(B);                                                      // factors
+  c.take<float>(static_cast<size_t>(B) * pl.row_chunks * pl.col_chunks); // sq partials
+  c.take<float>(static_cast<size_t>(B) * pl.row_chunks * n_out);         // column-sum partials
+  return c.off;
+}
+
+int fdp_bias_grad(const void* G, void* db, float* norms_out, float* factors_out, int B, int T,
+                  int n_out, int in_dtype, int out_dtype, const fdp_dp_params* p, void* workspace,
+                  size_t workspace_bytes, fdp_stream_t stream) {
+  if (G == nullptr || db == nullptr) return FDP_ERR_ARG;
+  if (B <= 0 || T <= 0 || n_out <= 0) return FDP_ERR_ARG;
+  if (!valid_dtype(in_dtype) || !valid_dtype(out_dtype)) return FDP_ERR_DTYPE;
+  int st = check_params(p);
+  if (st != FDP_OK) return st;
+  if ((st = current_device_ok()) != FDP_OK) return st;
+  if (workspace == nullptr || !aligned16(workspace) ||
+      workspace_bytes < fdp_bias_grad_workspace_bytes(B, T, n_out, in_dtype))
+    return FDP_ERR_WORKSPACE;
+  const GstatsPlan pl = gstats_plan(T, n_out, in_dtype);
+  Carver c(workspace);
+  float* factors = c.take<float>(B);
+  float* sq_part = c.take<float>(static_cast<size_t>(B) * pl.row_chunks * pl.col_chunks);
+  float* colsum_part = c.take<float>(static_cast<size_t>(B) * pl.row_chunks * n_out);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int div = p->batch_divisor > 0 ? p->batch_divisor : B;
+  // mean over the B*T rows (flashdp/core/linear_clip.py:122)
+  const float inv_div = 1.0f / (static_cast<float>(div) * static_cast<float>(T));
+  gstats(G, colsum_part, sq_part, B, T, n_out, in_dtype, pl, s);
+  clip_factors(sq_part, pl.row_chunks * pl.col_chunks, B, p->C, p->clamp_value, nullptr, factors,
+               norms_out, factors_out, s);
+  bias_finalize(colsum_part, factors, db, B, n_out, pl.row_chunks, out_dtype, inv_div,
+                make_noise_key(p, p->param_id), s);
+  FDP_LAUNCH_OK();
+  return FDP_OK;
+}
+
+// ---- input gradient ---------------------------------------------------------------------------------
+size_t fdp_linear_dgrad_workspace_bytes(int rows, int n_in, int n_out, int dtype) {
+  (void)rows; (void)n_in; (void)n_out; (void)dtype;
+  return 256;  // the status word
+}
+
+int fdp_linear_dgrad(const void* G, const void* W, void* dX, int rows, int n_in, int n_out,
+                     int dtype, int w_layout, void* workspace, size_t workspace_bytes,
+                     fdp_stream_t stream) {
+  if (G == nullptr || W == nullptr || dX == nullptr) return FDP_ERR_ARG;
+  if (rows <= 0 || n_in <= 0 || n_out <= 0) return FDP_ERR_ARG;
+  if (w_layout != FDP_OUT_IN && w_layout != FDP_IN_OUT) return FDP_ERR_ARG;
+  if (!valid_dtype(dtype)) return FDP_ERR_DTYPE;
+  int st = current_device_ok();
+  if (st != FDP_OK) return st;
+  if (workspace == nullptr || workspace_bytes < 256 || !aligned16(workspace)) return FDP_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int* status = static_cast<int*>(workspace);
+  FDP_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), s));
+  if (tc_dgrad_ok(rows, n_in, n_out, dtype) && aligned16(G) && aligned16(W) && aligned16(dX)) {
+    if ((st = tc_dgrad(G, W, dX, status, rows, n_in, n_out, dtype, w_layout, s)) != FDP_OK) return st;
+  } else {
+    simt_dgrad(G, W, dX, rows, n_in, n_out, dtype, w_layout, s);
+  }
+  FDP_LAUNCH_OK();
+  return FDP_OK;
+}
+
+// ---- LayerNorm ------------------------------------------------------------------------------------------
+int fdp_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean,
+                      float* rstd, int rows, int d, float eps, int dtype, int param_dtype,
+                      fdp_stream_t stream) {
+  if (x == nullptr || gamma == nullptr || beta == nullptr || y == nullptr || mean == nullptr || rstd == nullptr)
+    return FDP_ERR_ARG;
+  if (rows <= 0 || d <= 0) return FDP_ERR_ARG;
+  if (!valid_dtype(dtype) || !valid_dtype(param_dtype)) return FDP_ERR_DTYPE;
+  int st = current_device_ok();
+  if (st != FDP_OK) return st;
+  ln_fwd(x, gamma, beta, y, mean, rstd, rows, d, eps, dtype, param_dtype, static_cast<cudaStream_t>(stream));
+  FDP_LAUNCH_OK();
+  return FDP_OK;
+}
+
+size_t fdp_layernorm_bwd_workspace_bytes(int B, int T, int d) {
+  if (B <= 0 || T <= 0 || d <= 0) return 0;
+  const LnPlan pl = ln_plan(T, d, FDP_F32);  // the chunk count does not depend on the dtype
+  Carver c(nullptr);
+  c.take<float>(2 * B);                                          // sums of squares
+  c.take<float>(2 * B);                                          // factors
+  c.take<float>(static_cast<size_t>(2) * B * pl.chunks * d);     // partials, both tensors
+  return c.off;
+}
+
+int fdp_layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean,
+                      const float* rstd, void* dx, void* dgamma, void* dbeta, float* norms_gamma,
+                      float* norms_beta, int B, int T, int d, int dtype, int param_dtype,
+                      const fdp_dp_params* p, void* workspace, size_t workspace_bytes,
+                      fdp_stream_t stream) {
+  if (dy == nullptr || x == nullptr || gamma == nullptr || mean == nullptr || rstd == nullptr || dgamma == nullptr)
+    return FDP_ERR_ARG;
+  if (B <= 0 || T <= 0 || d <= 0) return FDP_ERR_ARG;
+  if (!valid_dtype(dtype) || !valid_dtype(param_dtype)) return FDP_ERR_DTYPE;
+  if (d > 8192) return FDP_ERR_SHAPE;
+  int st = check_params(p);
+  if (st != FDP_OK) return st;
+  if ((st = current_device_ok()) != FDP_OK) return st;
+  if (workspace == nullptr || !aligned16(workspace) ||
+      workspace_bytes < fdp_layernorm_bwd_workspace_bytes(B, T, d))
+    return FDP_ERR_WORKSPACE;
+  const LnPlan pl = ln_plan(T, d, dtype);
+  Carver c(workspace);
+  float* sumsq = c.take<float>(2 * B);
+  float* factors = c.take<float>(2 * B);
+  float* part = c.take<float>(static_cast<size_t>(2) * B * pl.chunks * d);
+  float* dg_part = part;
+  float* db_part = part + static_cast<size_t>(B) * pl.chunks * d;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int div = p->batch_divisor > 0 ? p->batch_divisor : B;
+  const float inv_div = 1.0f / static_cast<float>(div);
+  ln_bwd(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, dtype, param_dtype, pl, s);
+  ln_psgrad_reduce(part, sumsq, B, pl.chunks, d, s);
+  // norms over d, one per sample and tensor (one partial each)
+  clip_factors(sumsq, 1, B, p->C, p->clamp_value, nullptr, factors, norms_gamma, nullptr, s);
+  if (dbeta != nullptr)
+    clip_factors(sumsq + B, 1, B, p->C, p->clamp_value, nullptr, factors + B, norms_beta, nullptr, s);
+  ln_psgrad_finalize(dg_part, factors, dgamma, B, pl.chunks, d, param_dtype, inv_div,
+                     make_noise_key(p, p->param_id), s);
+  if (dbeta != nullptr)
+    ln_psgrad_finalize(db_part, factors + B, dbeta, B, pl.chunks, d, param_dtype, inv_div,
+                       make_noise_key(p, p->param_id2), s);
+  FDP_LAUNCH_OK();
+  return FDP_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,68 @@
+// Host-side launchers shared between the translation units of the library (internal).
+#pragma once
+#include "fdp_common.cuh"
+
+namespace fdp {
+
+// every kernel launch of the library is counted (fdp_launch_count)
+void note_launch(int n = 1);
+
+// ---- generic-shape kernels (any dtype, any size; fp32 FMA accumulation) -----------------------
+int simt_norm_tiles(int n_in, int n_out);
+// partials[b*ntiles + tile] = sum of squares of one 64x64 tile of G_b^T X_b
+void simt_norm_direct(const void* G, const void* X, float* partials, int B, int T, int n_in,
+                      int n_out, int dt, cudaStream_t s);
+// sumsq_b = fixed-order sum of partials[b, 0..nparts); norm = sqrt; factor = clip_factor(norm)
+void clip_factors(const float* partials, int nparts, int B, float C, float clamp, float* norms,
+                  float* factors, float* norms_out, float* factors_out, cudaStream_t s);
+// dW = inv_div * sum_{b,t} c_b G[b,t,:]^T X[b,t,:] + noise, stored as out_dt in `layout`
+void simt_clipped_wgrad(const void* G, const void* X, const float* factors, void* dW, int B, int T,
+                        int n_in, int n_out, int dt, int out_dt, int layout, float inv_div,
+                        NoiseKey nk, cudaStream_t s);
+// dX[rows,n_in] = G[rows,n_out] * W (W [n_out,n_in] if w_layout==FDP_OUT_IN else [n_in,n_out]^T)
+void simt_dgrad(const void* G, const void* W, void* dX, int rows, int n_in, int n_out, int dt,
+                int w_layout, cudaStream_t s);
+
+// ---- bias gradient (HBM-bound; G read once) ----------------------------------------------------
+struct GstatsPlan { int vec, cols_per_block, col_chunks, rows_per_chunk, row_chunks; };
+GstatsPlan gstats_plan(int T, int n_out, int dt);
+void gstats(const void* G, float* colsum_part, float* sq_part, int B, int T, int n_out, int dt,
+            const GstatsPlan& pl, cudaStream_t s);
+void bias_finalize(const float* colsum_part, const float* factors, void* db, int B, int n_out,
+                   int row_chunks, int out_dt, float inv_div, NoiseKey nk, cudaStream_t s);
+
+// ---- LayerNorm -----------------------------------------------------------------------------------
+struct LnPlan { int tpr, cpt, rows_per_block, chunks; bool vec; };
+LnPlan ln_plan(int T, int d, int dt);
+void ln_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+            int rows, int d, float eps, int dt, int pdt, cudaStream_t s);
+void ln_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+            void* dx, float* dg_part, float* db_part, int B, int T, int d, int dt, int pdt,
+            const LnPlan& pl, cudaStream_t s);
+// reduce partials over chunks -> per-sample grads [B,d] (in place in slot 0) and sums of squares
+void ln_psgrad_reduce(float* part, float* sumsq, int B, int chunks, int d, cudaStream_t s);
+void ln_psgrad_finalize(const float* part, const float* factors, void* out, int B, int chunks,
+                        int d, int out_dt, float inv_div, NoiseKey nk, cudaStream_t s);
+
+// ---- tcgen05 / TMEM / TMA kernels (bf16 / fp16, aligned shapes) ---------------------------------
+struct TcPlan {
+  bool ok;          // shapes admit the tensor-core path
+  int algo;         // FDP_NORM_DIRECT or FDP_NORM_GRAM
+  size_t ws_bytes;  // extra workspace (pre-scaled G, partials)
+  int nparts;       // norm partials per sample
+};
+TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo);
+int tc_norms(const void* G, const void* X, float* partials, int* dev_status, int B, int T, int n_in,
+             int n_out, int dt, const TcPlan& pl, cudaStream_t s);
+// Gs[r,:] = factors[r / T] * G[r,:]
+int tc_prescale(const void* G, const float* factors, void* Gs, int B, int T, int n_out, int dt,
+                cudaStream_t s);
+// dW = inv_div * Gs^T X + noise over K = B*T
+int tc_clipped_wgrad(const void* Gs, const void* X, void* dW, int* dev_status, int B, int T, int n_in,
+                     int n_out, int dt, int out_dt, int layout, float inv_div, NoiseKey nk,
+                     cudaStream_t s);
+bool tc_dgrad_ok(int rows, int n_in, int n_out, int dt);
+int tc_dgrad(const void* G, const void* W, void* dX, int* dev_status, int rows, int n_in, int n_out,
+             int dt, int w_layout, cudaStream_t s);
+
+}  // namespace fdp

@@ -1,0 +1,308 @@
+// LayerNorm forward, backward (dx + per-sample dgamma/dbeta partials) and the per-sample
+// clip / mean / noise finalisation.  All HBM-bound: 16-byte loads, each thread owns fixed columns
+// so the per-sample column sums accumulate in registers, no atomics, fixed reduction order.
+#include "fdp_kernels.h"
+
+namespace fdp {
+
+// ---------------------------------------------------------------------------------------------
+// forward: one warp per row; mean, biased variance (two-pass), rstd, y = xhat*gamma + beta
+// (flashdp/core/layernorm_clip.py:11-60)
+// ---------------------------------------------------------------------------------------------
+template <typename Tin, int VEC>
+__global__ void __launch_bounds__(128) ln_fwd_kernel(const Tin* __restrict__ x,
+                                                     const void* __restrict__ gamma,
+                                                     const void* __restrict__ beta,
+                                                     Tin* __restrict__ y, float* __restrict__ mean,
+                                                     float* __restrict__ rstd, int rows, int d,
+                                                     float eps, int pdt) {
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const Tin* xr = x + static_cast<size_t>(row) * d;
+  Tin* yr = y + static_cast<size_t>(row) * d;
+  float s = 0.f;
+  if (VEC > 1) {
+    for (int c = lane * VEC; c < d; c += 32 * VEC) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
+      const Tin* e = reinterpret_cast<const Tin*>(&raw);
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) s += to_f32<Tin>(e[v]);
+    }
+  } else {
+    for (int c = lane; c < d; c += 32) s += to_f32<Tin>(xr[c]);
+  }
+  const float mu = warp_sum(s) / d;
+  float q = 0.f;
+  if (VEC > 1) {
+    for (int c = lane * VEC; c < d; c += 32 * VEC) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
+      const Tin* e = reinterpret_cast<const Tin*>(&raw);
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) { const float t = to_f32<Tin>(e[v]) - mu; q = fmaf(t, t, q); }
+    }
+  } else {
+    for (int c = lane; c < d; c += 32) { const float t = to_f32<Tin>(xr[c]) - mu; q = fmaf(t, t, q); }
+  }
+  const float rs = 1.0f / sqrtf(warp_sum(q) / d + eps);
+  if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+  if (VEC > 1) {
+    for (int c = lane * VEC; c < d; c += 32 * VEC) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
+      const Tin* e = reinterpret_cast<const Tin*>(&raw);
+      uint4 outv;
+      Tin* o = reinterpret_cast<Tin*>(&outv);
+#pragma unroll
+      for (int v = 0; v < VEC; ++v)
+        o[v] = from_f32<Tin>((to_f32<Tin>(e[v]) - mu) * rs * load_as(gamma, pdt, c + v) + load_as(beta, pdt, c + v));
+      *reinterpret_cast<uint4*>(yr + c) = outv;
+    }
+  } else {
+    for (int c = lane; c < d; c += 32)
+      yr[c] = from_f32<Tin>((to_f32<Tin>(xr[c]) - mu) * rs * load_as(gamma, pdt, c) + load_as(beta, pdt, c));
+  }
+}
+
+template <typename Tin>
+static void ln_fwd_t(const void* x, const void* gamma, const void* beta, void* y, float* mean,
+                     float* rstd, int rows, int d, float eps, int pdt, bool vec, cudaStream_t s) {
+  constexpr int V = 16 / sizeof(Tin);
+  dim3 grid(ceil_div(rows, 4));
+  if (vec)
+    ln_fwd_kernel<Tin, V><<<grid, 128, 0, s>>>((const Tin*)x, gamma, beta, (Tin*)y, mean, rstd, rows, d, eps, pdt);
+  else
+    ln_fwd_kernel<Tin, 1><<<grid, 128, 0, s>>>((const Tin*)x, gamma, beta, (Tin*)y, mean, rstd, rows, d, eps, pdt);
+  note_launch();
+}
+
+void ln_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
+            int rows, int d, float eps, int dt, int pdt, cudaStream_t s) {
+  const int V = 16 / static_cast<int>(dtype_size(dt));
+  const bool vec = (d % V == 0) && aligned16(x) && aligned16(y);
+  if (dt == FDP_F32) ln_fwd_t<float>(x, gamma, beta, y, mean, rstd, rows, d, eps, pdt, vec, s);
+  else if (dt == FDP_BF16) ln_fwd_t<__nv_bfloat16>(x, gamma, beta, y, mean, rstd, rows, d, eps, pdt, vec, s);
+  else ln_fwd_t<__half>(x, gamma, beta, y, mean, rstd, rows, d, eps, pdt, vec, s);
+}
+
+// ---------------------------------------------------------------------------------------------
+// backward.  A block of 256 threads is RG = 256/TPR row groups of TPR threads; a row group walks
+// rows of one chunk of one sample, each thread owning NV vectors of VEC columns (vector j at
+// column (j*TPR + t)*VEC).  Per row: xhat, wdy = gamma*dy, the two row means, dx
+// (flashdp/core/layernorm_clip.py:95-103); per thread: running sums of dy*xhat and dy over the
+// rows it saw.  At the end the row groups are summed in fixed order and one partial
+// [sample, chunk, d] is written per tensor.
+// ---------------------------------------------------------------------------------------------
+template <typename Tin, int VEC, int NV, int TPR>
+__global__ void __launch_bounds__(256) ln_bwd_kernel(
+    const Tin* __restrict__ dy, const Tin* __restrict__ x, const void* __restrict__ gamma,
+    const float* __restrict__ mean, const float* __restrict__ rstd, Tin* __restrict__ dx,
+    float* __restrict__ dg_part, float* __restrict__ db_part, int T, int d, int pdt,
+    int rows_per_block, int chunks) {
+  constexpr int RG = 256 / TPR;
+  constexpr int NWG = TPR / 32;  // warps per row group
+  extern __shared__ float sm[];  // [RG][TPR*NV*VEC] for the final cross-group sum
+  __shared__ float2 xch[RG][NWG > 1 ? NWG : 1];
+  const int rg = threadIdx.x / TPR, t = threadIdx.x % TPR;
+  const int lane = threadIdx.x & 31, wig = (threadIdx.x % TPR) >> 5;
+  const int b = blockIdx.y, chunk = blockIdx.x;
+  const int r0 = chunk * rows_per_block, r1 = min(T, r0 + rows_per_block);
+
+  float gam[NV * VEC], accg[NV * VEC], accb[NV * VEC];
+#pragma unroll
+  for (int j = 0; j < NV; ++j)
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) {
+      const int c = (j * TPR + t) * VEC + v;
+      gam[j * VEC + v] = (c < d) ? load_as(gamma, pdt, c) : 0.f;
+      accg[j * VEC + v] = 0.f; accb[j * VEC + v] = 0.f;
+    }
+  const float inv_d = 1.0f / d;
+
+  for (int r = r0 + rg; r < r1; r += RG) {
+    const size_t row = static_cast<size_t>(b) * T + r;
+    const Tin* xr = x + row * d;
+    const Tin* dyr = dy + row * d;
+    const float mu = mean[row], rs = rstd[row];
+    float xh[NV * VEC], wd[NV * VEC];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int c = (j * TPR + t) * VEC;
+      if (VEC > 1) {
+        if (c < d) {
+          const uint4 rx = *reinterpret_cast<const uint4*>(xr + c);
+          const uint4 rd = *reinterpret_cast<const uint4*>(dyr + c);
+          const Tin* ex = reinterpret_cast<const Tin*>(&rx);
+          const Tin* ed = reinterpret_cast<const Tin*>(&rd);
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) {
+            const int i = j * VEC + v;
+            const float xv = (to_f32<Tin>(ex[v]) - mu) * rs, dv = to_f32<Tin>(ed[v]);
+            xh[i] = xv; wd[i] = dv * gam[i];
+            accg[i] = fmaf(dv, xv, accg[i]); accb[i] += dv;
+            s1 = fmaf(xv, wd[i], s1); s2 += wd[i];
+          }
+        } else {
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) { xh[j * VEC + v] = 0.f; wd[j * VEC + v] = 0.f; }
+        }
+      } else {
+        const int i = j;
+        if (c < d) {
+          const float xv = (to_f32<Tin>(xr[c]) - mu) * rs, dv = to_f32<Tin>(dyr[c]);
+          xh[i] = xv; wd[i] = dv * gam[i];
+          accg[i] = fmaf(dv, xv, accg[i]); accb[i] += dv;
+          s1 = fmaf(xv, wd[i], s1); s2 += wd[i];
+        } else { xh[i] = 0.f; wd[i] = 0.f; }
+      }
+    }
+    s1 = warp_sum(s1); s2 = warp_sum(s2);
+    if (NWG > 1) {
+      if (lane == 0) xch[rg][wig] = make_float2(s1, s2);
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + rg), "r"(TPR) : "memory");
+      s1 = 0.f; s2 = 0.f;
+#pragma unroll
+      for (int w = 0; w < NWG; ++w) { s1 += xch[rg][w].x; s2 += xch[rg][w].y; }
+      asm volatile("bar.sync %0, %1;" ::"r"(1 + rg), "r"(TPR) : "memory");
+    }
+    if (dx != nullptr) {
+      const float c1 = s1 * inv_d, c2 = s2 * inv_d;
+      Tin* dxr = dx + row * d;
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const int c = (j * TPR + t) * VEC;
+        if (c >= d) continue;
+        if (VEC > 1) {
+          uint4 outv;
+          Tin* o = reinterpret_cast<Tin*>(&outv);
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) {
+            const int i = j * VEC + v;
+            o[v] = from_f32<Tin>((wd[i] - (xh[i] * c1 + c2)) * rs);
+          }
+          *reinterpret_cast<uint4*>(dxr + c) = outv;
+        } else {
+          dxr[c] = from_f32<Tin>((wd[j] - (xh[j] * c1 + c2)) * rs);
+        }
+      }
+    }
+  }
+
+  // cross-row-group sum, fixed order, one tensor at a time through the same shared buffer
+  constexpr int CPG = TPR * NV * VEC;  // columns covered by a row group
+  float* outp[2] = {dg_part, db_part};
+#pragma unroll
+  for (int which = 0; which < 2; ++which) {
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < NV; ++j)
+#pragma unroll
+      for (int v = 0; v < VEC; ++v)
+        sm[rg * CPG + (j * TPR + t) * VEC + v] = which == 0 ? accg[j * VEC + v] : accb[j * VEC + v];
+    __syncthreads();
+    float* dst = outp[which] + (static_cast<size_t>(b) * chunks + chunk) * d;
+    for (int c = threadIdx.x; c < d; c += 256) {
+      float tot = 0.f;
+#pragma unroll
+      for (int g = 0; g < RG; ++g) tot += sm[g * CPG + c];
+      dst[c] = tot;
+    }
+  }
+}
+
+LnPlan ln_plan(int T, int d, int dt) {
+  LnPlan pl;
+  const int V = 16 / static_cast<int>(dtype_size(dt));
+  pl.vec = (d % V == 0);
+  const int vec = pl.vec ? V : 1;
+  const int nv_max = pl.vec ? (32 / V) : 32;  // 32 columns per thread at most
+  pl.cpt = nv_max * vec;
+  pl.tpr = 32;
+  while (pl.tpr < 256 && pl.tpr * pl.cpt < d) pl.tpr *= 2;
+  pl.rows_per_block = 32;
+  pl.chunks = ceil_div(T, pl.rows_per_block);
+  return pl;
+}
+
+template <typename Tin, int VEC, int NV>
+static void ln_bwd_launch(const void* dy, const void* x, const void* gamma, const float* mean,
+                          const float* rstd, void* dx, float* dg_part, float* db_part, int B, int T,
+                          int d, int pdt, const LnPlan& pl, cudaStream_t s) {
+  dim3 grid(pl.chunks, B);
+  const size_t smem = static_cast<size_t>(256) * NV * VEC * sizeof(float);
+#define FDP_LN_CASE(TPRV)                                                                           \
+  ln_bwd_kernel<Tin, VEC, NV, TPRV><<<grid, 256, smem, s>>>(                                         \
+      (const Tin*)dy, (const Tin*)x, gamma, mean, rstd, (Tin*)dx, dg_part, db_part, T, d, pdt,      \
+      pl.rows_per_block, pl.chunks)
+  switch (pl.tpr) {
+    case 32: FDP_LN_CASE(32); break;
+    case 64: FDP_LN_CASE(64); break;
+    case 128: FDP_LN_CASE(128); break;
+    default: FDP_LN_CASE(256); break;
+  }
+#undef FDP_LN_CASE
+  note_launch();
+}
+
+void ln_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
+            void* dx, float* dg_part, float* db_part, int B, int T, int d, int dt, int pdt,
+            const LnPlan& pl, cudaStream_t s) {
+  const bool vec = pl.vec && aligned16(dy) && aligned16(x) && (dx == nullptr || aligned16(dx));
+  if (dt == FDP_F32) {
+    if (vec) ln_bwd_launch<float, 4, 8>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s);
+    else ln_bwd_launch<float, 1, 32>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s);
+  } else if (dt == FDP_BF16) {
+    if (vec) ln_bwd_launch<__nv_bfloat16, 8, 4>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s);
+    else ln_bwd_launch<__nv_bfloat16, 1, 32>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s);
+  } else {
+    if (vec) ln_bwd_launch<__half, 8, 4>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s);
+    else ln_bwd_launch<__half, 1, 32>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+// per-sample finalisation.  `part` holds [2 tensors][B][chunks][d]; the reduced per-sample
+// gradient lands in chunk slot 0.  sumsq[tensor*B + b] = ||per-sample grad||^2 over d.
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) ln_psgrad_reduce_kernel(float* __restrict__ part,
+                                                               float* __restrict__ sumsq, int chunks,
+                                                               int d) {
+  __shared__ float red[32];
+  float* p = part + static_cast<size_t>(blockIdx.x) * chunks * d;  // blockIdx.x = tensor*B + b
+  float sq = 0.f;
+  for (int c = threadIdx.x; c < d; c += 256) {
+    float t = 0.f;
+    for (int k = 0; k < chunks; ++k) t += p[static_cast<size_t>(k) * d + c];
+    p[c] = t;
+    sq = fmaf(t, t, sq);
+  }
+  sq = block_sum(sq, red);
+  if (threadIdx.x == 0) sumsq[blockIdx.x] = sq;
+}
+
+void ln_psgrad_reduce(float* part, float* sumsq, int B, int chunks, int d, cudaStream_t s) {
+  ln_psgrad_reduce_kernel<<<2 * B, 256, 0, s>>>(part, sumsq, chunks, d);
+  note_launch();
+}
+
+__global__ void __launch_bounds__(256) ln_psgrad_finalize_kernel(const float* __restrict__ part,
+                                                                 const float* __restrict__ factors,
+                                                                 void* __restrict__ out, int B,
+                                                                 int chunks, int d, int out_dt,
+                                                                 float inv_div, NoiseKey nk) {
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  if (c >= d) return;
+  float acc = 0.f;
+  for (int b = 0; b < B; ++b) acc = fmaf(factors[b], part[static_cast<size_t>(b) * chunks * d + c], acc);
+  float v = acc * inv_div;
+  if (nk.std != 0.f) v += noise_at(nk, c);
+  store_as(out, out_dt, c, v);
+}
+
+void ln_psgrad_finalize(const float* part, const float* factors, void* out, int B, int chunks,
+                        int d, int out_dt, float inv_div, NoiseKey nk, cudaStream_t s) {
+  ln_psgrad_finalize_kernel<<<ceil_div(d, 256), 256, 0, s>>>(part, factors, out, B, chunks, d, out_dt, inv_div, nk);
+  note_launch();
+}
+
+}  // namespace fdp

@@ -1,0 +1,300 @@
+// Generic-shape kernels: per-sample norm, clip factors, clipped-sum weight gradient, input
+// gradient and the bias-gradient reduction.  Any dtype, any size, true fp32 FMA accumulation
+// (the 1e-5 fp32 tolerance rules out TF32).  The aligned bf16/fp16 shapes take the tcgen05
+// kernels instead; these cover fp32 and ragged shapes.
+#include "fdp_kernels.h"
+
+namespace fdp {
+
+constexpr int TM = 64, TN = 64, TK = 16;  // block tile; 256 threads, 4x4 outputs per thread
+
+// acc[i][j] += sum_k A(k, m0+4*ty+i) * B(k, n0+4*tx+j), operands addressed through strides so the
+// same body serves the weight gradient (contraction over rows) and the input gradient.
+// SCALED multiplies A(k, .) by factors[k / T] (the per-sample clip factor of row k).
+template <typename Tin, bool SCALED>
+__device__ __forceinline__ void simt_tile(const Tin* __restrict__ A, long sAk, long sAm,
+                                          const Tin* __restrict__ Bm, long sBk, long sBn, int K,
+                                          int M, int N, int m0, int n0,
+                                          const float* __restrict__ factors, int T,
+                                          float acc[4][4]) {
+  __shared__ __align__(16) float As[TK][TM];
+  __shared__ __align__(16) float Bs[TK][TN];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  for (int k0 = 0; k0 < K; k0 += TK) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int idx = tid + i * 256;
+      int kk, mm;
+      if (sAm == 1) { kk = idx >> 6; mm = idx & 63; } else { mm = idx >> 4; kk = idx & 15; }
+      const int k = k0 + kk, m = m0 + mm;
+      float v = 0.f;
+      if (k < K && m < M) {
+        v = to_f32<Tin>(A[k * sAk + m * sAm]);
+        if (SCALED) v *= factors[k / T];
+      }
+      As[kk][mm] = v;
+      int nn;
+      if (sBn == 1) { kk = idx >> 6; nn = idx & 63; } else { nn = idx >> 4; kk = idx & 15; }
+      const int kb = k0 + kk, n = n0 + nn;
+      Bs[kk][nn] = (kb < K && n < N) ? to_f32<Tin>(Bm[kb * sBk + n * sBn]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < TK; ++kk) {
+      const float4 a = *reinterpret_cast<const float4*>(&As[kk][ty * 4]);
+      const float4 b = *reinterpret_cast<const float4*>(&Bs[kk][tx * 4]);
+      const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+}
+
+// ---- per-sample norm, direct: one block = one 64x64 tile of G_b^T X_b, squared and summed -------
+template <typename Tin>
+__global__ void __launch_bounds__(256) simt_norm_direct_kernel(const Tin* __restrict__ G,
+                                                               const Tin* __restrict__ X,
+                                                               float* __restrict__ partials, int T,
+                                                               int n_in, int n_out) {
+  __shared__ float red[32];
+  const int b = blockIdx.z;
+  const Tin* Gb = G + static_cast<size_t>(b) * T * n_out;
+  const Tin* Xb = X + static_cast<size_t>(b) * T * n_in;
+  float acc[4][4] = {};
+  simt_tile<Tin, false>(Gb, n_out, 1, Xb, n_in, 1, T, n_out, n_in, blockIdx.y * TM, blockIdx.x * TN,
+                        nullptr, 1, acc);
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) s = fmaf(acc[i][j], acc[i][j], s);
+  s = block_sum(s, red);
+  if (threadIdx.x == 0)
+    partials[(static_cast<size_t>(b) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x] = s;
+}
+
+int simt_norm_tiles(int n_in, int n_out) { return ceil_div(n_in, TN) * ceil_div(n_out, TM); }
+
+void simt_norm_direct(const void* G, const void* X, float* partials, int B, int T, int n_in,
+                      int n_out, int dt, cudaStream_t s) {
+  dim3 grid(ceil_div(n_in, TN), ceil_div(n_out, TM), B);
+  if (dt == FDP_F32)
+    simt_norm_direct_kernel<float><<<grid, 256, 0, s>>>((const float*)G, (const float*)X, partials, T, n_in, n_out);
+  else if (dt == FDP_BF16)
+    simt_norm_direct_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)G, (const __nv_bfloat16*)X, partials, T, n_in, n_out);
+  else
+    simt_norm_direct_kernel<__half><<<grid, 256, 0, s>>>((const __half*)G, (const __half*)X, partials, T, n_in, n_out);
+  note_launch();
+}
+
+// ---- clip factors --------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) clip_factors_kernel(const float* __restrict__ partials,
+                                                           int nparts, float C, float clamp,
+                                                           float* norms, float* factors,
+                                                           float* norms_out, float* factors_out) {
+  __shared__ float red[32];
+  const int b = blockIdx.x;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < nparts; i += blockDim.x) s += partials[static_cast<size_t>(b) * nparts + i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) {
+    const float n = sqrtf(fmaxf(s, 0.f));
+    const float f = clip_factor(n, C, clamp);
+    if (norms) norms[b] = n;
+    factors[b] = f;
+    if (norms_out) norms_out[b] = n;
+    if (factors_out) factors_out[b] = f;
+  }
+}
+
+void clip_factors(const float* partials, int nparts, int B, float C, float clamp, float* norms,
+                  float* factors, float* norms_out, float* factors_out, cudaStream_t s) {
+  clip_factors_kernel<<<B, 256, 0, s>>>(partials, nparts, C, clamp, norms, factors, norms_out, factors_out);
+  note_launch();
+}
+
+// ---- clipped-sum weight gradient: one GEMM over K = B*T with c_b folded into the G operand ------
+template <typename Tin>
+__global__ void __launch_bounds__(256) simt_clipped_wgrad_kernel(
+    const Tin* __restrict__ G, const Tin* __restrict__ X, const float* __restrict__ factors,
+    void* __restrict__ dW, int B, int T, int n_in, int n_out, int out_dt, int layout, float inv_div,
+    NoiseKey nk) {
+  float acc[4][4] = {};
+  const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+  simt_tile<Tin, true>(G, n_out, 1, X, n_in, 1, B * T, n_out, n_in, m0, n0, factors, T, acc);
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= n_out) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= n_in) continue;
+      const size_t idx = (layout == FDP_OUT_IN) ? static_cast<size_t>(m) * n_in + n
+                                                : static_cast<size_t>(n) * n_out + m;
+      float v = acc[i][j] * inv_div;
+      if (nk.std != 0.f) v += noise_at(nk, idx);
+      store_as(dW, out_dt, idx, v);
+    }
+  }
+}
+
+void simt_clipped_wgrad(const void* G, const void* X, const float* factors, void* dW, int B, int T,
+                        int n_in, int n_out, int dt, int out_dt, int layout, float inv_div,
+                        NoiseKey nk, cudaStream_t s) {
+  dim3 grid(ceil_div(n_in, TN), ceil_div(n_out, TM));
+  if (dt == FDP_F32)
+    simt_clipped_wgrad_kernel<float><<<grid, 256, 0, s>>>((const float*)G, (const float*)X, factors, dW, B, T, n_in, n_out, out_dt, layout, inv_div, nk);
+  else if (dt == FDP_BF16)
+    simt_clipped_wgrad_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)G, (const __nv_bfloat16*)X, factors, dW, B, T, n_in, n_out, out_dt, layout, inv_div, nk);
+  else
+    simt_clipped_wgrad_kernel<__half><<<grid, 256, 0, s>>>((const __half*)G, (const __half*)X, factors, dW, B, T, n_in, n_out, out_dt, layout, inv_div, nk);
+  note_launch();
+}
+
+// ---- input gradient: dX[r,i] = sum_o G[r,o] W(o,i) ------------------------------------------------
+template <typename Tin>
+__global__ void __launch_bounds__(256) simt_dgrad_kernel(const Tin* __restrict__ G,
+                                                         const Tin* __restrict__ W,
+                                                         Tin* __restrict__ dX, int rows, int n_in,
+                                                         int n_out, int w_layout) {
+  float acc[4][4] = {};
+  const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+  // A(k=o, m=r) = G[r*n_out + o];  B(k=o, n=i) = W[o*n_in + i] (OUT_IN) or W[i*n_out + o] (IN_OUT)
+  const long sBk = (w_layout == FDP_OUT_IN) ? n_in : 1, sBn = (w_layout == FDP_OUT_IN) ? 1 : n_out;
+  simt_tile<Tin, false>(G, 1, n_out, W, sBk, sBn, n_out, rows, n_in, m0, n0, nullptr, 1, acc);
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < n_in) dX[static_cast<size_t>(m) * n_in + n] = from_f32<Tin>(acc[i][j]);
+    }
+  }
+}
+
+void simt_dgrad(const void* G, const void* W, void* dX, int rows, int n_in, int n_out, int dt,
+                int w_layout, cudaStream_t s) {
+  dim3 grid(ceil_div(n_in, TN), ceil_div(rows, TM));
+  if (dt == FDP_F32)
+    simt_dgrad_kernel<float><<<grid, 256, 0, s>>>((const float*)G, (const float*)W, (float*)dX, rows, n_in, n_out, w_layout);
+  else if (dt == FDP_BF16)
+    simt_dgrad_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)G, (const __nv_bfloat16*)W, (__nv_bfloat16*)dX, rows, n_in, n_out, w_layout);
+  else
+    simt_dgrad_kernel<__half><<<grid, 256, 0, s>>>((const __half*)G, (const __half*)W, (__half*)dX, rows, n_in, n_out, w_layout);
+  note_launch();
+}
+
+// ---- bias gradient statistics: one read of G -> per-sample sum of squares + column sums ---------
+// Block = 32 column-threads x 8 row-threads.  A column-thread owns VEC adjacent columns (one
+// 16-byte load per row); the 8 row-threads stride over the rows of the chunk.  Partials are
+// combined in a fixed order, so results are bit-reproducible.
+template <typename Tin, int VEC>
+__global__ void __launch_bounds__(256) gstats_kernel(const Tin* __restrict__ G,
+                                                     float* __restrict__ colsum_part,
+                                                     float* __restrict__ sq_part, int T, int n_out,
+                                                     int rows_per_chunk, int vec_ok) {
+  __shared__ float cs[8][32 * VEC];
+  __shared__ float red[32];
+  const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
+  const int b = blockIdx.z, rc = blockIdx.y;
+  const int c0 = (blockIdx.x * 32 + x) * VEC;
+  const int r0 = rc * rows_per_chunk, r1 = min(T, r0 + rows_per_chunk);
+  const Tin* Gb = G + static_cast<size_t>(b) * T * n_out;
+  float acc[VEC];
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) acc[v] = 0.f;
+  float sq = 0.f;
+  if (vec_ok) {
+    if (c0 < n_out) {
+      for (int r = r0 + y; r < r1; r += 8) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(Gb + static_cast<size_t>(r) * n_out + c0));
+        const Tin* e = reinterpret_cast<const Tin*>(&raw);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) { const float f = to_f32<Tin>(e[v]); acc[v] += f; sq = fmaf(f, f, sq); }
+      }
+    }
+  } else {
+    for (int r = r0 + y; r < r1; r += 8) {
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) {
+        if (c0 + v < n_out) {
+          const float f = to_f32<Tin>(Gb[static_cast<size_t>(r) * n_out + c0 + v]);
+          acc[v] += f; sq = fmaf(f, f, sq);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < VEC; ++v) cs[y][x * VEC + v] = acc[v];
+  sq = block_sum(sq, red);  // contains the __syncthreads that publishes cs
+  if (threadIdx.x == 0)
+    sq_part[(static_cast<size_t>(b) * gridDim.y + rc) * gridDim.x + blockIdx.x] = sq;
+  for (int c = threadIdx.x; c < 32 * VEC; c += 256) {
+    const int col = blockIdx.x * 32 * VEC + c;
+    if (col < n_out) {
+      float t = 0.f;
+#pragma unroll
+      for (int yy = 0; yy < 8; ++yy) t += cs[yy][c];
+      colsum_part[(static_cast<size_t>(b) * gridDim.y + rc) * n_out + col] = t;
+    }
+  }
+}
+
+GstatsPlan gstats_plan(int T, int n_out, int dt) {
+  GstatsPlan pl;
+  pl.vec = (dt == FDP_F32) ? 4 : 8;
+  pl.cols_per_block = 32 * pl.vec;
+  pl.col_chunks = ceil_div(n_out, pl.cols_per_block);
+  pl.rows_per_chunk = 64;
+  pl.row_chunks = ceil_div(T, pl.rows_per_chunk);
+  return pl;
+}
+
+void gstats(const void* G, float* colsum_part, float* sq_part, int B, int T, int n_out, int dt,
+            const GstatsPlan& pl, cudaStream_t s) {
+  dim3 grid(pl.col_chunks, pl.row_chunks, B);
+  const int vec_ok = (n_out % pl.vec == 0) && aligned16(G);
+  if (dt == FDP_F32)
+    gstats_kernel<float, 4><<<grid, 256, 0, s>>>((const float*)G, colsum_part, sq_part, T, n_out, pl.rows_per_chunk, vec_ok);
+  else if (dt == FDP_BF16)
+    gstats_kernel<__nv_bfloat16, 8><<<grid, 256, 0, s>>>((const __nv_bfloat16*)G, colsum_part, sq_part, T, n_out, pl.rows_per_chunk, vec_ok);
+  else
+    gstats_kernel<__half, 8><<<grid, 256, 0, s>>>((const __half*)G, colsum_part, sq_part, T, n_out, pl.rows_per_chunk, vec_ok);
+  note_launch();
+}
+
+// db[o] = inv_div * sum_b c_b * sum_rc colsum_part[b,rc,o] + noise
+__global__ void __launch_bounds__(256) bias_finalize_kernel(const float* __restrict__ colsum_part,
+                                                            const float* __restrict__ factors,
+                                                            void* __restrict__ db, int B, int n_out,
+                                                            int row_chunks, int out_dt,
+                                                            float inv_div, NoiseKey nk) {
+  const int o = blockIdx.x * blockDim.x + threadIdx.x;
+  if (o >= n_out) return;
+  float acc = 0.f;
+  for (int b = 0; b < B; ++b) {
+    float t = 0.f;
+    for (int rc = 0; rc < row_chunks; ++rc)
+      t += colsum_part[(static_cast<size_t>(b) * row_chunks + rc) * n_out + o];
+    acc = fmaf(factors[b], t, acc);
+  }
+  float v = acc * inv_div;
+  if (nk.std != 0.f) v += noise_at(nk, o);
+  store_as(db, out_dt, o, v);
+}
+
+void bias_finalize(const float* colsum_part, const float* factors, void* db, int B, int n_out,
+                   int row_chunks, int out_dt, float inv_div, NoiseKey nk, cudaStream_t s) {
+  bias_finalize_kernel<<<ceil_div(n_out, 256), 256, 0, s>>>(colsum_part, factors, db, B, n_out, row_chunks, out_dt, inv_div, nk);
+  note_launch();
+}
+
+}  // namespace fdp

@@ -1,0 +1,616 @@
+// Tensor-core path for bf16 / fp16: one persistent, warp-specialised GEMM kernel template built
+// on TMA (cp.async.bulk.tensor, 128-byte swizzle) -> shared-memory ring -> tcgen05.mma with fp32
+// accumulators in TMEM -> tcgen05.ld epilogue.  Instances:
+//   wgrad   A,B MN-major   dW = scale * Gs^T X + noise        (K = B*T, Gs = c_b-scaled G)
+//   direct  A,B MN-major   per-sample ||G_b^T X_b||_F^2 tiles, squared in the epilogue, not stored
+//   gram    A,B K-major    sum_{t,s} (G_b G_b^T)_{ts} (X_b X_b^T)_{ts}, two accumulators in TMEM
+//   dgrad   A K-major, B MN- or K-major   dX = G W
+// Roles in a CTA of 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner,
+// warps 2-5 = epilogue (one TMEM lane quarter each).  Every mbarrier wait is bounded: when one
+// runs out the CTA records a code in the status word, drains and leaves.
+// No TMA load here uses cluster multicast.
+#include <cuda.h>
+#include <mutex>
+
+#include "fdp_kernels.h"
+
+namespace fdp {
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4, UMMA_K = 16;
+constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
+constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int BAR_BYTES = 256;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + BAR_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // about a second
+
+enum { EPI_STORE = 0, EPI_SUMSQ = 1, EPI_GRAM = 2 };
+
+struct TcArgs {
+  int M, N;             // extents of the output space of one batch (masks)
+  int tiles_m, tiles_n; // tile grid of one batch (EPI_GRAM: tiles_m = t-blocks of 128, tiles_n = s-blocks of 256)
+  int tiles_per_batch;
+  int batch;
+  int k_stages, k_stages2;  // K loop of operand pair 1 (and pair 2 for EPI_GRAM)
+  int batch_rows;           // rows of one batch along the row coordinate of the tensor maps
+  void* out; int out_dt; long long ld_out; float scale; NoiseKey nk;
+  float* partials;
+  int T;
+  int* status;
+  uint32_t idesc;
+};
+
+// ---- PTX wrappers ---------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// bounded wait; false when it gave up (own limit or another role's abort)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int code) {
+  if (mbar_try(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
+    if (mbar_try(bar, parity)) return true;
+    if (*abort_flag != 0) return false;
+    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+      *abort_flag = 1;
+      atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t r[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets in
+// 16-byte units, version 1, 128-byte swizzle
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr >> 4) & 0x3FFF);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= static_cast<uint64_t>(1) << 46;  // descriptor version of sm_100
+  d |= static_cast<uint64_t>(2) << 61;  // SWIZZLE_128B
+  return d;
+}
+// Descriptor of the k16-th UMMA_K slice of an operand stage.
+//  MN-major: 64-element (128 B) MN chunks of BK rows each, chunk stride BK*128 B (leading offset),
+//            8-row groups 1024 B apart (stride offset); a K=16 slice is 16 rows = 2048 B further.
+//  K-major : rows of 128 B (64 K elements), 8-row groups 1024 B apart; a K=16 slice is 32 B further.
+template <bool MN_MAJOR>
+__device__ __forceinline__ uint64_t operand_desc(uint32_t stage_base, int k16) {
+  if (MN_MAJOR) return make_desc(stage_base + k16 * (UMMA_K * 128), BK * 128, 1024);
+  return make_desc(stage_base + k16 * (UMMA_K * 2), 0, 1024);
+}
+
+// ---- the kernel ---------------------------------------------------------------------------------------
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
+               const TcArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* gen_base = smem_raw + (base - raw_addr);
+  const uint32_t bar_base = base + STAGES * STAGE_BYTES;
+  uint8_t* bar_gen = gen_base + STAGES * STAGE_BYTES;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 4);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * (2 * STAGES + 5));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * (2 * STAGES + 5) + 4);
+  float* red = reinterpret_cast<float*>(bar_gen + 8 * (2 * STAGES + 6));  // 4 floats
+
+  constexpr int NUM_ACC = (EPI == EPI_GRAM) ? 1 : 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = args.batch * args.tiles_per_batch;
+  const int kst_total = args.k_stages + (EPI == EPI_GRAM ? args.k_stages2 : 0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+    mbar_init(drain_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // tile -> (batch, m0, n0); EPI_GRAM enumerates the (t-block, s-block) pairs that touch s >= t
+  auto decode = [&](int tile, int& b, int& m0, int& n0) {
+    b = tile / args.tiles_per_batch;
+    int q = tile - b * args.tiles_per_batch;
+    if (EPI == EPI_GRAM) {
+      int j = 0;
+      while (true) {
+        const int cnt = min(2 * j + 2, args.tiles_m);
+        if (q < cnt) break;
+        q -= cnt; ++j;
+      }
+      m0 = q * BM; n0 = j * BN;
+    } else {
+      m0 = (q % args.tiles_m) * BM;
+      n0 = (q / args.tiles_m) * BN;
+    }
+  };
+
+  if (warp == 0) {
+    // ================= TMA producer =================
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        int b, m0, n0;
+        decode(tile, b, m0, n0);
+        const int row0 = b * args.batch_rows;
+        for (int ks = 0; ks < kst_total; ++ks) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 1)) { ok = false; break; }
+          const bool second = (EPI == EPI_GRAM) && ks >= args.k_stages;
+          const CUtensorMap* ma = second ? &tmA2 : &tmA;
+          const CUtensorMap* mb = second ? &tmB2 : &tmB;
+          const int k0 = (second ? ks - args.k_stages : ks) * BK;
+          const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
+          mbar_expect_tx(full_bar(stage), STAGE_BYTES);
+          if (A_MN) {
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * (BK * 128), ma, m0 + 64 * i, row0 + k0, full_bar(stage));
+          } else {
+            tma_load_2d(sa, ma, k0, row0 + m0, full_bar(stage));
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), mb, n0 + 64 * j, row0 + k0, full_bar(stage));
+          } else {
+            tma_load_2d(sb, mb, k0, row0 + n0, full_bar(stage));
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // wait (bounded) for the copies already in flight before the CTA may leave
+        for (int s = 0; s < STAGES; ++s) {
+          const long long t0 = clock64();
+          const uint32_t ph = (s < stage) ? phase : (phase ^ 1u);
+          while (!mbar_try(full_bar(s), ph) && clock64() - t0 < WAIT_LIMIT_CYCLES / 8) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ================= MMA issuer =================
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+        const int acc = it % NUM_ACC;
+        const uint32_t acc_phase = (it / NUM_ACC) & 1u;
+        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, args.status, 2)) { ok = false; break; }
+        tc_fence_after();
+        for (int ks = 0; ks < kst_total; ++ks) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 3)) { ok = false; break; }
+          tc_fence_after();
+          const bool second = (EPI == EPI_GRAM) && ks >= args.k_stages;
+          const uint32_t d = tmem_base + (EPI == EPI_GRAM ? (second ? BN : 0) : acc * BN);
+          const bool first_stage = second ? (ks == args.k_stages) : (ks == 0);
+          const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
+#pragma unroll
+          for (int k16 = 0; k16 < BK / UMMA_K; ++k16)
+            tc_mma(d, operand_desc<A_MN>(sa, k16), operand_desc<B_MN>(sb, k16), args.idesc,
+                   (first_stage && k16 == 0) ? 0u : 1u);
+          tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tc_commit(tfull_bar(acc));
+      }
+      if (!ok) {
+        // let MMAs already issued finish before TMEM is released
+        tc_commit(drain_bar);
+        const long long t0 = clock64();
+        while (!mbar_try(drain_bar, 0) && clock64() - t0 < WAIT_LIMIT_CYCLES / 8) {}
+      }
+    }
+  } else {
+    // ================= epilogue: warps 2..5, TMEM lane quarter = warp % 4 =================
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      int b, m0, n0;
+      decode(tile, b, m0, n0);
+      const int acc = it % NUM_ACC;
+      const uint32_t acc_phase = (it / NUM_ACC) & 1u;
+      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, args.status, 4)) { ok = false; break; }
+      tc_fence_after();
+      const uint32_t tbase = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (EPI == EPI_GRAM ? 0 : acc * BN);
+      float part = 0.f;
+      if (EPI == EPI_STORE) {
+        const int m = m0 + row;
+        const size_t esz = dtype_size(args.out_dt);
+        const bool vec_ok = (args.ld_out * esz) % 16 == 0;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tc_ld32(tbase + c, r);
+          tc_wait_ld();
+          const int n = n0 + c;
+          if (m < args.M && n < args.N) {
+            const size_t idx0 = static_cast<size_t>(m) * args.ld_out + n;
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * args.scale;
+            if (args.nk.std != 0.f) {
+              if ((idx0 & 3) == 0) {
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                  float z[4];
+                  noise_group(args.nk, (idx0 >> 2) + g, z);
+                  v[4 * g] += z[0]; v[4 * g + 1] += z[1]; v[4 * g + 2] += z[2]; v[4 * g + 3] += z[3];
+                }
+              } else {
+#pragma unroll 1
+                for (int j = 0; j < 32; ++j) v[j] += noise_at(args.nk, idx0 + j);
+              }
+            }
+            if (n + 32 <= args.N && vec_ok) {
+              if (args.out_dt == FDP_F32) {
+                float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(args.out) + idx0);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) o[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+              } else {
+                uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(args.out) + idx0);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  uint32_t w[4];
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    const float lo = v[8 * j + 2 * e], hi = v[8 * j + 2 * e + 1];
+                    if (args.out_dt == FDP_BF16) {
+                      __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+                      w[e] = *reinterpret_cast<uint32_t*>(&h);
+                    } else {
+                      __half2 h = __floats2half2_rn(lo, hi);
+                      w[e] = *reinterpret_cast<uint32_t*>(&h);
+                    }
+                  }
+                  o[j] = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+              }
+            } else {
+#pragma unroll 1
+              for (int j = 0; j < 32; ++j)
+                if (n + j < args.N) store_as(args.out, args.out_dt, idx0 + j, v[j]);
+            }
+          }
+        }
+      } else if (EPI == EPI_SUMSQ) {
+        // rows / columns outside the matrix were zero-filled by TMA, so they add nothing
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tc_ld32(tbase + c, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) { const float f = __uint_as_float(r[j]); part = fmaf(f, f, part); }
+        }
+      } else {
+        // weight 2 above the diagonal, 1 on it, 0 below it and outside the sample
+        const int t = m0 + row;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t p[32], q[32];
+          tc_ld32(tbase + c, p);
+          tc_ld32(tbase + BN + c, q);
+          tc_wait_ld();
+          if (t < args.T) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int s = n0 + c + j;
+              const float w = (s >= args.T || s < t) ? 0.f : (s == t ? 1.f : 2.f);
+              part = fmaf(w * __uint_as_float(p[j]), __uint_as_float(q[j]), part);
+            }
+          }
+        }
+      }
+      // accumulator drained: hand it back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (EPI != EPI_STORE) {
+        part = warp_sum(part);
+        if (lane == 0) red[quarter] = part;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) args.partials[tile] = (red[0] + red[1]) + (red[2] + red[3]);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      }
+    }
+  }
+
+  // ================= teardown =================
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ---- c_b pre-scale: Gs[r,:] = c[r / T] * G[r,:] (HBM-bound, 16-byte vectors) ------------------------
+template <typename Tin>
+__global__ void __launch_bounds__(256) prescale_kernel(const Tin* __restrict__ G, const float* __restrict__ factors,
+                                                       Tin* __restrict__ Gs, size_t nvec, int vec_per_sample) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const float c = factors[i / vec_per_sample];
+    const uint4 raw = __ldg(reinterpret_cast<const uint4*>(G) + i);
+    const Tin* e = reinterpret_cast<const Tin*>(&raw);
+    uint4 outv;
+    Tin* o = reinterpret_cast<Tin*>(&outv);
+#pragma unroll
+    for (int v = 0; v < 8; ++v) o[v] = from_f32<Tin>(to_f32<Tin>(e[v]) * c);
+    reinterpret_cast<uint4*>(Gs)[i] = outv;
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static std::mutex mu;
+  static EncodeTiledFn fn = nullptr;
+  std::lock_guard<std::mutex> lk(mu);
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+    else
+      cudaGetLastError();
+  }
+  return fn;
+}
+
+// 2-D map over a row-major [rows, cols] matrix of 16-bit elements, 128-byte swizzle, zero fill
+bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_cols,
+              uint32_t box_rows, int dt) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = fn(m, dt == FDP_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2,
+                        const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+uint32_t make_idesc(int dt, bool a_mn, bool b_mn) {
+  uint32_t d = 0;
+  d |= 1u << 4;                                   // accumulator format: F32
+  d |= (dt == FDP_BF16 ? 1u : 0u) << 7;           // A format
+  d |= (dt == FDP_BF16 ? 1u : 0u) << 10;          // B format
+  d |= (a_mn ? 1u : 0u) << 15;                    // A major: 1 = MN-major
+  d |= (b_mn ? 1u : 0u) << 16;                    // B major
+  d |= static_cast<uint32_t>(BN >> 3) << 17;      // N
+  d |= static_cast<uint32_t>(BM >> 4) << 24;      // M
+  return d;
+}
+
+int sm_count() {
+  static std::mutex mu;
+  static int cache[64];
+  static bool have[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return 148; }
+  std::lock_guard<std::mutex> lk(mu);
+  if (!have[dev]) {
+    int n = 148;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) { cudaGetLastError(); n = 148; }
+    cache[dev] = n; have[dev] = true;
+  }
+  return cache[dev];
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, const CUtensorMap& b2,
+           const TcArgs& args, cudaStream_t s) {
+  // the opt-in to >48 KiB of dynamic shared memory is per device
+  static std::mutex mu;
+  static bool done[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return FDP_ERR_LAUNCH; }
+  {
+    std::lock_guard<std::mutex> lk(mu);
+    if (!done[dev]) {
+      if (cudaFuncSetAttribute(tc_gemm_kernel<A_MN, B_MN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               SMEM_BYTES) != cudaSuccess) {
+        cudaGetLastError();
+        return FDP_ERR_LAUNCH;
+      }
+      done[dev] = true;
+    }
+  }
+  const int total = args.batch * args.tiles_per_batch;
+  const int grid = total < sm_count() ? total : sm_count();
+  tc_gemm_kernel<A_MN, B_MN, EPI><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(a, b, a2, b2, args);
+  note_launch();
+  return cudaPeekAtLastError() == cudaSuccess ? FDP_OK : (cudaGetLastError(), FDP_ERR_LAUNCH);
+}
+
+int gram_tiles(int T) {
+  const int tm = ceil_div(T, BM), tn = ceil_div(T, BN);
+  int n = 0;
+  for (int j = 0; j < tn; ++j) n += (2 * j + 2 < tm) ? 2 * j + 2 : tm;
+  return n;
+}
+
+}  // namespace
+
+// The tensor-core path needs 16-bit inputs, row pitches that are multiples of 16 bytes, and
+// matrices large enough that the 128x256 tile is not mostly padding.
+TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo) {
+  TcPlan p; p.ok = false; p.algo = FDP_NORM_DIRECT; p.ws_bytes = 0; p.nparts = 0;
+  if (dt != FDP_BF16 && dt != FDP_F16) return p;
+  if (n_in % 8 != 0 || n_out % 8 != 0 || n_in < 128 || n_out < 128 || T < 64) return p;
+  const bool direct_ok = (T % BK == 0);   // a K stage must not run into the next sample's rows
+  // tensor-core work of the two norm algorithms, in padded tile units
+  const double direct = 2.0 * T * (ceil_div(n_out, BM) * BM) * static_cast<double>(ceil_div(n_in, BN) * BN);
+  const double gram = 2.0 * gram_tiles(T) * BM * BN * (static_cast<double>(ceil_div(n_in, BK) + ceil_div(n_out, BK)) * BK);
+  int algo = norm_algo;
+  if (algo == FDP_NORM_AUTO) algo = (direct_ok && direct <= gram) ? FDP_NORM_DIRECT : FDP_NORM_GRAM;
+  if (algo == FDP_NORM_DIRECT && !direct_ok) algo = FDP_NORM_GRAM;
+  p.ok = true;
+  p.algo = algo;
+  p.nparts = (algo == FDP_NORM_DIRECT) ? ceil_div(n_out, BM) * ceil_div(n_in, BN) : gram_tiles(T);
+  p.ws_bytes = static_cast<size_t>(B) * T * n_out * 2;  // the c_b-scaled copy of G
+  (void)B;
+  return p;
+}
+
+int tc_norms(const void* G, const void* X, float* partials, int* dev_status, int B, int T, int n_in,
+             int n_out, int dt, const TcPlan& pl, cudaStream_t s) {
+  const uint64_t rows = static_cast<uint64_t>(B) * T;
+  CUtensorMap a, b, a2, b2;
+  TcArgs args{};
+  args.batch = B; args.batch_rows = T; args.partials = partials; args.status = dev_status; args.T = T;
+  if (pl.algo == FDP_NORM_DIRECT) {
+    if (!make_map(&a, G, rows, n_out, 64, BK, dt) || !make_map(&b, X, rows, n_in, 64, BK, dt)) return FDP_ERR_LAUNCH;
+    args.M = n_out; args.N = n_in;
+    args.tiles_m = ceil_div(n_out, BM); args.tiles_n = ceil_div(n_in, BN);
+    args.tiles_per_batch = args.tiles_m * args.tiles_n;
+    args.k_stages = T / BK;
+    args.idesc = make_idesc(dt, true, true);
+    return launch<true, true, EPI_SUMSQ>(a, b, a, b, args, s);
+  }
+  if (!make_map(&a, G, rows, n_out, BK, BM, dt) || !make_map(&b, G, rows, n_out, BK, BN, dt) ||
+      !make_map(&a2, X, rows, n_in, BK, BM, dt) || !make_map(&b2, X, rows, n_in, BK, BN, dt))
+    return FDP_ERR_LAUNCH;
+  args.M = T; args.N = T;
+  args.tiles_m = ceil_div(T, BM); args.tiles_n = ceil_div(T, BN);
+  args.tiles_per_batch = gram_tiles(T);
+  args.k_stages = ceil_div(n_out, BK); args.k_stages2 = ceil_div(n_in, BK);
+  args.idesc = make_idesc(dt, false, false);
+  return launch<false, false, EPI_GRAM>(a, b, a2, b2, args, s);
+}
+
+int tc_prescale(const void* G, const float* factors, void* Gs, int B, int T, int n_out, int dt, cudaStream_t s) {
+  const size_t nvec = static_cast<size_t>(B) * T * n_out / 8;
+  const int vps = T * (n_out / 8);
+  const int grid = sm_count() * 8;
+  if (dt == FDP_BF16)
+    prescale_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)G, factors, (__nv_bfloat16*)Gs, nvec, vps);
+  else
+    prescale_kernel<__half><<<grid, 256, 0, s>>>((const __half*)G, factors, (__half*)Gs, nvec, vps);
+  note_launch();
+  return FDP_OK;
+}
+
+int tc_clipped_wgrad(const void* Gs, const void* X, void* dW, int* dev_status, int B, int T, int n_in,
+                     int n_out, int dt, int out_dt, int layout, float inv_div, NoiseKey nk, cudaStream_t s) {
+  const uint64_t rows = static_cast<uint64_t>(B) * T;
+  CUtensorMap mg, mx;
+  if (!make_map(&mg, Gs, rows, n_out, 64, BK, dt) || !make_map(&mx, X, rows, n_in, 64, BK, dt)) return FDP_ERR_LAUNCH;
+  TcArgs args{};
+  args.batch = 1; args.batch_rows = 0; args.status = dev_status;
+  args.k_stages = static_cast<int>((rows + BK - 1) / BK);
+  args.out = dW; args.out_dt = out_dt; args.scale = inv_div; args.nk = nk;
+  args.idesc = make_idesc(dt, true, true);
+  // [out,in]: A = Gs (M = n_out), B = X (N = n_in); [in,out]: operands swap roles, no transpose pass
+  const bool oi = (layout == FDP_OUT_IN);
+  args.M = oi ? n_out : n_in; args.N = oi ? n_in : n_out; args.ld_out = args.N;
+  args.tiles_m = ceil_div(args.M, BM); args.tiles_n = ceil_div(args.N, BN);
+  args.tiles_per_batch = args.tiles_m * args.tiles_n;
+  return oi ? launch<true, true, EPI_STORE>(mg, mx, mg, mx, args, s)
+            : launch<true, true, EPI_STORE>(mx, mg, mx, mg, args, s);
+}
+
+bool tc_dgrad_ok(int rows, int n_in, int n_out, int dt) {
+  return (dt == FDP_BF16 || dt == FDP_F16) && n_in % 8 == 0 && n_out % 8 == 0 && n_in >= 128 && n_out >= 64 && rows >= 128;
+}
+
+int tc_dgrad(const void* G, const void* W, void* dX, int* dev_status, int rows, int n_in, int n_out,
+             int dt, int w_layout, cudaStream_t s) {
+  CUtensorMap mg, mw;
+  if (!make_map(&mg, G, rows, n_out, BK, BM, dt)) return FDP_ERR_LAUNCH;
+  TcArgs args{};
+  args.batch = 1; args.batch_rows = 0; args.status = dev_status;
+  args.M = rows; args.N = n_in; args.ld_out = n_in;
+  args.tiles_m = ceil_div(rows, BM); args.tiles_n = ceil_div(n_in, BN);
+  args.tiles_per_batch = args.tiles_m * args.tiles_n;
+  args.k_stages = ceil_div(n_out, BK);
+  args.out = dX; args.out_dt = dt; args.scale = 1.0f; args.nk = NoiseKey{};
+  if (w_layout == FDP_OUT_IN) {  // W [n_out, n_in]: rows are K, N contiguous
+    if (!make_map(&mw, W, n_out, n_in, 64, BK, dt)) return FDP_ERR_LAUNCH;
+    args.idesc = make_idesc(dt, false, true);
+    return launch<false, true, EPI_STORE>(mg, mw, mg, mw, args, s);
+  }
+  if (!make_map(&mw, W, n_in, n_out, BK, BN, dt)) return FDP_ERR_LAUNCH;  // W [n_in, n_out]: K contiguous
+  args.idesc = make_idesc(dt, false, false);
+  return launch<false, false, EPI_STORE>(mg, mw, mg, mw, args, s);
+}
+
+}  // namespace fdp

@@ -1,0 +1,38 @@
+"""Shared pieces of the DP layer backward passes."""
+from .. import runtime
+from ..core.ops import NoiseSpec, noise_std
+
+
+class DPLayerMixin:
+    """Hyper-parameters and noise bookkeeping common to the DP layers."""
+
+    def _init_dp(self, C, clamp_value, noise_multiplier, n_tensors=2):
+        self.dp = True
+        self.C = C
+        self.clamp_value = clamp_value
+        self.noise_multiplier = noise_multiplier
+        self._dp_param_ids = [runtime.next_param_id() for _ in range(n_tensors)]
+        self._dp_step = 0
+
+    def _next_step(self):
+        self._dp_step += 1
+        return self._dp_step
+
+
+def reshape_to_3d(input, grad_output):
+    """(B,T,.) views of the saved input and the upstream gradient: 2-D gets T=1, >3-D folds the
+    middle axes into T (flashdp/layers/linear.py:51-58)."""
+    if input.dim() == 2:
+        return input.unsqueeze(1), grad_output.unsqueeze(1)
+    if input.dim() > 3:
+        B = input.shape[0]
+        return input.reshape(B, -1, input.shape[-1]), grad_output.reshape(B, -1, grad_output.shape[-1])
+    return input, grad_output
+
+
+def dp_scalars(local_batch, noise_multiplier, param_id, step, param_id2=0):
+    """(batch_divisor, NoiseSpec) for one backward call under the current run layout."""
+    rank, world = runtime.data_parallel()
+    global_batch = local_batch * world
+    return global_batch, NoiseSpec(std=noise_std(noise_multiplier, global_batch), seed=runtime.get_seed(),
+                                   param_id=param_id, param_id2=param_id2, step=step, rank=rank, world=world)

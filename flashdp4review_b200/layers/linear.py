@@ -1,0 +1,80 @@
+"""DPLinear: nn.Linear whose backward yields per-sample-clipped, noised parameter gradients.
+
+Same constructor and attributes as the reference's DPLinear (flashdp/layers/linear.py:11-32).
+Backward = `_DPLinearFunc.backward` (flashdp/layers/linear.py:49-104): grad_input, then one
+library call for the weight gradient (norms -> clip factors -> clipped sum / B -> noise) and one
+for the bias gradient.  Unlike the reference, 2-D and >3-D inputs get a grad_input of the
+input's own shape, and grad_output is left unmodified.
+"""
+import torch
+import torch.nn as nn
+from torch.autograd.function import Function
+
+from .. import runtime
+from ..core import ops
+from ..core.ops import RuntimeAutoTuner
+from .utils import DPParameter as Parameter
+from ._common import DPLayerMixin, reshape_to_3d, dp_scalars
+
+
+class _DPLinearFunc(Function):
+    @staticmethod
+    def forward(ctx, input, weight, bias, layer):
+        ctx.save_for_backward(input, weight, bias)
+        ctx.layer = layer
+        output = input @ weight.t()
+        if bias is not None:
+            output = output + bias
+        return output
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        input, weight, bias = ctx.saved_tensors
+        layer = ctx.layer
+        x3, g3 = reshape_to_3d(input, grad_output)
+        B = x3.shape[0]
+        step = layer._next_step()
+        grad_input = grad_weight = grad_bias = None
+
+        if ctx.needs_input_grad[0]:
+            if runtime.input_grad_impl() == "native":
+                grad_input = ops.linear_input_grad(g3, weight, "out_in")
+            else:
+                grad_input = g3 @ weight.to(g3.dtype)
+            grad_input = grad_input.reshape(input.shape)
+
+        if ctx.needs_input_grad[1]:
+            div, noise = dp_scalars(B, layer.noise_multiplier, layer._dp_param_ids[0], step)
+            grad_weight = ops.dp_linear_weight_grad(
+                x3, g3, layer.C, layer.clamp_value, batch_divisor=div, noise=noise,
+                layout="out_in", out_dtype=weight.dtype, norm_algo=layer.norm_algo)
+            if grad_weight.shape != weight.shape:
+                raise RuntimeError(f"grad_weight shape {grad_weight.shape} is not equal to weight shape {weight.shape}")
+
+        if bias is not None and ctx.needs_input_grad[2]:
+            div, noise = dp_scalars(B, layer.noise_multiplier, layer._dp_param_ids[1], step)
+            grad_bias = ops.dp_bias_grad(g3, layer.C, layer.clamp_value, batch_divisor=div,
+                                         noise=noise, out_dtype=bias.dtype)
+            if grad_bias.shape != bias.shape:
+                raise RuntimeError(f"grad_bias shape {grad_bias.shape} is not equal to bias shape {bias.shape}")
+
+        return grad_input, grad_weight, grad_bias, None
+
+
+class DPLinear(nn.Linear, DPLayerMixin):
+    def __init__(self, in_features: int, out_features: int, bias: bool = True, device=None,
+                 dtype=None, C: float = 1.0, clamp_value: float = 1.0, noise_multiplier: float = 1.0,
+                 auto_tune: bool = True, norm_algo: str = "auto"):
+        # `bias=None` means no bias, anything else (True, False, a tensor) means bias:
+        # the reference's rule (flashdp/layers/linear.py:14), kept for drop-in behaviour
+        use_bias = bias is not None
+        super().__init__(in_features, out_features, use_bias, device=device, dtype=dtype)
+        self._init_dp(C, clamp_value, noise_multiplier)
+        self.runtime_tuner = RuntimeAutoTuner(enable=auto_tune)
+        self.norm_algo = norm_algo
+        self.weight = Parameter(self.weight.data)
+        if use_bias:
+            self.bias = Parameter(self.bias.data)
+
+    def forward(self, input):
+        return _DPLinearFunc.apply(input, self.weight, self.bias, self)

@@ -1,0 +1,63 @@
+"""Process-wide DP run state: noise seed, parameter ids, data-parallel layout.
+
+The reference keeps no such state (it draws from torch's global generator and knows one GPU).
+Here the noise is a pure function of (seed, param_id, step, element index), and a
+data-parallel job is described once so every layer scales by the global batch and draws only
+its share of the noise before the all-reduce of the clipped sums.
+"""
+import itertools
+import threading
+
+_state = threading.local()
+_ids = itertools.count(1)
+
+
+class _Run:
+    seed = 0
+    world = 1
+    rank = 0
+    input_grad_impl = "library"   # "library": cuBLAS via torch (as the reference); "native": fdp_linear_dgrad
+
+
+_run = _Run()
+
+
+def manual_seed(seed: int):
+    """Fix the Philox key of every DP layer's noise (reproducible runs)."""
+    _run.seed = int(seed)
+
+
+def get_seed() -> int:
+    return _run.seed
+
+
+def set_data_parallel(rank: int, world: int):
+    """Declare that the batch each DP layer sees is one of `world` equal shards.
+
+    Layers then divide by world*B_local and use std = noise_multiplier/sqrt(world*B_local); rank r
+    draws only its 1/world share of the noise elements, so the SUM all-reduce of the gradients
+    (see flashdp4review_b200.distributed) yields the gradient and exactly one noise draw of the
+    concatenated batch.
+    """
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError(f"bad data-parallel layout rank={rank} world={world}")
+    _run.rank, _run.world = int(rank), int(world)
+
+
+def data_parallel():
+    return _run.rank, _run.world
+
+
+def set_input_grad_impl(name: str):
+    if name not in ("library", "native"):
+        raise ValueError("input_grad_impl must be 'library' or 'native'")
+    _run.input_grad_impl = name
+
+
+def input_grad_impl():
+    return _run.input_grad_impl
+
+
+def next_param_id() -> int:
+    """A fresh id per DP parameter tensor, in construction order."""
+    return next(_ids)

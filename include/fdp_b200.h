@@ -1,0 +1,146 @@
+/*
+ * fdp_b200.h -- C ABI of the B200 (sm_100a) DP-SGD backward kernels.
+ *
+ * Every entry point is `extern "C"`, takes raw device pointers to contiguous row-major
+ * tensors, sizes, and the CUDA stream to launch on.  Nothing here allocates device memory,
+ * synchronises the host or throws: the caller passes a workspace whose size the matching
+ * `*_workspace_bytes` query returns, and reads a status code (0 = FDP_OK, negative = error;
+ * `fdp_status_string` names it).  Inputs are never modified.
+ *
+ * The comments cite, as file:line inside the FlashDP4Review project, the Python-level
+ * interface of the reference that each entry point takes the place of.
+ */
+#ifndef FDP_B200_H
+#define FDP_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FDP_ABI_VERSION 1
+
+typedef void* fdp_stream_t; /* a cudaStream_t */
+
+enum fdp_status {
+  FDP_OK = 0,
+  FDP_ERR_ARG = -1,       /* null pointer, non-positive size, bad enum */
+  FDP_ERR_DTYPE = -2,     /* dtype not supported by this entry point */
+  FDP_ERR_SHAPE = -3,     /* shape outside what the kernels cover */
+  FDP_ERR_ALIGN = -4,     /* pointer not 16-byte aligned */
+  FDP_ERR_WORKSPACE = -5, /* workspace missing or too small */
+  FDP_ERR_ARCH = -6,      /* device is not sm_100 */
+  FDP_ERR_LAUNCH = -7,    /* CUDA reported a launch/runtime error */
+  FDP_ERR_TIMEOUT = -8    /* a bounded device-side wait ran out (see fdp_device_status) */
+};
+
+/* number types: supported_acc_dtypes of flashdp/core/utils.py:9-12 (fp32 accumulation for all) */
+enum fdp_dtype { FDP_F32 = 0, FDP_BF16 = 1, FDP_F16 = 2 };
+
+/* orientation of the weight gradient: [out,in] for nn.Linear (flashdp/core/linear_clip.py:94-104),
+ * [in,out] for transformers Conv1D (flashdp/core/transformers_conv1d_clip.py:22-28) */
+enum fdp_layout { FDP_OUT_IN = 0, FDP_IN_OUT = 1 };
+
+/* how the per-sample norms ||G_b^T X_b||_F are obtained */
+enum fdp_norm_algo {
+  FDP_NORM_AUTO = 0,   /* pick per shape */
+  FDP_NORM_DIRECT = 1, /* per-sample GEMM tiles, squared and reduced in the epilogue, never stored */
+  FDP_NORM_GRAM = 2    /* sum_{t,s} (G_b G_b^T)_{ts} (X_b X_b^T)_{ts} */
+};
+
+/* DP hyper-parameters of one call.  C / clamp_value are the arguments of
+ * get_clip_factor_torch (flashdp/core/clip_fn.py:6-8); noise_std is
+ * noise_multiplier / sqrt(B_global) (flashdp/layers/linear.py:74-80). */
+typedef struct fdp_dp_params {
+  float C;
+  float clamp_value;
+  float noise_std;       /* 0 disables the noise epilogue */
+  int32_t batch_divisor; /* the mean is sum/batch_divisor; <=0 means the local batch size B */
+  uint64_t seed;         /* Philox key */
+  uint32_t param_id;     /* Philox counter word 2: which parameter tensor */
+  uint32_t param_id2;    /* second tensor of the call (LayerNorm beta) */
+  uint32_t step;         /* Philox counter word 3: training step */
+  int32_t noise_rank;    /* this rank draws the noise of element groups g with g % noise_world == noise_rank */
+  int32_t noise_world;   /* <=1: this rank draws all of it */
+} fdp_dp_params;
+
+int fdp_abi_version(void);
+const char* fdp_status_string(int status);
+
+/* 0 if device `device` can run the library (compute capability 10.x), else FDP_ERR_ARCH. */
+int fdp_check_device(int device);
+
+/* Reads the device-side status word that the tensor-core kernels keep at the start of the
+ * workspace (0 = no bounded wait ran out).  Synchronises `stream`.  Returns FDP_OK,
+ * FDP_ERR_TIMEOUT or FDP_ERR_LAUNCH. */
+int fdp_device_status(const void* workspace, fdp_stream_t stream);
+
+/* ---- instrumentation (no counterpart in the reference, which only wall-clocks whole functions in
+ * RuntimeAutoTuner._measure_time, flashdp/core/utils.py:42-47) ---------------------------------------
+ * fdp_launch_count: kernels launched by this library in this process so far.
+ * fdp_profile_enable(1): later fdp_linear_wgrad calls record CUDA events on their stream between
+ *   their phases; fdp_profile_read waits for the last such call and writes the milliseconds of
+ *   {norm pass, clip factors, c_b pre-scale, clipped-sum GEMM} to ms[0..3]; returns 4 or an error. */
+unsigned long long fdp_launch_count(void);
+int fdp_profile_enable(int on);
+int fdp_profile_read(float* ms, int capacity);
+
+/* ---- DP weight gradient of Linear / Conv1D --------------------------------------------------
+ * Takes the place of linear_weight_flashdp(input, grad_output, C, clamp_value, tuner)
+ * (flashdp/core/linear_clip.py:107-113) together with the `.div_(B)` and the torch.normal noise
+ * of its caller (flashdp/layers/linear.py:72-80; flashdp/layers/transformers_conv1d.py:79-87).
+ *   G [B,T,n_out], X [B,T,n_in] in `in_dtype`;  dW in `out_dtype`, [n_out,n_in] or [n_in,n_out].
+ *   norms_out / factors_out: optional float[B] (per-sample Frobenius norms and clip factors).
+ */
+size_t fdp_linear_wgrad_workspace_bytes(int B, int T, int n_in, int n_out, int in_dtype,
+                                        int norm_algo);
+int fdp_linear_wgrad(const void* G, const void* X, void* dW, float* norms_out, float* factors_out,
+                     int B, int T, int n_in, int n_out, int in_dtype, int out_dtype, int layout,
+                     int norm_algo, const fdp_dp_params* p, void* workspace, size_t workspace_bytes,
+                     fdp_stream_t stream);
+
+/* ---- DP bias gradient -------------------------------------------------------------------------
+ * Takes the place of linear_bias_grad_clip(grad_output, C, clamp_value)
+ * (flashdp/core/linear_clip.py:116-123) plus its caller's noise (flashdp/layers/linear.py:84-92):
+ * norm of sample b over its whole T x n_out block, db = sum_b c_b sum_t G[b,t,:] / (divisor*T).
+ * G is read once and not written (the reference scales it in place).
+ */
+size_t fdp_bias_grad_workspace_bytes(int B, int T, int n_out, int in_dtype);
+int fdp_bias_grad(const void* G, void* db, float* norms_out, float* factors_out, int B, int T,
+                  int n_out, int in_dtype, int out_dtype, const fdp_dp_params* p, void* workspace,
+                  size_t workspace_bytes, fdp_stream_t stream);
+
+/* ---- input gradient ---------------------------------------------------------------------------
+ * `grad_output @ weight` of flashdp/layers/linear.py:62-67 (w_layout FDP_OUT_IN, W [n_out,n_in]) and
+ * `grad_output @ weight.t()` of flashdp/layers/transformers_conv1d.py:70-75 (FDP_IN_OUT, W [n_in,n_out]).
+ *   G [rows,n_out], dX [rows,n_in], all in `dtype`.
+ */
+size_t fdp_linear_dgrad_workspace_bytes(int rows, int n_in, int n_out, int dtype);
+int fdp_linear_dgrad(const void* G, const void* W, void* dX, int rows, int n_in, int n_out,
+                     int dtype, int w_layout, void* workspace, size_t workspace_bytes,
+                     fdp_stream_t stream);
+
+/* ---- LayerNorm ----------------------------------------------------------------------------------
+ * fdp_layernorm_fwd: layernorm_fwd_fused(input, weight, bias, eps) (flashdp/core/layernorm_clip.py:201-239):
+ *   x,y [rows,d] in `dtype`; gamma,beta [d] in `param_dtype`; mean,rstd float[rows].
+ * fdp_layernorm_bwd: dx as in _layer_norm_bwd_dx_fused_clip (flashdp/core/layernorm_clip.py:95-103);
+ *   dgamma/dbeta with the per-sample clipping of layernorm_dw_clip / layernorm_db_clip
+ *   (flashdp/core/layernorm_clip.py:163-198) and the noise of flashdp/layers/layernorm.py:139-155
+ *   (one draw per tensor).  dx, dbeta and the norms outputs may be NULL.
+ */
+int fdp_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean,
+                      float* rstd, int rows, int d, float eps, int dtype, int param_dtype,
+                      fdp_stream_t stream);
+size_t fdp_layernorm_bwd_workspace_bytes(int B, int T, int d);
+int fdp_layernorm_bwd(const void* dy, const void* x, const void* gamma, const float* mean,
+                      const float* rstd, void* dx, void* dgamma, void* dbeta, float* norms_gamma,
+                      float* norms_beta, int B, int T, int d, int dtype, int param_dtype,
+                      const fdp_dp_params* p, void* workspace, size_t workspace_bytes,
+                      fdp_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FDP_B200_H */

@@ -182,15 +182,16 @@ def gaussian_noise(n: int, std: float, seed: int, param_id: int, step: int) -> n
 
     Element ``i`` uses Philox counter ``(i>>2 low, i>>2 high, param_id, step)`` under key
     ``(seed low, seed high)``; lanes 0/1 are the cos/sin Box-Muller pair of words (0,1) and
-    lanes 2/3 that of words (2,3); a word ``w`` maps to the uniform ``(w + 0.5) * 2^-32``.
+    lanes 2/3 that of words (2,3); a word ``w`` maps to the uniform ``((w >> 9) + 0.5) * 2^-23``
+    (exactly representable in fp32, so host and device agree on it bit for bit).
     """
     groups = (n + 3) // 4
     idx = np.arange(groups, dtype=np.uint64)
     ctr = np.stack([idx & np.uint64(0xFFFFFFFF), idx >> np.uint64(32),
                     np.full(groups, param_id, np.uint64), np.full(groups, step, np.uint64)], axis=1)
     key = np.array([seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF], dtype=np.uint64)
-    r = philox4x32_10(ctr, key).astype(np.float64)
-    u = (r + 0.5) * (2.0 ** -32)
+    r = (philox4x32_10(ctr, key) >> np.uint32(9)).astype(np.float64)
+    u = (r + 0.5) * (2.0 ** -23)
     z = np.empty((groups, 4))
     for p in range(2):
         rad = np.sqrt(-2.0 * np.log(u[:, 2 * p]))

@@ -1,0 +1,99 @@
+"""The tcgen05 / TMEM / TMA kernels (bf16 and fp16, 16-byte-aligned row pitches) against the oracle:
+both norm algorithms, the clipped-sum GEMM in both orientations, partial tiles, the input gradient."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import dp_oracle as O
+from conftest import rel_err, norm_err
+from gpu_util import TOL, dev, check_wgrad
+
+pytestmark = pytest.mark.gpu
+
+# (B, T, n_in, n_out): full tiles, partial tiles in M / N / K, T not a multiple of the tile
+SHAPES = [(2, 128, 256, 128), (3, 64, 136, 200), (2, 256, 512, 384), (1, 192, 768, 1024),
+          (4, 320, 264, 520), (2, 1024, 256, 256)]
+
+
+@pytest.mark.parametrize("algo", ["direct", "gram", "auto"])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_wgrad_tensorcore(shape, algo):
+    B, T, n_in, n_out = shape
+    X, G, _ = O.make_linear_inputs(B, T, n_in, n_out, 1e-3, seed=sum(shape), dtype=torch.bfloat16)
+    G[0] *= 40.0                      # one sample clipped harder than the others
+    check_wgrad(X, G, 1e-2, 1.0, torch.bfloat16, norm_algo=algo)
+
+
+@pytest.mark.parametrize("shape", [(2, 128, 256, 128), (3, 64, 136, 200)])
+def test_wgrad_tensorcore_conv1d_layout_fp16_fp32out(shape):
+    B, T, n_in, n_out = shape
+    X, G, _ = O.make_linear_inputs(B, T, n_in, n_out, 1e-2, seed=7, dtype=torch.float16)
+    check_wgrad(X, G, 0.05, 1.0, torch.float16, layout="in_out")
+    check_wgrad(X, G, 0.05, 1.0, torch.float16, layout="out_in", out_dtype=torch.float32, tol=2e-3)
+
+
+def test_gram_T_not_multiple_of_tile():
+    # T = 200: the direct algorithm is not eligible (a K stage would cross samples); Gram masks rows
+    X, G, _ = O.make_linear_inputs(3, 200, 256, 128, 1e-3, seed=21, dtype=torch.bfloat16)
+    check_wgrad(X, G, 1e-2, 1.0, torch.bfloat16, norm_algo="auto")
+
+
+def test_norm_algorithms_agree_and_are_deterministic():
+    from flashdp4review_b200.core import ops
+    X, G, _ = O.make_linear_inputs(4, 256, 512, 256, 1e-3, seed=3, dtype=torch.bfloat16)
+    Xd, Gd = X.to(dev()), G.to(dev())
+    res = {}
+    for algo in ("direct", "gram"):
+        a = ops.dp_linear_weight_grad(Xd, Gd, 1e-2, 1.0, norm_algo=algo, return_norms=True)
+        b = ops.dp_linear_weight_grad(Xd, Gd, 1e-2, 1.0, norm_algo=algo, return_norms=True)
+        assert torch.equal(a[0], b[0]) and torch.equal(a[1], b[1])      # bit-reproducible
+        res[algo] = a
+    assert norm_err(res["direct"][1].cpu().numpy(), res["gram"][1].cpu().numpy()) < 1e-4
+
+
+def test_tensorcore_noise_matches_host_stream():
+    from flashdp4review_b200.core import ops
+    X = torch.zeros(2, 128, 256, device=dev(), dtype=torch.bfloat16)
+    G = torch.zeros(2, 128, 384, device=dev(), dtype=torch.bfloat16)
+    ns = ops.NoiseSpec(std=0.75, seed=99, param_id=4, step=6)
+    for layout, shape in (("out_in", (384, 256)), ("in_out", (256, 384))):
+        a = ops.dp_linear_weight_grad(X, G, 1.0, 1.0, noise=ns, layout=layout, out_dtype=torch.float32)
+        want = O.gaussian_noise(384 * 256, 0.75, 99, 4, 6).reshape(shape)
+        assert np.abs(a.cpu().numpy() - want).max() < 3e-6
+    # partition over ranks
+    acc = sum(ops.dp_linear_weight_grad(X, G, 1.0, 1.0, layout="out_in", out_dtype=torch.float32,
+                                        noise=ops.NoiseSpec(0.75, 99, 4, 0, 6, r, 2)) for r in range(2))
+    assert np.abs(acc.cpu().numpy() - O.gaussian_noise(384 * 256, 0.75, 99, 4, 6).reshape(384, 256)).max() < 3e-6
+
+
+@pytest.mark.parametrize("layout", ["out_in", "in_out"])
+@pytest.mark.parametrize("shape", [(256, 256, 128), (200, 136, 328), (1024, 512, 768)])
+def test_input_grad_tensorcore(shape, layout):
+    from flashdp4review_b200.core import ops
+    rows, n_in, n_out = shape
+    gen = torch.Generator().manual_seed(rows)
+    G = (torch.randn(2, rows // 2, n_out, generator=gen) * 0.1).to(torch.bfloat16)
+    W = (torch.randn(n_out, n_in, generator=gen) * 0.05).to(torch.bfloat16)
+    Wd = W if layout == "out_in" else W.t().contiguous()
+    dX = ops.linear_input_grad(G.to(dev()), Wd.to(dev()), layout)
+    want = G.double().numpy() @ W.double().numpy()
+    assert rel_err(dX.float().cpu().numpy(), want) < 1e-2
+
+
+def test_no_bounded_wait_ran_out():
+    """After a tensor-core call the status word at the head of the workspace is still zero."""
+    from flashdp4review_b200 import _lib
+    lib = _lib.load()
+    B, T, n_in, n_out = 2, 128, 256, 256
+    X = torch.randn(B, T, n_in, device=dev(), dtype=torch.bfloat16)
+    G = torch.randn(B, T, n_out, device=dev(), dtype=torch.bfloat16)
+    dW = torch.empty(n_out, n_in, device=dev(), dtype=torch.bfloat16)
+    ws = torch.empty(lib.fdp_linear_wgrad_workspace_bytes(B, T, n_in, n_out, _lib.FDP_BF16, 0),
+                     dtype=torch.uint8, device=dev())
+    p = _lib.DPParams(1.0, 1.0, 0.0, 0, 0, 0, 0, 0, 0, 1)
+    import ctypes
+    st = lib.fdp_linear_wgrad(G.data_ptr(), X.data_ptr(), dW.data_ptr(), None, None, B, T, n_in, n_out,
+                              _lib.FDP_BF16, _lib.FDP_BF16, 0, 0, ctypes.byref(p), ws.data_ptr(), ws.numel(),
+                              torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    assert lib.fdp_device_status(ws.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0

@@ -1,0 +1,101 @@
+"""CPU-side checks: the shared library loads and exports the whole C ABI, and the wrap API keeps
+the reference's selection rules and errors (flashdp/api/wrap_model.py)."""
+import os
+import re
+
+import pytest
+import torch
+import torch.nn as nn
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    from flashdp4review_b200 import _lib
+    lib = _lib.load()
+    header = open(os.path.join(ROOT, "include", "fdp_b200.h")).read()
+    declared = set(re.findall(r"\b(fdp_[a-z0-9_]+)\s*\(", header))
+    assert declared, "no declarations found"
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in include/fdp_b200.h but not exported"
+    assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
+    assert lib.fdp_abi_version() == 1
+    assert lib.fdp_status_string(0) == b"ok"
+    assert b"workspace" in lib.fdp_status_string(_lib.FDP_ERR_WORKSPACE)
+    # pure host-side queries work without a device
+    assert lib.fdp_linear_wgrad_workspace_bytes(4, 128, 768, 768, _lib.FDP_F32, 0) > 0
+    assert lib.fdp_linear_wgrad_workspace_bytes(0, 128, 768, 768, _lib.FDP_F32, 0) == 0
+    assert lib.fdp_bias_grad_workspace_bytes(4, 128, 768, _lib.FDP_BF16) > 0
+    assert lib.fdp_layernorm_bwd_workspace_bytes(16, 1024, 1024) > 0
+
+
+def test_no_cpu_fallback():
+    from flashdp4review_b200.core import ops
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.dp_linear_weight_grad(torch.zeros(1, 2, 8), torch.zeros(1, 2, 8), 1.0, 1.0)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.dp_bias_grad(torch.zeros(1, 2, 8), 1.0, 1.0)
+
+
+def _model():
+    return nn.Sequential(nn.Linear(8, 8), nn.LayerNorm(8),
+                         nn.Sequential(nn.Linear(8, 4, bias=False), nn.ReLU()), nn.Linear(4, 2))
+
+
+def test_wrap_argument_errors():
+    from flashdp4review_b200 import wrap_with_flashdp_layers
+    with pytest.raises(ValueError):
+        wrap_with_flashdp_layers(_model())
+    with pytest.raises(ValueError):
+        wrap_with_flashdp_layers(_model(), target_modules=[])
+    with pytest.raises(ValueError):
+        wrap_with_flashdp_layers(_model(), target_layers=["0"])          # target_layers alone is rejected
+    with pytest.raises(ValueError):
+        wrap_with_flashdp_layers(_model(), target_modules=[nn.Conv2d])
+
+
+def test_wrap_selection_rules():
+    import flashdp4review_b200 as fdp
+    m = fdp.wrap_with_flashdp_layers(_model(), target_modules=[nn.Linear, nn.LayerNorm], skip_layers=["3"],
+                                     C=0.3, noise_multiplier=0.7, clamp_value=0.9, feedback=False)
+    assert isinstance(m[0], fdp.DPLinear) and isinstance(m[1], fdp.DPLayerNorm)
+    assert isinstance(m[2][0], fdp.DPLinear) and m[2][0].bias is None
+    assert type(m[3]) is nn.Linear
+    assert (m[0].C, m[0].noise_multiplier, m[0].clamp_value) == (0.3, 0.7, 0.9)
+    # skipping a container does not skip its children (exact-name match only)
+    m = fdp.wrap_with_flashdp_layers(_model(), target_modules=[nn.Linear], skip_layers=["2"], feedback=False)
+    assert isinstance(m[2][0], fdp.DPLinear)
+    # target_layers restricts the candidates
+    m = fdp.wrap_with_flashdp_layers(_model(), target_modules=[nn.Linear], target_layers=["0"], feedback=False)
+    assert isinstance(m[0], fdp.DPLinear) and type(m[3]) is nn.Linear
+
+
+def test_wrap_keeps_weights_dtype_mode_and_ties():
+    import flashdp4review_b200 as fdp
+
+    class Tied(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb = nn.Embedding(10, 8)
+            self.body = nn.Linear(8, 8)
+            self.lm_head = nn.Linear(8, 10, bias=False)
+            self.lm_head.weight = self.emb.weight
+    src = Tied().to(torch.bfloat16).eval()
+    ref_w = src.body.weight.detach().clone()
+    m = fdp.wrap_with_flashdp_layers(src, target_modules=[nn.Linear], skip_layers=["lm_head"], feedback=False)
+    assert torch.equal(m.body.weight.detach(), ref_w)
+    assert m.body.weight.dtype == torch.bfloat16 and not m.body.training
+    assert m.lm_head.weight is m.emb.weight
+    assert set(m.state_dict()) == set(Tied().state_dict())            # parameter names round-trip
+
+
+def test_conv1d_twin_and_constructor_attributes():
+    import flashdp4review_b200 as fdp
+    from flashdp4review_b200.layers import Conv1D
+    m = nn.Sequential(Conv1D(24, 8))
+    fdp.wrap_with_flashdp_layers(m, target_modules=[Conv1D], feedback=False)
+    assert isinstance(m[0], fdp.DPConv1D) and m[0].weight.shape == (8, 24) and m[0].nf == 24
+    lin = fdp.DPLinear(4, 6, C=2.0, clamp_value=0.5, noise_multiplier=0.1, auto_tune=False)
+    assert lin.dp and lin.runtime_tuner.enable is False and lin.weight.requires_dp
+    ln = fdp.DPLayerNorm(6, use_fused=False, bias=None)
+    assert ln.bias is None and ln.use_fused is False
