@@ -51,21 +51,33 @@ def flops_bwd(B, T, n_in, n_out):
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
-    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """nvidia-smi clock / throttle-reason samples (20 ms period) with their wall-clock stamps, so the
+    ones that fall inside a timed region can be picked out afterwards."""
+    Q = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, gpu_index):
         self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
         self.p = None
         try:
             self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                       "-lms", "100", "-i", str(gpu_index)], stdout=self.f, stderr=subprocess.DEVNULL)
+                                       "-lms", "20", "-i", str(gpu_index)], stdout=self.f, stderr=subprocess.DEVNULL)
         except Exception:
             self.p = None
 
-    def stop(self):
+    def wait_first_sample(self, limit_s=5.0):
+        t0 = time.time()
+        while self.p is not None and time.time() - t0 < limit_s:
+            if os.path.getsize(self.f.name) > 0:
+                return True
+            time.sleep(0.02)
+        return False
+
+    def stop(self, windows):
+        """windows: list of (t_start, t_end) wall-clock pairs; samples inside any of them count."""
+        import datetime
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
         if self.p is None:
             return out
@@ -76,23 +88,31 @@ class ClockSampler:
             self.p.kill()
         self.f.flush()
         self.f.seek(0)
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        sm, mx, reasons, power = [], [], set(), []
         for line in self.f.read().splitlines():
             parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 9:
+            if len(parts) < 8:
                 continue
             try:
-                sm.append(float(parts[1]))
-                mx.append(float(parts[2]))
+                ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                clk, clk_max = float(parts[1]), float(parts[2])
             except ValueError:
                 continue
-            for name, val in zip(names, parts[5:9]):
+            if not any(a <= ts <= b for a, b in windows):
+                continue
+            sm.append(clk)
+            mx.append(clk_max)
+            try:
+                power.append(float(parts[3]))
+            except ValueError:
+                pass
+            for name, val in zip(self.NAMES, parts[4:8]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
         os.unlink(self.f.name)
         if sm:
-            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm),
+                       power_w_max=max(power) if power else None)
         return out
 
 
@@ -146,7 +166,6 @@ def run_native(args, wl):
     import flashdp4review_b200 as fdp
     from flashdp4review_b200 import _lib
     from flashdp4review_b200.core import ops
-    from oracle import dp_oracle as O  # input recipe + the cpu_baseline leg only
 
     B, T, n_in, n_out, dtn, g_scale = wl
     rank = int(os.environ.get("RANK", "0"))
@@ -165,7 +184,10 @@ def run_native(args, wl):
     dt = torch.bfloat16 if dtn == "bf16" else torch.float32
 
     # synthetic inputs: X~N(0,1), G~N(0,g_scale^2), W~N(0,0.02^2); a different seed per rank (its shard)
-    Xh, Gh, Wh = O.make_linear_inputs(B, T, n_in, n_out, g_scale, seed=rank, dtype=dt)
+    gen = torch.Generator().manual_seed(rank)
+    Xh = torch.randn(B, T, n_in, generator=gen).to(dt)
+    Gh = (torch.randn(B, T, n_out, generator=gen) * g_scale).to(dt)
+    Wh = (torch.randn(n_out, n_in, generator=gen) * 0.02).to(dt)
     Xh, Gh = Xh.pin_memory(), Gh.pin_memory()
     X, G, W = Xh.to(dev), Gh.to(dev), Wh.to(dev)
     step_no = [0]
@@ -200,16 +222,55 @@ def run_native(args, wl):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return float(ms.item())
 
+    # L2 hygiene: the default workload's inputs (0.5 GB) exceed the 126 MB L2; smaller workloads
+    # get the L2 overwritten by a 256 MB fill between steps, each step timed by its own event pair
+    in_bytes = (X.numel() + G.numel()) * X.element_size()
+    flush = None if in_bytes > 2 * 126e6 else torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def timed_steps(steps):
+        if flush is None:
+            return timed(lambda: step(X, G), steps)
+        barrier()
+        evs = []
+        for _ in range(steps):
+            flush.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            step(X, G)
+            e1.record()
+            evs.append((e0, e1))
+        barrier()
+        ms = torch.tensor([sum(a.elapsed_time(b) for a, b in evs)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    sampler = ClockSampler(local_rank) if rank == 0 else None
     for _ in range(max(args.warmup, 3)):
         step(X, G)
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.wait_first_sample()
     launches0 = lib.fdp_launch_count()
-    total_ms = timed(lambda: step(X, G), args.steps)
+    w0 = time.time()
+    total_ms = timed_steps(args.steps)
+    windows = [(w0, time.time())]
     launches = lib.fdp_launch_count() - launches0
-    clocks = sampler.stop() if sampler else None
     ms_per_step = total_ms / args.steps
     value = world * flops_bwd(B, T, n_in, n_out) / (ms_per_step * 1e-3) / 1e12
-
+    clocks = None
+    if sampler:
+        # a short timed region may see too few 20 ms samples: keep the same load running (untimed)
+        # until about 0.6 s of it has been observed, and say so
+        extra = 0
+        if windows[0][1] - windows[0][0] < 0.6:
+            w1 = time.time()
+            while time.time() - w1 < 0.6:
+                step(X, G)
+                extra += 1
+            torch.cuda.synchronize()
+            windows.append((w1, time.time()))
+        clocks = sampler.stop(windows)
+        clocks["window"] = "timed region" + (f" + {extra} more identical steps" if extra else "")
     # end to end: host (pinned) inputs in, gradient back to the host, every step
     dW_host = torch.empty(n_out, n_in, dtype=torch.float32).pin_memory()
 
@@ -265,7 +326,8 @@ def run_native(args, wl):
                 "config": {"workload": args.workload, "B_per_gpu": B, "T": T, "in": n_in, "out": n_out,
                            "C": 1.0, "noise_multiplier": 1.0, "bias": False, "grad_dtype": "f32",
                            "flops_per_step_per_gpu": flops_bwd(B, T, n_in, n_out),
-                           "l2": "inputs (X, G: %.0f MB) larger than the 126 MB L2" % (h2d / 1e6),
+                           "l2": ("inputs (X, G: %.0f MB) larger than the 126 MB L2" % (h2d / 1e6)) if flush is None
+                           else "L2 overwritten by a 256 MB fill between steps",
                            "parallelism": f"dp{world}" + (" + NCCL all-reduce of dW" if world > 1 else "")},
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": e2e_ms, "steps": e2e_steps},

@@ -24,7 +24,7 @@ class _DPLinearFunc(Function):
         ctx.layer = layer
         output = input @ weight.t()
         if bias is not None:
-            output = output + bias
+            output += bias     # in place, so a bf16 autocast output stays bf16 (as in the reference)
         return output
 
     @staticmethod

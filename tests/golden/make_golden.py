@@ -158,8 +158,7 @@ def main():
     lay.update(ln_meta=np.array([B, T, d]), ln_C=0.9, ln_X=np32(X), ln_DY=np32(DY),
                ln_gamma=np32(gamma), ln_beta=np32(beta), ln_y=np32(y), ln_dx=np32(x.grad),
                ln_dgamma=np32(ln.weight.grad).reshape(-1), ln_dbeta_fn=np32(dgb).reshape(-1),
-               ln_dgamma_fn=np32(dgw).reshape(-1),
-               ln_bias_grad_is_none=np.array(ln.bias.grad is None))
+               ln_dgamma_fn=np32(dgw).reshape(-1), ln_dbeta=np32(ln.bias.grad).reshape(-1))
     np.savez_compressed(os.path.join(HERE, "layers.npz"), **lay)
 
     # ---- noise statistics of the reference at sigma = 1 (distribution is the parity target) --

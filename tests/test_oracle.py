@@ -91,6 +91,7 @@ def test_layernorm_against_reference(golden):
     assert rel_err(dgamma, g["ln_dgamma_fn"]) < FP32_TOL
     assert rel_err(dbeta, g["ln_dbeta_fn"]) < FP32_TOL
     assert rel_err(dgamma, g["ln_dgamma"]) < FP32_TOL      # through the module, sigma = 0
+    assert rel_err(dbeta, g["ln_dbeta"]) < FP32_TOL
     assert rel_err(O.layernorm_bwd_dx(DY, X, gamma, mean, rstd), g["ln_dx"]) < 5e-5
 
 
