@@ -33,6 +33,7 @@ struct TcArgs {
   int M, N;             // extents of the output space of one batch (masks)
   int tiles_m, tiles_n; // tile grid of one batch (EPI_GRAM: tiles_m = t-blocks of 128, tiles_n = s-blocks of 256)
   int tiles_per_batch;
+  int n_fastest;        // tile order: 1 = consecutive tiles walk along N (keeps the B operand in L2), 0 = along M
   int batch;
   int k_stages, k_stages2;  // K loop of operand pair 1 (and pair 2 for EPI_GRAM)
   int batch_rows;           // rows of one batch along the row coordinate of the tensor maps
@@ -41,6 +42,10 @@ struct TcArgs {
   int T;
   int* status;
   uint32_t idesc;
+  // split-K tail (EPI_STORE only): work units [0, units_full) are whole tiles; each later tile is cut
+  // into `split` K ranges whose raw fp32 accumulators go to split_ws[slot][BM][BN] for the fix-up kernel
+  int units_full, split;
+  float* split_ws;
 };
 
 // ---- PTX wrappers ---------------------------------------------------------------------------------
@@ -156,6 +161,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_tiles = args.batch * args.tiles_per_batch;
   const int kst_total = args.k_stages + (EPI == EPI_GRAM ? args.k_stages2 : 0);
+  const int total_units = args.units_full + (total_tiles - args.units_full) * args.split;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -186,10 +192,24 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         q -= cnt; ++j;
       }
       m0 = q * BM; n0 = j * BN;
+    } else if (args.n_fastest) {
+      n0 = (q % args.tiles_n) * BN;
+      m0 = (q / args.tiles_n) * BM;
     } else {
       m0 = (q % args.tiles_m) * BM;
       n0 = (q / args.tiles_m) * BN;
     }
+  };
+
+  // work unit -> tile, K-stage range, slot in split_ws (-1: whole tile, normal epilogue)
+  auto decode_unit = [&](int u, int& tile, int& ks0, int& ks1, int& slot) {
+    if (u < args.units_full) { tile = u; ks0 = 0; ks1 = kst_total; slot = -1; return; }
+    const int v = u - args.units_full;
+    const int part = v % args.split;
+    tile = args.units_full + v / args.split;
+    ks0 = static_cast<int>(static_cast<long long>(kst_total) * part / args.split);
+    ks1 = static_cast<int>(static_cast<long long>(kst_total) * (part + 1) / args.split);
+    slot = v;
   };
 
   if (warp == 0) {
@@ -197,11 +217,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-        int b, m0, n0;
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+        int tile, ks0, ks1, slot, b, m0, n0;
+        decode_unit(u, tile, ks0, ks1, slot);
         decode(tile, b, m0, n0);
         const int row0 = b * args.batch_rows;
-        for (int ks = 0; ks < kst_total; ++ks) {
+        for (int ks = ks0; ks < ks1; ++ks) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 1)) { ok = false; break; }
           const bool second = (EPI == EPI_GRAM) && ks >= args.k_stages;
           const CUtensorMap* ma = second ? &tmA2 : &tmA;
@@ -239,17 +260,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0; uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++it) {
+        int tile, ks0, ks1, slot;
+        decode_unit(u, tile, ks0, ks1, slot);
         const int acc = it % NUM_ACC;
         const uint32_t acc_phase = (it / NUM_ACC) & 1u;
         if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, args.status, 2)) { ok = false; break; }
         tc_fence_after();
-        for (int ks = 0; ks < kst_total; ++ks) {
+        for (int ks = ks0; ks < ks1; ++ks) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 3)) { ok = false; break; }
           tc_fence_after();
           const bool second = (EPI == EPI_GRAM) && ks >= args.k_stages;
           const uint32_t d = tmem_base + (EPI == EPI_GRAM ? (second ? BN : 0) : acc * BN);
-          const bool first_stage = second ? (ks == args.k_stages) : (ks == 0);
+          const bool first_stage = second ? (ks == args.k_stages) : (ks == ks0);
           const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
 #pragma unroll
           for (int k16 = 0; k16 < BK / UMMA_K; ++k16)
@@ -273,8 +296,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int row = quarter * 32 + lane;
     int it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++it) {
-      int b, m0, n0;
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++it) {
+      int tile, ks0, ks1, slot, b, m0, n0;
+      decode_unit(u, tile, ks0, ks1, slot);
       decode(tile, b, m0, n0);
       const int acc = it % NUM_ACC;
       const uint32_t acc_phase = (it / NUM_ACC) & 1u;
@@ -282,7 +306,20 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_after();
       const uint32_t tbase = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (EPI == EPI_GRAM ? 0 : acc * BN);
       float part = 0.f;
-      if (EPI == EPI_STORE) {
+      if (EPI == EPI_STORE && slot >= 0) {
+        // K-split unit: park the raw accumulator; the fix-up kernel adds the parts in fixed order
+        float4* dst = reinterpret_cast<float4*>(args.split_ws + (static_cast<size_t>(slot) * BM + row) * BN);
+#pragma unroll 1
+        for (int c = 0; c < BN; c += 32) {
+          uint32_t r[32];
+          tc_ld32(tbase + c, r);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            dst[c / 4 + j] = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                         __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+        }
+      } else if (EPI == EPI_STORE) {
         const int m = m0 + row;
         const size_t esz = dtype_size(args.out_dt);
         const bool vec_ok = (args.ld_out * esz) % 16 == 0;
@@ -394,6 +431,39 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
 }
 
+// ---- split-K fix-up: out = scale * (part_0 + part_1 + ...) + noise for the tiles of the tail wave ------
+__global__ void __launch_bounds__(256) splitk_fixup_kernel(const float* __restrict__ ws, int first_tile, int split,
+                                                           int M, int N, int tiles_m, int tiles_n, int n_fastest,
+                                                           void* __restrict__ out, int out_dt, long long ld_out,
+                                                           float scale, NoiseKey nk) {
+  const int t = blockIdx.y;  // index among the split tiles
+  const int q = first_tile + t;
+  const int m0 = (n_fastest ? q / tiles_n : q % tiles_m) * BM;
+  const int n0 = (n_fastest ? q % tiles_n : q / tiles_m) * BN;
+  const int e = (blockIdx.x * 256 + threadIdx.x) * 4;  // element of the tile, 4 adjacent columns
+  const int row = e / BN, col = e % BN;
+  const int m = m0 + row, n = n0 + col;
+  if (m >= M || n >= N) return;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int p = 0; p < split; ++p) {
+    const float4 v = *reinterpret_cast<const float4*>(ws + (static_cast<size_t>(t * split + p) * BM + row) * BN + col);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+  }
+  float v[4] = {acc.x * scale, acc.y * scale, acc.z * scale, acc.w * scale};
+  const size_t idx0 = static_cast<size_t>(m) * ld_out + n;
+  if (nk.std != 0.f) {
+    if ((idx0 & 3) == 0) {
+      float z[4];
+      noise_group(nk, idx0 >> 2, z);
+      v[0] += z[0]; v[1] += z[1]; v[2] += z[2]; v[3] += z[3];
+    } else {
+      for (int j = 0; j < 4; ++j) v[j] += noise_at(nk, idx0 + j);
+    }
+  }
+  for (int j = 0; j < 4; ++j)
+    if (n + j < N) store_as(out, out_dt, idx0 + j, v[j]);
+}
+
 // ---- c_b pre-scale: Gs[r,:] = c[r / T] * G[r,:] (HBM-bound, 16-byte vectors) ------------------------
 template <typename Tin>
 __global__ void __launch_bounds__(256) prescale_kernel(const Tin* __restrict__ G, const float* __restrict__ factors,
@@ -494,12 +564,42 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, co
       done[dev] = true;
     }
   }
-  const int total = args.batch * args.tiles_per_batch;
-  const int grid = total < sm_count() ? total : sm_count();
-  tc_gemm_kernel<A_MN, B_MN, EPI><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(a, b, a2, b2, args);
+  TcArgs la = args;
+  const int total = la.batch * la.tiles_per_batch;
+  if (la.split <= 1) { la.split = 1; la.units_full = total; }
+  const int units = la.units_full + (total - la.units_full) * la.split;
+  const int grid = units < sm_count() ? units : sm_count();
+  tc_gemm_kernel<A_MN, B_MN, EPI><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(a, b, a2, b2, la);
   note_launch();
   return cudaPeekAtLastError() == cudaSuccess ? FDP_OK : (cudaGetLastError(), FDP_ERR_LAUNCH);
 }
+
+// K-split of the tail wave: `rem` tiles left after the full waves are cut into s parts each so that
+// the last round keeps more SMs busy; cost in tile-times = ceil(rem*s/sms)/s.  At most 2*sms units.
+int plan_tail_split(int total_tiles, int k_stages, int sms) {
+  if (total_tiles <= sms) {
+    // fewer tiles than SMs: one partial wave
+    if (k_stages < 64) return 1;
+    int best_s = 1; double best = 1.0;
+    for (int sp = 2; sp <= 8; ++sp) {
+      if (total_tiles * sp > 2 * sms || k_stages / sp < 16) break;
+      const double cost = static_cast<double>((total_tiles * sp + sms - 1) / sms) / sp;
+      if (cost < best - 0.05) { best = cost; best_s = sp; }
+    }
+    return best_s;
+  }
+  const int rem = total_tiles % sms;
+  if (rem == 0 || k_stages < 64) return 1;
+  int best_s = 1; double best = 1.0;
+  for (int sp = 2; sp <= 8; ++sp) {
+    if (rem * sp > 2 * sms || k_stages / sp < 16) break;
+    const double cost = static_cast<double>((rem * sp + sms - 1) / sms) / sp;
+    if (cost < best - 0.05) { best = cost; best_s = sp; }
+  }
+  return best_s;
+}
+size_t split_ws_bytes() { return static_cast<size_t>(2) * sm_count() * BM * BN * sizeof(float); }
+size_t align256(size_t n) { return (n + 255) & ~static_cast<size_t>(255); }
 
 int gram_tiles(int T) {
   const int tm = ceil_div(T, BM), tn = ceil_div(T, BN);
@@ -526,8 +626,8 @@ TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo) {
   p.ok = true;
   p.algo = algo;
   p.nparts = (algo == FDP_NORM_DIRECT) ? ceil_div(n_out, BM) * ceil_div(n_in, BN) : gram_tiles(T);
-  p.ws_bytes = static_cast<size_t>(B) * T * n_out * 2;  // the c_b-scaled copy of G
-  (void)B;
+  // the c_b-scaled copy of G, then the parked accumulators of the split-K tail
+  p.ws_bytes = align256(static_cast<size_t>(B) * T * n_out * 2) + split_ws_bytes();
   return p;
 }
 
@@ -584,8 +684,26 @@ int tc_clipped_wgrad(const void* Gs, const void* X, void* dW, int* dev_status, i
   args.M = oi ? n_out : n_in; args.N = oi ? n_in : n_out; args.ld_out = args.N;
   args.tiles_m = ceil_div(args.M, BM); args.tiles_n = ceil_div(args.N, BN);
   args.tiles_per_batch = args.tiles_m * args.tiles_n;
-  return oi ? launch<true, true, EPI_STORE>(mg, mx, mg, mx, args, s)
-            : launch<true, true, EPI_STORE>(mx, mg, mx, mg, args, s);
+  // tail wave: split K so the SMs left idle by the tile count get work; parts are parked in the
+  // workspace behind Gs and summed in fixed order by the fix-up kernel (deterministic, no waits)
+  const int total = args.tiles_per_batch, sms = sm_count();
+  const int split = plan_tail_split(total, args.k_stages, sms);
+  int n_split_tiles = 0;
+  if (split > 1) {
+    n_split_tiles = total <= sms ? total : total % sms;
+    args.split = split;
+    args.units_full = total - n_split_tiles;
+    args.split_ws = reinterpret_cast<float*>(const_cast<char*>(static_cast<const char*>(Gs)) +
+                                             align256(static_cast<size_t>(rows) * n_out * 2));
+  }
+  const int st = oi ? launch<true, true, EPI_STORE>(mg, mx, mg, mx, args, s)
+                    : launch<true, true, EPI_STORE>(mx, mg, mx, mg, args, s);
+  if (st != FDP_OK || split <= 1) return st;
+  dim3 grid(BM * BN / (256 * 4), n_split_tiles);
+  splitk_fixup_kernel<<<grid, 256, 0, s>>>(args.split_ws, args.units_full, split, args.M, args.N, args.tiles_m,
+                                           args.tiles_n, args.n_fastest, dW, out_dt, args.ld_out, inv_div, nk);
+  note_launch();
+  return FDP_OK;
 }
 
 bool tc_dgrad_ok(int rows, int n_in, int n_out, int dt) {
@@ -602,6 +720,9 @@ int tc_dgrad(const void* G, const void* W, void* dX, int* dev_status, int rows, 
   args.tiles_m = ceil_div(rows, BM); args.tiles_n = ceil_div(n_in, BN);
   args.tiles_per_batch = args.tiles_m * args.tiles_n;
   args.k_stages = ceil_div(n_out, BK);
+  // G is streamed once: CTAs that run together cover a band of rows times all of n_in, so the
+  // band of G and the whole of W stay in L2 (walking along M first would re-read G per n-tile)
+  args.n_fastest = 1;
   args.out = dX; args.out_dt = dt; args.scale = 1.0f; args.nk = NoiseKey{};
   if (w_layout == FDP_OUT_IN) {  // W [n_out, n_in]: rows are K, N contiguous
     if (!make_map(&mw, W, n_out, n_in, 64, BK, dt)) return FDP_ERR_LAUNCH;

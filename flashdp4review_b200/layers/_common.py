@@ -36,3 +36,18 @@ def dp_scalars(local_batch, noise_multiplier, param_id, step, param_id2=0):
     global_batch = local_batch * world
     return global_batch, NoiseSpec(std=noise_std(noise_multiplier, global_batch), seed=runtime.get_seed(),
                                    param_id=param_id, param_id2=param_id2, step=step, rank=rank, world=world)
+
+
+def autocast_dtype(*tensors):
+    """The CUDA autocast dtype if autocast is on and the tensors live on a GPU, else None.
+
+    Under autocast the DP layers behave like their plain twins (nn.Linear, Conv1D): operands are
+    cast to the autocast dtype in forward, the output comes out in it, and the cast input is what
+    backward sees -- so the upstream gradient is 16-bit and the tensor-core kernels run.  (In the
+    reference the Conv1D forward adds an fp32 bias to the bf16 product, the output and hence the
+    whole backward become fp32 -- flashdp/layers/transformers_conv1d.py:40-43.)
+    """
+    import torch
+    if torch.is_autocast_enabled("cuda") and all(t is None or t.is_cuda for t in tensors):
+        return torch.get_autocast_dtype("cuda")
+    return None

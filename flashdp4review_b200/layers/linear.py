@@ -14,33 +14,37 @@ from .. import runtime
 from ..core import ops
 from ..core.ops import RuntimeAutoTuner
 from .utils import DPParameter as Parameter
-from ._common import DPLayerMixin, reshape_to_3d, dp_scalars
+from ._common import DPLayerMixin, reshape_to_3d, dp_scalars, autocast_dtype
 
 
 class _DPLinearFunc(Function):
     @staticmethod
     def forward(ctx, input, weight, bias, layer):
-        ctx.save_for_backward(input, weight, bias)
+        dt = autocast_dtype(input, weight)
+        x = input if dt is None else input.to(dt)
+        w = weight if dt is None else weight.to(dt)
+        ctx.save_for_backward(x, weight, bias, w if dt is not None else None)
         ctx.layer = layer
-        output = input @ weight.t()
+        output = x @ w.t()
         if bias is not None:
-            output += bias     # in place, so a bf16 autocast output stays bf16 (as in the reference)
+            output += bias if dt is None else bias.to(dt)
         return output
 
     @staticmethod
     def backward(ctx, grad_output):
-        input, weight, bias = ctx.saved_tensors
+        input, weight, bias, w_cast = ctx.saved_tensors
         layer = ctx.layer
         x3, g3 = reshape_to_3d(input, grad_output)
+        w_for_dx = weight if w_cast is None else w_cast
         B = x3.shape[0]
         step = layer._next_step()
         grad_input = grad_weight = grad_bias = None
 
         if ctx.needs_input_grad[0]:
             if runtime.input_grad_impl() == "native":
-                grad_input = ops.linear_input_grad(g3, weight, "out_in")
+                grad_input = ops.linear_input_grad(g3, w_for_dx, "out_in")
             else:
-                grad_input = g3 @ weight.to(g3.dtype)
+                grad_input = g3 @ w_for_dx.to(g3.dtype)
             grad_input = grad_input.reshape(input.shape)
 
         if ctx.needs_input_grad[1]:

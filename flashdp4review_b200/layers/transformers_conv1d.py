@@ -31,20 +31,24 @@ from .. import runtime
 from ..core import ops
 from ..core.ops import RuntimeAutoTuner
 from .utils import DPParameter as Parameter
-from ._common import DPLayerMixin, reshape_to_3d, dp_scalars
+from ._common import DPLayerMixin, reshape_to_3d, dp_scalars, autocast_dtype
 
 
 class _DPConv1DFunc(Function):
     @staticmethod
     def forward(ctx, bias, input, weight, layer):
-        ctx.save_for_backward(bias, input, weight)
+        dt = autocast_dtype(input, weight)
+        x = input if dt is None else input.to(dt)
+        w = weight if dt is None else weight.to(dt)
+        ctx.save_for_backward(bias, x, weight, w if dt is not None else None)
         ctx.layer = layer
-        return input @ weight + bias
+        return x @ w + (bias if dt is None else bias.to(dt))
 
     @staticmethod
     def backward(ctx, grad_output):
-        bias, input, weight = ctx.saved_tensors
+        bias, input, weight, w_cast = ctx.saved_tensors
         layer = ctx.layer
+        w_for_dx = weight if w_cast is None else w_cast
         x3, g3 = reshape_to_3d(input, grad_output)
         B = x3.shape[0]
         step = layer._next_step()
@@ -63,9 +67,9 @@ class _DPConv1DFunc(Function):
 
         if ctx.needs_input_grad[1]:
             if runtime.input_grad_impl() == "native":
-                grad_input = ops.linear_input_grad(g3, weight, "in_out")
+                grad_input = ops.linear_input_grad(g3, w_for_dx, "in_out")
             else:
-                grad_input = g3 @ weight.to(g3.dtype).t()
+                grad_input = g3 @ w_for_dx.to(g3.dtype).t()
             grad_input = grad_input.reshape(input.shape)
 
         if ctx.needs_input_grad[2]:
