@@ -11,6 +11,8 @@ LIB_PATH = os.path.join(PKG, "libfdp_b200.so")
 FDP_OK = 0
 FDP_ERR_ARG, FDP_ERR_DTYPE, FDP_ERR_SHAPE, FDP_ERR_ALIGN = -1, -2, -3, -4
 FDP_ERR_WORKSPACE, FDP_ERR_ARCH, FDP_ERR_LAUNCH, FDP_ERR_TIMEOUT = -5, -6, -7, -8
+FDP_ERR_STATIC_LIMIT = -9
+FDP_STATIC_SCRATCH_BYTES = 8 << 20
 FDP_F32, FDP_BF16, FDP_F16 = 0, 1, 2
 FDP_OUT_IN, FDP_IN_OUT = 0, 1
 FDP_NORM_AUTO, FDP_NORM_DIRECT, FDP_NORM_GRAM = 0, 1, 2
@@ -42,6 +44,8 @@ SIGNATURES = {
     "fdp_bias_grad_workspace_bytes": (c_size_t, [c_int] * 4),
     "fdp_bias_grad": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 5 +
                       [ctypes.POINTER(DPParams), c_void_p, c_size_t, c_void_p]),
+    "fdp_bias_grad_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 5 +
+                             [ctypes.POINTER(DPParams), c_void_p]),
     "fdp_linear_dgrad_workspace_bytes": (c_size_t, [c_int] * 4),
     "fdp_linear_dgrad": (c_int, [c_void_p, c_void_p, c_void_p] + [c_int] * 5 +
                          [c_void_p, c_size_t, c_void_p]),

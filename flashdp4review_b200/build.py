@@ -11,7 +11,7 @@ import sys
 PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "libfdp_b200.so")
-SOURCES = ["fdp_abi.cu", "fdp_simt.cu", "fdp_layernorm.cu", "fdp_tc.cu"]
+SOURCES = ["fdp_abi.cu", "fdp_simt.cu", "fdp_layernorm.cu", "fdp_tc.cu", "fdp_static.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC"]
 

@@ -127,6 +127,7 @@ const char* fdp_status_string(int status) {
     case FDP_ERR_ARCH: return "device is not sm_100 (B200)";
     case FDP_ERR_LAUNCH: return "CUDA launch/runtime error";
     case FDP_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    case FDP_ERR_STATIC_LIMIT: return "problem needs more scratch than the library's fixed buffer (FDP_STATIC_SCRATCH_BYTES)";
     default: return "unknown status";
   }
 }

@@ -33,7 +33,8 @@ enum fdp_status {
   FDP_ERR_WORKSPACE = -5, /* workspace missing or too small */
   FDP_ERR_ARCH = -6,      /* device is not sm_100 */
   FDP_ERR_LAUNCH = -7,    /* CUDA reported a launch/runtime error */
-  FDP_ERR_TIMEOUT = -8    /* a bounded device-side wait ran out (see fdp_device_status) */
+  FDP_ERR_TIMEOUT = -8,   /* a bounded device-side wait ran out (see fdp_device_status) */
+  FDP_ERR_STATIC_LIMIT = -9 /* fdp_bias_grad_static: the problem needs more scratch than FDP_STATIC_SCRATCH_BYTES */
 };
 
 /* number types: supported_acc_dtypes of flashdp/core/utils.py:9-12 (fp32 accumulation for all) */
@@ -111,6 +112,26 @@ size_t fdp_bias_grad_workspace_bytes(int B, int T, int n_out, int in_dtype);
 int fdp_bias_grad(const void* G, void* db, float* norms_out, float* factors_out, int B, int T,
                   int n_out, int in_dtype, int out_dtype, const fdp_dp_params* p, void* workspace,
                   size_t workspace_bytes, fdp_stream_t stream);
+
+/* ---- DP bias gradient without a caller workspace ---------------------------------------------
+ * No counterpart in the reference.  Same arguments and results as fdp_bias_grad minus the
+ * workspace: the partial sums go to a fixed buffer of FDP_STATIC_SCRATCH_BYTES that the library
+ * image itself carries in device memory (every GPU that loads the library holds it until exit).
+ * It is for callers that cannot allocate device memory: a host binding with no device allocator,
+ * a process whose memory pool already owns the whole GPU, or a path that must avoid the
+ * device-wide synchronisation of cudaMalloc/cudaFree.  The call itself allocates nothing.
+ * Problems that need more than the fixed buffer return FDP_ERR_STATIC_LIMIT and launch nothing
+ * (the need equals fdp_bias_grad_workspace_bytes of the same arguments).
+ * All calls on a device share the buffer: calls that overlap on the GPU race and must be
+ * serialised by the caller; the buffer keeps the previous call's contents, and every call
+ * overwrites what it reads, so no clearing is required.
+ * The first call on each device resolves the buffer's device address; issue it before starting
+ * any stream capture.
+ */
+#define FDP_STATIC_SCRATCH_BYTES (8u << 20)
+int fdp_bias_grad_static(const void* G, void* db, float* norms_out, float* factors_out, int B, int T,
+                         int n_out, int in_dtype, int out_dtype, const fdp_dp_params* p,
+                         fdp_stream_t stream);
 
 /* ---- input gradient ---------------------------------------------------------------------------
  * `grad_output @ weight` of flashdp/layers/linear.py:62-67 (w_layout FDP_OUT_IN, W [n_out,n_in]) and
