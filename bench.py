@@ -13,6 +13,7 @@ pure-PyTorch per-sample path on the host cores instead (rank 0 only).
 """
 import argparse
 import ctypes
+import datetime
 import json
 import os
 import statistics
@@ -34,6 +35,9 @@ WORKLOADS = {
 }
 DEFAULT_WORKLOAD = "linear_bf16_b32_t1024_4096x4096"
 METRIC, UNIT = "dp_linear_bwd_tflops", "TFLOP/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of one clipped-sum GEMM launch (ncu capture summarised
+# in profiles/tc_gemm_kernels_bf16_b32_t1024_4096x4096_ncu_full.md)
+TRAFFIC = {"linear_bf16_b32_t1024_4096x4096": 1.462e9}
 
 
 def peaks():
@@ -176,7 +180,8 @@ def run_native(args, wl):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        # a short collective timeout: a rank that falls out of step ends the job in minutes, not hours
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     lib = _lib.load()
     _lib.check(lib.fdp_check_device(local_rank), "fdp_check_device")
     fdp.manual_seed(1234)
@@ -257,32 +262,54 @@ def run_native(args, wl):
     launches = lib.fdp_launch_count() - launches0
     ms_per_step = total_ms / args.steps
     value = world * flops_bwd(B, T, n_in, n_out) / (ms_per_step * 1e-3) / 1e12
+    # a short timed region may see too few 20 ms clock samples: keep the same load running (untimed)
+    # until about 0.6 s of it has been observed.  Every rank runs the same number of extra steps
+    # (ms_per_step is the all-reduced maximum), because each step holds a collective.
+    extra = 0
+    if total_ms < 600.0:
+        extra = int(600.0 / max(ms_per_step, 1e-3)) + 1
+        w1 = time.time()
+        for _ in range(extra):
+            step(X, G)
+        torch.cuda.synchronize()
+        windows.append((w1, time.time()))
     clocks = None
     if sampler:
-        # a short timed region may see too few 20 ms samples: keep the same load running (untimed)
-        # until about 0.6 s of it has been observed, and say so
-        extra = 0
-        if windows[0][1] - windows[0][0] < 0.6:
-            w1 = time.time()
-            while time.time() - w1 < 0.6:
-                step(X, G)
-                extra += 1
-            torch.cuda.synchronize()
-            windows.append((w1, time.time()))
         clocks = sampler.stop(windows)
         clocks["window"] = "timed region" + (f" + {extra} more identical steps" if extra else "")
-    # end to end: host (pinned) inputs in, gradient back to the host, every step
+    # end to end: every step copies its inputs from pinned host memory and its gradient back.  The
+    # copies of step i+1 run on a second stream into a second pair of device buffers while step i
+    # computes (the copy engine and the SMs overlap; the PCIe transfer is the longer of the two).
     dW_host = torch.empty(n_out, n_in, dtype=torch.float32).pin_memory()
+    bufs = [(X, G), (torch.empty_like(X), torch.empty_like(G))]
+    copy_stream = torch.cuda.Stream(dev)
+    h2d_done = [torch.cuda.Event(), torch.cuda.Event()]
+    free = [torch.cuda.Event(), torch.cuda.Event()]
 
-    def e2e_step():
-        X.copy_(Xh, non_blocking=True)
-        G.copy_(Gh, non_blocking=True)
-        dW, dX = step(X, G)
-        dW_host.copy_(dW, non_blocking=True)
+    def h2d(slot):
+        with torch.cuda.stream(copy_stream):
+            copy_stream.wait_event(free[slot])
+            bufs[slot][0].copy_(Xh, non_blocking=True)
+            bufs[slot][1].copy_(Gh, non_blocking=True)
+            h2d_done[slot].record(copy_stream)
+
+    def e2e_run(steps):
+        cur = torch.cuda.current_stream(dev)
+        for f in free:
+            f.record(cur)
+        h2d(0)
+        for i in range(steps):
+            slot = i % 2
+            if i + 1 < steps:
+                h2d(1 - slot)
+            cur.wait_event(h2d_done[slot])
+            dW, dX = step(*bufs[slot])
+            free[slot].record(cur)
+            dW_host.copy_(dW, non_blocking=True)
 
     e2e_steps = max(2, min(args.steps, 10))
-    e2e_step()
-    e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
+    e2e_run(2)
+    e2e_ms = timed(lambda: e2e_run(e2e_steps), 1) / e2e_steps
     e2e_value = world * flops_bwd(B, T, n_in, n_out) / (e2e_ms * 1e-3) / 1e12
     h2d = Xh.numel() * Xh.element_size() + Gh.numel() * Gh.element_size()
     d2h = dW_host.numel() * 4
@@ -291,15 +318,18 @@ def run_native(args, wl):
     pk = peaks()
     roof = None
     phases = None
+    # (every rank runs these steps: each holds a collective; only rank 0 reads the phase times)
     if rank == 0:
         lib.fdp_profile_enable(1)
-        acc = [[], [], [], []]
-        for _ in range(5):
-            step(X, G)
+    acc = [[], [], [], []]
+    for _ in range(5):
+        step(X, G)
+        if rank == 0:
             ms = (ctypes.c_float * 4)()
             if lib.fdp_profile_read(ms, 4) == 4:
                 for i in range(4):
                     acc[i].append(ms[i])
+    if rank == 0:
         lib.fdp_profile_enable(0)
         if acc[3]:
             phases = {n: statistics.mean(v) for n, v in zip(("norm_pass_ms", "clip_factors_ms", "prescale_ms",
@@ -310,7 +340,7 @@ def run_native(args, wl):
                     "bound": "tensor", "achieved": achieved, "peak": pk["bf16_sustained"], "unit": "TFLOP/s",
                     "frac": achieved / pk["bf16_sustained"], "frac_of_burst_peak": achieved / pk["bf16"],
                     "peak_source": pk["source"] + " (sustained cuBLAS bf16; kernel timed inside the step loop)",
-                    "traffic": None, "phases_ms": phases,
+                    "traffic": TRAFFIC.get(args.workload), "phases_ms": phases,
                     "wgrad_path_tflops": gemm_flops / (sum(phases.values()) * 1e-3) / 1e12}
     barrier()
 
@@ -356,7 +386,9 @@ def run_hbm(args):
     G = (torch.randn(B, T, n_out, generator=gen) * 1e-3).to(dt).to(dev)
     gamma = torch.ones(d, device=dev)
     beta = torch.zeros(d, device=dev)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    # 1 GiB fill before every timed call: it overwrites the L2 and keeps the GPU busy (~170 us) while the
+    # host prepares the call, so the event pair brackets back-to-back kernels, not host latency
+    flush = torch.empty(1 << 30, dtype=torch.uint8, device=dev)
     noise = ops.NoiseSpec(std=0.25, seed=1, param_id=1, param_id2=2, step=1)
     y, buf, _ = ops.layernorm_fwd_fused(x, gamma, beta, 1e-5)
     cases = {
@@ -387,7 +419,7 @@ def run_hbm(args):
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": k["ms"], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": args.workload, "B": B, "T": T, "d": d, "n_out": n_out,
-                       "l2": "L2 overwritten by a 256 MB fill between calls",
+                       "l2": "L2 overwritten by a 1 GiB fill before every timed call",
                        "timing": "whole library call (all its kernels) per CUDA-event pair, median"},
             "roofline": {"bound": "hbm", "achieved": k["achieved_gbs"], "peak": pk["hbm"], "unit": "GB/s",
                          "frac": k["frac_of_measured_hbm"], "traffic": None, "peak_source": pk["source"]},
@@ -414,7 +446,7 @@ def run_gpt2(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     lib = _lib.load()
     fdp.manual_seed(1234)
     fdp.set_data_parallel(rank, world)

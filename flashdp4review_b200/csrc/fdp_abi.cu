@@ -184,10 +184,15 @@ int fdp_linear_wgrad(const void* G, const void* X, void* dW, float* norms_out, f
   clip_factors(w.partials, w.nparts, B, p->C, p->clamp_value, w.norms, w.factors, norms_out, factors_out, s);
   prof_mark(2, s);
   if (w.tc.ok) {
-    if ((st = tc_prescale(G, w.factors, w.tc_extra, B, T, n_out, in_dtype, s)) != FDP_OK) return st;
+    float* split_ws = static_cast<float*>(w.tc_extra);
+    char* gs = static_cast<char*>(w.tc_extra) + w.tc.split_bytes;
+    if (!w.tc.scaled_epilogue) {
+      if ((st = tc_prescale(G, w.factors, gs, B, T, n_out, in_dtype, s)) != FDP_OK) return st;
+    }
     prof_mark(3, s);
-    if ((st = tc_clipped_wgrad(w.tc_extra, X, dW, w.status, B, T, n_in, n_out, in_dtype, out_dtype, layout,
-                               inv_div, nk, s)) != FDP_OK) return st;
+    if ((st = tc_clipped_wgrad(w.tc.scaled_epilogue ? G : gs, X, w.tc.scaled_epilogue ? w.factors : nullptr,
+                               split_ws, dW, w.status, B, T, n_in, n_out, in_dtype, out_dtype, layout, inv_div,
+                               nk, s)) != FDP_OK) return st;
   } else {
     prof_mark(3, s);
     simt_clipped_wgrad(G, X, w.factors, dW, B, T, n_in, n_out, in_dtype, out_dtype, layout, inv_div, nk, s);

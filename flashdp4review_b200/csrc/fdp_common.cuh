@@ -4,6 +4,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <stdint.h>
+#include <mutex>
 
 #include "../../include/fdp_b200.h"
 
@@ -131,6 +132,23 @@ struct Carver {
     return p;
   }
 };
+
+// Opt a kernel in to more than 48 KiB of dynamic shared memory, once per device.  `done` and `mu`
+// are statics of the caller (one set per kernel).
+template <typename K>
+inline bool smem_opt_in(bool (&done)[64], std::mutex& mu, K kernel, size_t bytes) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return false; }
+  std::lock_guard<std::mutex> lk(mu);
+  if (!done[dev]) {
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess) {
+      cudaGetLastError();
+      return false;
+    }
+    done[dev] = true;
+  }
+  return true;
+}
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 inline int ceil_div(int a, int b) { return (a + b - 1) / b; }

@@ -48,8 +48,10 @@ void ln_psgrad_finalize(const float* part, const float* factors, void* out, int 
 struct TcPlan {
   bool ok;          // shapes admit the tensor-core path
   int algo;         // FDP_NORM_DIRECT or FDP_NORM_GRAM
-  size_t ws_bytes;  // extra workspace (pre-scaled G, partials)
+  size_t ws_bytes;  // extra workspace: split-K parking area, then the pre-scaled G if needed
+  size_t split_bytes;
   int nparts;       // norm partials per sample
+  bool scaled_epilogue;  // clip factors applied per sample in the GEMM epilogue, no pre-scale pass
 };
 TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo);
 int tc_norms(const void* G, const void* X, float* partials, int* dev_status, int B, int T, int n_in,
@@ -57,10 +59,11 @@ int tc_norms(const void* G, const void* X, float* partials, int* dev_status, int
 // Gs[r,:] = factors[r / T] * G[r,:]
 int tc_prescale(const void* G, const float* factors, void* Gs, int B, int T, int n_out, int dt,
                 cudaStream_t s);
-// dW = inv_div * Gs^T X + noise over K = B*T
-int tc_clipped_wgrad(const void* Gs, const void* X, void* dW, int* dev_status, int B, int T, int n_in,
-                     int n_out, int dt, int out_dt, int layout, float inv_div, NoiseKey nk,
-                     cudaStream_t s);
+// dW = inv_div * sum_b c_b G_b^T X_b + noise over K = B*T.  factors == nullptr: Gs is the pre-scaled
+// copy; otherwise Gs is G itself and c_b is applied per sample in the epilogue.
+int tc_clipped_wgrad(const void* Gs, const void* X, const float* factors, float* split_ws, void* dW,
+                     int* dev_status, int B, int T, int n_in, int n_out, int dt, int out_dt, int layout,
+                     float inv_div, NoiseKey nk, cudaStream_t s);
 bool tc_dgrad_ok(int rows, int n_in, int n_out, int dt);
 int tc_dgrad(const void* G, const void* W, void* dX, int* dev_status, int rows, int n_in, int n_out,
              int dt, int w_layout, cudaStream_t s);

@@ -1,6 +1,7 @@
 // LayerNorm forward, backward (dx + per-sample dgamma/dbeta partials) and the per-sample
 // clip / mean / noise finalisation.  All HBM-bound: 16-byte loads, each thread owns fixed columns
 // so the per-sample column sums accumulate in registers, no atomics, fixed reduction order.
+#include "fdp_async.cuh"
 #include "fdp_kernels.h"
 
 namespace fdp {
@@ -63,10 +64,112 @@ __global__ void __launch_bounds__(128) ln_fwd_kernel(const Tin* __restrict__ x,
   }
 }
 
+// Staged forward: a producer warp streams groups of 8 rows into a shared-memory ring with bulk
+// async copies (several groups in flight per SM, so HBM latency is covered whatever the occupancy);
+// eight consumer warps take one row each, reduce mean and variance out of shared memory and write y.
+constexpr int LN_MAX_STAGES = 8;
+constexpr size_t LN_SMEM_BUDGET = 192 * 1024;
+template <typename Tin>
+__global__ void __launch_bounds__(288) ln_fwd_staged_kernel(const Tin* __restrict__ x,
+                                                            const void* __restrict__ gamma,
+                                                            const void* __restrict__ beta,
+                                                            Tin* __restrict__ y, float* __restrict__ mean,
+                                                            float* __restrict__ rstd, int rows, int d,
+                                                            float eps, int pdt, int n_stages,
+                                                            int groups_per_block) {
+  constexpr int VEC = 16 / sizeof(Tin);
+  extern __shared__ __align__(128) unsigned char ln_smem[];
+  __shared__ __align__(8) unsigned long long bars[2 * LN_MAX_STAGES];
+  __shared__ int abort_flag_s;
+  volatile int* abort_flag = &abort_flag_s;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t row_bytes = static_cast<uint32_t>(d) * sizeof(Tin);
+  const uint32_t stage_bytes = 8 * row_bytes;
+  const int g0 = blockIdx.x * groups_per_block;
+  const int g1 = min(g0 + groups_per_block, (rows + 7) / 8);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < n_stages; ++s) { mbar_init(smem_u32(&bars[s]), 1); mbar_init(smem_u32(&bars[LN_MAX_STAGES + s]), 8); }
+    abort_flag_s = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (warp == 8) {
+    if (lane == 0) {
+      int s = 0; uint32_t ph = 0;
+      for (int g = g0; g < g1; ++g) {
+        if (!mbar_wait(smem_u32(&bars[LN_MAX_STAGES + s]), ph ^ 1u, abort_flag, nullptr, 0)) break;
+        const int nrows = min(8, rows - g * 8);
+        mbar_expect_tx(smem_u32(&bars[s]), nrows * row_bytes);
+        bulk_load(smem_u32(ln_smem + s * stage_bytes), x + static_cast<size_t>(g) * 8 * d, nrows * row_bytes, smem_u32(&bars[s]));
+        if (++s == n_stages) { s = 0; ph ^= 1u; }
+      }
+    }
+    return;
+  }
+  int s = 0; uint32_t ph = 0;
+  for (int g = g0; g < g1; ++g) {
+    if (!mbar_wait(smem_u32(&bars[s]), ph, abort_flag, nullptr, 0)) break;
+    const int row = g * 8 + warp;
+    if (row < rows) {
+      const Tin* xr = reinterpret_cast<const Tin*>(ln_smem + s * stage_bytes + warp * row_bytes);
+      float sum = 0.f;
+      for (int c = lane * VEC; c < d; c += 32 * VEC) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
+        const Tin* e = reinterpret_cast<const Tin*>(&raw);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) sum += to_f32<Tin>(e[v]);
+      }
+      const float mu = warp_sum(sum) / d;
+      float q = 0.f;
+      for (int c = lane * VEC; c < d; c += 32 * VEC) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
+        const Tin* e = reinterpret_cast<const Tin*>(&raw);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) { const float t = to_f32<Tin>(e[v]) - mu; q = fmaf(t, t, q); }
+      }
+      const float rs = 1.0f / sqrtf(warp_sum(q) / d + eps);
+      if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+      Tin* yr = y + static_cast<size_t>(row) * d;
+      for (int c = lane * VEC; c < d; c += 32 * VEC) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
+        const Tin* e = reinterpret_cast<const Tin*>(&raw);
+        uint4 outv;
+        Tin* o = reinterpret_cast<Tin*>(&outv);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v)
+          o[v] = from_f32<Tin>((to_f32<Tin>(e[v]) - mu) * rs * load_as(gamma, pdt, c + v) + load_as(beta, pdt, c + v));
+        *reinterpret_cast<uint4*>(yr + c) = outv;
+      }
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(smem_u32(&bars[LN_MAX_STAGES + s]));
+    if (++s == n_stages) { s = 0; ph ^= 1u; }
+  }
+}
+
 template <typename Tin>
 static void ln_fwd_t(const void* x, const void* gamma, const void* beta, void* y, float* mean,
                      float* rstd, int rows, int d, float eps, int pdt, bool vec, cudaStream_t s) {
   constexpr int V = 16 / sizeof(Tin);
+  const size_t stage_bytes = static_cast<size_t>(8) * d * sizeof(Tin);
+  if (vec && stage_bytes * 2 <= LN_SMEM_BUDGET) {
+    const int groups = ceil_div(rows, 8);
+    // a few row groups per block, one ring stage per group: several blocks share an SM and together
+    // keep most of its shared memory in flight, while the grid still covers the GPU several times
+    int gpb = groups / (148 * 4);
+    if (gpb < 2) gpb = 2;
+    if (gpb > LN_MAX_STAGES) gpb = LN_MAX_STAGES;
+    int n_stages = static_cast<int>(LN_SMEM_BUDGET / stage_bytes);
+    if (n_stages > gpb) n_stages = gpb;
+    static bool done[64];
+    static std::mutex mu;
+    if (smem_opt_in(done, mu, ln_fwd_staged_kernel<Tin>, LN_SMEM_BUDGET)) {
+      ln_fwd_staged_kernel<Tin><<<ceil_div(groups, gpb), 288, n_stages * stage_bytes, s>>>(
+          (const Tin*)x, gamma, beta, (Tin*)y, mean, rstd, rows, d, eps, pdt, n_stages, gpb);
+      note_launch();
+      return;
+    }
+  }
   dim3 grid(ceil_div(rows, 4));
   if (vec)
     ln_fwd_kernel<Tin, V><<<grid, 128, 0, s>>>((const Tin*)x, gamma, beta, (Tin*)y, mean, rstd, rows, d, eps, pdt);
@@ -92,20 +195,41 @@ void ln_fwd(const void* x, const void* gamma, const void* beta, void* y, float* 
 // rows it saw.  At the end the row groups are summed in fixed order and one partial
 // [sample, chunk, d] is written per tensor.
 // ---------------------------------------------------------------------------------------------
-template <typename Tin, int VEC, int NV, int TPR>
-__global__ void __launch_bounds__(256) ln_bwd_kernel(
+// STAGED: a ninth warp streams the rows of x and dy into a shared-memory ring with bulk async
+// copies (one stage = the RG rows the row groups work on at once), so several stages are in flight
+// per SM whatever the register-limited occupancy; the row groups read their row from the ring.
+template <typename Tin, int VEC, int NV, int TPR, bool STAGED>
+__global__ void __launch_bounds__(STAGED ? 288 : 256) ln_bwd_kernel(
     const Tin* __restrict__ dy, const Tin* __restrict__ x, const void* __restrict__ gamma,
     const float* __restrict__ mean, const float* __restrict__ rstd, Tin* __restrict__ dx,
     float* __restrict__ dg_part, float* __restrict__ db_part, int T, int d, int pdt,
-    int rows_per_block, int chunks) {
+    int rows_per_block, int chunks, int n_stages) {
   constexpr int RG = 256 / TPR;
   constexpr int NWG = TPR / 32;  // warps per row group
-  extern __shared__ float sm[];  // [RG][TPR*NV*VEC] for the final cross-group sum
+  // dynamic shared memory: the ring (STAGED), reused at the end as [RG][TPR*NV*VEC] floats for the
+  // cross-group sum
+  extern __shared__ __align__(128) unsigned char ln_smem[];
+  float* sm = reinterpret_cast<float*>(ln_smem);
   __shared__ float2 xch[RG][NWG > 1 ? NWG : 1];
-  const int rg = threadIdx.x / TPR, t = threadIdx.x % TPR;
+  __shared__ __align__(8) unsigned long long bars[2 * LN_MAX_STAGES];
+  __shared__ int abort_flag_s;
+  volatile int* abort_flag = &abort_flag_s;
+  const int rg = (threadIdx.x & 255) / TPR, t = threadIdx.x % TPR;
   const int lane = threadIdx.x & 31, wig = (threadIdx.x % TPR) >> 5;
   const int b = blockIdx.y, chunk = blockIdx.x;
   const int r0 = chunk * rows_per_block, r1 = min(T, r0 + rows_per_block);
+  const int n_iter = (r1 - r0 + RG - 1) / RG;
+  const uint32_t row_bytes = static_cast<uint32_t>(d) * sizeof(Tin);
+  const uint32_t stage_bytes = 2 * RG * row_bytes;
+
+  if (STAGED) {
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < n_stages; ++s) { mbar_init(smem_u32(&bars[s]), 1); mbar_init(smem_u32(&bars[LN_MAX_STAGES + s]), 8); }
+      abort_flag_s = 0;
+      mbar_fence_init();
+    }
+    __syncthreads();
+  }
 
   float gam[NV * VEC], accg[NV * VEC], accb[NV * VEC];
 #pragma unroll
@@ -118,71 +242,107 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(
     }
   const float inv_d = 1.0f / d;
 
-  for (int r = r0 + rg; r < r1; r += RG) {
-    const size_t row = static_cast<size_t>(b) * T + r;
-    const Tin* xr = x + row * d;
-    const Tin* dyr = dy + row * d;
-    const float mu = mean[row], rs = rstd[row];
-    float xh[NV * VEC], wd[NV * VEC];
-    float s1 = 0.f, s2 = 0.f;
-#pragma unroll
-    for (int j = 0; j < NV; ++j) {
-      const int c = (j * TPR + t) * VEC;
-      if (VEC > 1) {
-        if (c < d) {
-          const uint4 rx = *reinterpret_cast<const uint4*>(xr + c);
-          const uint4 rd = *reinterpret_cast<const uint4*>(dyr + c);
-          const Tin* ex = reinterpret_cast<const Tin*>(&rx);
-          const Tin* ed = reinterpret_cast<const Tin*>(&rd);
-#pragma unroll
-          for (int v = 0; v < VEC; ++v) {
-            const int i = j * VEC + v;
-            const float xv = (to_f32<Tin>(ex[v]) - mu) * rs, dv = to_f32<Tin>(ed[v]);
-            xh[i] = xv; wd[i] = dv * gam[i];
-            accg[i] = fmaf(dv, xv, accg[i]); accb[i] += dv;
-            s1 = fmaf(xv, wd[i], s1); s2 += wd[i];
-          }
-        } else {
-#pragma unroll
-          for (int v = 0; v < VEC; ++v) { xh[j * VEC + v] = 0.f; wd[j * VEC + v] = 0.f; }
-        }
-      } else {
-        const int i = j;
-        if (c < d) {
-          const float xv = (to_f32<Tin>(xr[c]) - mu) * rs, dv = to_f32<Tin>(dyr[c]);
-          xh[i] = xv; wd[i] = dv * gam[i];
-          accg[i] = fmaf(dv, xv, accg[i]); accb[i] += dv;
-          s1 = fmaf(xv, wd[i], s1); s2 += wd[i];
-        } else { xh[i] = 0.f; wd[i] = 0.f; }
+  if (STAGED && threadIdx.x >= 256) {
+    // ---- producer warp ----
+    if (threadIdx.x == 256) {
+      int s = 0; uint32_t ph = 0;
+      for (int it = 0; it < n_iter; ++it) {
+        if (!mbar_wait(smem_u32(&bars[LN_MAX_STAGES + s]), ph ^ 1u, abort_flag, nullptr, 0)) break;
+        const int rb = r0 + it * RG;
+        const int nrows = min(RG, r1 - rb);
+        const size_t goff = (static_cast<size_t>(b) * T + rb) * d;
+        mbar_expect_tx(smem_u32(&bars[s]), 2 * nrows * row_bytes);
+        bulk_load(smem_u32(ln_smem + s * stage_bytes), x + goff, nrows * row_bytes, smem_u32(&bars[s]));
+        bulk_load(smem_u32(ln_smem + s * stage_bytes + RG * row_bytes), dy + goff, nrows * row_bytes, smem_u32(&bars[s]));
+        if (++s == n_stages) { s = 0; ph ^= 1u; }
       }
     }
-    s1 = warp_sum(s1); s2 = warp_sum(s2);
-    if (NWG > 1) {
-      if (lane == 0) xch[rg][wig] = make_float2(s1, s2);
-      asm volatile("bar.sync %0, %1;" ::"r"(1 + rg), "r"(TPR) : "memory");
-      s1 = 0.f; s2 = 0.f;
+  } else {
+    // ---- row groups ----
+    int s = 0; uint32_t ph = 0;
+    for (int it = 0; it < n_iter; ++it) {
+      const int r = r0 + it * RG + rg;
+      const bool valid = r < r1;
+      const size_t row = static_cast<size_t>(b) * T + r;
+      const Tin* xr = x + row * d;
+      const Tin* dyr = dy + row * d;
+      if (STAGED) {
+        if (!mbar_wait(smem_u32(&bars[s]), ph, abort_flag, nullptr, 0)) break;
+        xr = reinterpret_cast<const Tin*>(ln_smem + s * stage_bytes + rg * row_bytes);
+        dyr = reinterpret_cast<const Tin*>(ln_smem + s * stage_bytes + (RG + rg) * row_bytes);
+      }
+      float xh[NV * VEC], wd[NV * VEC];
+      float s1 = 0.f, s2 = 0.f;
+      float mu = 0.f, rs = 0.f;
+      if (valid) {
+        mu = mean[row]; rs = rstd[row];
 #pragma unroll
-      for (int w = 0; w < NWG; ++w) { s1 += xch[rg][w].x; s2 += xch[rg][w].y; }
-      asm volatile("bar.sync %0, %1;" ::"r"(1 + rg), "r"(TPR) : "memory");
-    }
-    if (dx != nullptr) {
-      const float c1 = s1 * inv_d, c2 = s2 * inv_d;
-      Tin* dxr = dx + row * d;
+        for (int j = 0; j < NV; ++j) {
+          const int c = (j * TPR + t) * VEC;
+          if (VEC > 1) {
+            if (c < d) {
+              const uint4 rx = *reinterpret_cast<const uint4*>(xr + c);
+              const uint4 rd = *reinterpret_cast<const uint4*>(dyr + c);
+              const Tin* ex = reinterpret_cast<const Tin*>(&rx);
+              const Tin* ed = reinterpret_cast<const Tin*>(&rd);
 #pragma unroll
-      for (int j = 0; j < NV; ++j) {
-        const int c = (j * TPR + t) * VEC;
-        if (c >= d) continue;
-        if (VEC > 1) {
-          uint4 outv;
-          Tin* o = reinterpret_cast<Tin*>(&outv);
+              for (int v = 0; v < VEC; ++v) {
+                const int i = j * VEC + v;
+                const float xv = (to_f32<Tin>(ex[v]) - mu) * rs, dv = to_f32<Tin>(ed[v]);
+                xh[i] = xv; wd[i] = dv * gam[i];
+                accg[i] = fmaf(dv, xv, accg[i]); accb[i] += dv;
+                s1 = fmaf(xv, wd[i], s1); s2 += wd[i];
+              }
+            } else {
 #pragma unroll
-          for (int v = 0; v < VEC; ++v) {
-            const int i = j * VEC + v;
-            o[v] = from_f32<Tin>((wd[i] - (xh[i] * c1 + c2)) * rs);
+              for (int v = 0; v < VEC; ++v) { xh[j * VEC + v] = 0.f; wd[j * VEC + v] = 0.f; }
+            }
+          } else {
+            const int i = j;
+            if (c < d) {
+              const float xv = (to_f32<Tin>(xr[c]) - mu) * rs, dv = to_f32<Tin>(dyr[c]);
+              xh[i] = xv; wd[i] = dv * gam[i];
+              accg[i] = fmaf(dv, xv, accg[i]); accb[i] += dv;
+              s1 = fmaf(xv, wd[i], s1); s2 += wd[i];
+            } else { xh[i] = 0.f; wd[i] = 0.f; }
           }
-          *reinterpret_cast<uint4*>(dxr + c) = outv;
-        } else {
-          dxr[c] = from_f32<Tin>((wd[j] - (xh[j] * c1 + c2)) * rs);
+        }
+      }
+      if (STAGED) {
+        // the row is in registers: hand the stage back to the producer
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bars[LN_MAX_STAGES + s]));
+        if (++s == n_stages) { s = 0; ph ^= 1u; }
+      }
+      if (!valid) continue;
+      s1 = warp_sum(s1); s2 = warp_sum(s2);
+      if (NWG > 1) {
+        if (lane == 0) xch[rg][wig] = make_float2(s1, s2);
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + rg), "r"(TPR) : "memory");
+        s1 = 0.f; s2 = 0.f;
+#pragma unroll
+        for (int w = 0; w < NWG; ++w) { s1 += xch[rg][w].x; s2 += xch[rg][w].y; }
+        asm volatile("bar.sync %0, %1;" ::"r"(1 + rg), "r"(TPR) : "memory");
+      }
+      if (dx != nullptr) {
+        const float c1 = s1 * inv_d, c2 = s2 * inv_d;
+        Tin* dxr = dx + row * d;
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+          const int c = (j * TPR + t) * VEC;
+          if (c >= d) continue;
+          if (VEC > 1) {
+            uint4 outv;
+            Tin* o = reinterpret_cast<Tin*>(&outv);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) {
+              const int i = j * VEC + v;
+              o[v] = from_f32<Tin>((wd[i] - (xh[i] * c1 + c2)) * rs);
+            }
+            *reinterpret_cast<uint4*>(dxr + c) = outv;
+          } else {
+            dxr[c] = from_f32<Tin>((wd[j] - (xh[j] * c1 + c2)) * rs);
+          }
         }
       }
     }
@@ -194,18 +354,22 @@ __global__ void __launch_bounds__(256) ln_bwd_kernel(
 #pragma unroll
   for (int which = 0; which < 2; ++which) {
     __syncthreads();
+    if (threadIdx.x < 256) {
 #pragma unroll
-    for (int j = 0; j < NV; ++j)
+      for (int j = 0; j < NV; ++j)
 #pragma unroll
-      for (int v = 0; v < VEC; ++v)
-        sm[rg * CPG + (j * TPR + t) * VEC + v] = which == 0 ? accg[j * VEC + v] : accb[j * VEC + v];
+        for (int v = 0; v < VEC; ++v)
+          sm[rg * CPG + (j * TPR + t) * VEC + v] = which == 0 ? accg[j * VEC + v] : accb[j * VEC + v];
+    }
     __syncthreads();
     float* dst = outp[which] + (static_cast<size_t>(b) * chunks + chunk) * d;
-    for (int c = threadIdx.x; c < d; c += 256) {
-      float tot = 0.f;
+    if (threadIdx.x < 256) {
+      for (int c = threadIdx.x; c < d; c += 256) {
+        float tot = 0.f;
 #pragma unroll
-      for (int g = 0; g < RG; ++g) tot += sm[g * CPG + c];
-      dst[c] = tot;
+        for (int g = 0; g < RG; ++g) tot += sm[g * CPG + c];
+        dst[c] = tot;
+      }
     }
   }
 }
@@ -219,21 +383,48 @@ LnPlan ln_plan(int T, int d, int dt) {
   pl.cpt = nv_max * vec;
   pl.tpr = 32;
   while (pl.tpr < 256 && pl.tpr * pl.cpt < d) pl.tpr *= 2;
+  // 64-row chunks when that still gives every SM a block; partials are [B, chunks, d]
   pl.rows_per_block = 32;
   pl.chunks = ceil_div(T, pl.rows_per_block);
   return pl;
+}
+
+template <typename Tin, int VEC, int NV, int TPRV, bool STAGED>
+static bool ln_bwd_launch_one(const void* dy, const void* x, const void* gamma, const float* mean,
+                              const float* rstd, void* dx, float* dg_part, float* db_part, int B, int T,
+                              int d, int pdt, const LnPlan& pl, int n_stages, cudaStream_t s) {
+  dim3 grid(pl.chunks, B);
+  constexpr int RG = 256 / TPRV;
+  const size_t reduce_bytes = static_cast<size_t>(256) * NV * VEC * sizeof(float);
+  const size_t stage_bytes = static_cast<size_t>(2) * RG * d * sizeof(Tin);
+  size_t smem = reduce_bytes;
+  if (STAGED && n_stages * stage_bytes > smem) smem = n_stages * stage_bytes;
+  static bool done[64];
+  static std::mutex mu;
+  if (smem > 48 * 1024 && !smem_opt_in(done, mu, ln_bwd_kernel<Tin, VEC, NV, TPRV, STAGED>, LN_SMEM_BUDGET)) return false;
+  ln_bwd_kernel<Tin, VEC, NV, TPRV, STAGED><<<grid, STAGED ? 288 : 256, smem, s>>>(
+      (const Tin*)dy, (const Tin*)x, gamma, mean, rstd, (Tin*)dx, dg_part, db_part, T, d, pdt,
+      pl.rows_per_block, pl.chunks, n_stages);
+  note_launch();
+  return true;
 }
 
 template <typename Tin, int VEC, int NV>
 static void ln_bwd_launch(const void* dy, const void* x, const void* gamma, const float* mean,
                           const float* rstd, void* dx, float* dg_part, float* db_part, int B, int T,
                           int d, int pdt, const LnPlan& pl, cudaStream_t s) {
-  dim3 grid(pl.chunks, B);
-  const size_t smem = static_cast<size_t>(256) * NV * VEC * sizeof(float);
-#define FDP_LN_CASE(TPRV)                                                                           \
-  ln_bwd_kernel<Tin, VEC, NV, TPRV><<<grid, 256, smem, s>>>(                                         \
-      (const Tin*)dy, (const Tin*)x, gamma, mean, rstd, (Tin*)dx, dg_part, db_part, T, d, pdt,      \
-      pl.rows_per_block, pl.chunks)
+  // ring of up to 3 stages (two blocks then share an SM); needs 16-byte rows, i.e. the vector path
+  const size_t stage_bytes = static_cast<size_t>(2) * (256 / pl.tpr) * d * sizeof(Tin);
+  int n_stages = static_cast<int>((96 * 1024) / stage_bytes);
+  if (n_stages > 3) n_stages = 3;
+  const int n_iter = ceil_div(pl.rows_per_block, 256 / pl.tpr);
+  if (n_stages > n_iter) n_stages = n_iter;
+  const bool staged = VEC > 1 && n_stages >= 2;
+#define FDP_LN_CASE(TPRV)                                                                                    \
+  if (staged && ln_bwd_launch_one<Tin, VEC, NV, TPRV, (VEC > 1)>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, \
+                                                                 T, d, pdt, pl, n_stages, s))                  \
+    return;                                                                                                  \
+  ln_bwd_launch_one<Tin, VEC, NV, TPRV, false>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, 0, s)
   switch (pl.tpr) {
     case 32: FDP_LN_CASE(32); break;
     case 64: FDP_LN_CASE(64); break;
@@ -241,7 +432,6 @@ static void ln_bwd_launch(const void* dy, const void* x, const void* gamma, cons
     default: FDP_LN_CASE(256); break;
   }
 #undef FDP_LN_CASE
-  note_launch();
 }
 
 void ln_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,

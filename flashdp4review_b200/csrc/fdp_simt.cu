@@ -214,7 +214,21 @@ __global__ void __launch_bounds__(256) gstats_kernel(const Tin* __restrict__ G,
   float sq = 0.f;
   if (vec_ok) {
     if (c0 < n_out) {
-      for (int r = r0 + y; r < r1; r += 8) {
+      // four independent 16-byte loads in flight per thread before any of them is consumed
+      int r = r0 + y;
+      for (; r + 24 < r1; r += 32) {
+        uint4 raw[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          raw[k] = __ldg(reinterpret_cast<const uint4*>(Gb + static_cast<size_t>(r + 8 * k) * n_out + c0));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const Tin* e = reinterpret_cast<const Tin*>(&raw[k]);
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) { const float f = to_f32<Tin>(e[v]); acc[v] += f; sq = fmaf(f, f, sq); }
+        }
+      }
+      for (; r < r1; r += 8) {
         const uint4 raw = __ldg(reinterpret_cast<const uint4*>(Gb + static_cast<size_t>(r) * n_out + c0));
         const Tin* e = reinterpret_cast<const Tin*>(&raw);
 #pragma unroll

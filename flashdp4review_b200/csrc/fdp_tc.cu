@@ -10,8 +10,10 @@
 // runs out the CTA records a code in the status word, drains and leaves.
 // No TMA load here uses cluster multicast.
 #include <cuda.h>
+#include <cstdlib>
 #include <mutex>
 
+#include "fdp_async.cuh"
 #include "fdp_kernels.h"
 
 namespace fdp {
@@ -23,11 +25,12 @@ constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int BAR_BYTES = 256;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + BAR_BYTES;
-constexpr int NUM_THREADS = 192;
 constexpr int TMEM_COLS = 512;
-constexpr long long WAIT_LIMIT_CYCLES = 2000000000LL;  // about a second
 
-enum { EPI_STORE = 0, EPI_SUMSQ = 1, EPI_GRAM = 2 };
+// EPI_STORE_SCALED: the accumulator of each sample (K segment) is drained on its own and added, times
+// that sample's clip factor, to fp32 registers of eight epilogue warps; G needs no scaled copy.
+enum { EPI_STORE = 0, EPI_SUMSQ = 1, EPI_GRAM = 2, EPI_STORE_SCALED = 3 };
+constexpr int threads_for(int epi) { return epi == EPI_STORE_SCALED ? 320 : 192; }
 
 struct TcArgs {
   int M, N;             // extents of the output space of one batch (masks)
@@ -46,49 +49,23 @@ struct TcArgs {
   // into `split` K ranges whose raw fp32 accumulators go to split_ws[slot][BM][BN] for the fix-up kernel
   int units_full, split;
   float* split_ws;
+  // EPI_STORE_SCALED: K is `segs` segments (samples) of `seg_stages` stages; factors[seg] scales each
+  const float* factors;
+  int segs, seg_stages;
+  // producer prefetches the A operand's boxes of stage ks + prefetch_dist into L2 (0 = off)
+  int prefetch_dist;
 };
 
-// ---- PTX wrappers ---------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok != 0;
-}
-// bounded wait; false when it gave up (own limit or another role's abort)
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
-  if (mbar_try(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (true) {
-    if (mbar_try(bar, parity)) return true;
-    if (*abort_flag != 0) return false;
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-      *abort_flag = 1;
-      atomicCAS(status, 0, code);
-      return false;
-    }
-  }
-}
+// ---- PTX wrappers (mbarrier helpers live in fdp_async.cuh) --------------------------------------------
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+// pull a box into L2 ahead of the shared-memory load that will use it
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
+               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -136,9 +113,58 @@ __device__ __forceinline__ uint64_t operand_desc(uint32_t stage_base, int k16) {
   return make_desc(stage_base + k16 * (UMMA_K * 2), 0, 1024);
 }
 
+// Finish 32 adjacent output columns of row m starting at column n: add the noise, convert, store.
+__device__ __forceinline__ void store_chunk32(const TcArgs& args, float v[32], int m, int n) {
+  if (m >= args.M || n >= args.N) return;
+  const size_t idx0 = static_cast<size_t>(m) * args.ld_out + n;
+  if (args.nk.std != 0.f) {
+    if ((idx0 & 3) == 0) {
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        float z[4];
+        noise_group(args.nk, (idx0 >> 2) + g, z);
+        v[4 * g] += z[0]; v[4 * g + 1] += z[1]; v[4 * g + 2] += z[2]; v[4 * g + 3] += z[3];
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] += noise_at(args.nk, idx0 + j);
+    }
+  }
+  const bool vec_ok = (args.ld_out * static_cast<long long>(dtype_size(args.out_dt))) % 16 == 0;
+  if (n + 32 <= args.N && vec_ok) {
+    if (args.out_dt == FDP_F32) {
+      float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(args.out) + idx0);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+    } else {
+      uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(args.out) + idx0);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float lo = v[8 * j + 2 * e], hi = v[8 * j + 2 * e + 1];
+          if (args.out_dt == FDP_BF16) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+            w[e] = *reinterpret_cast<uint32_t*>(&h);
+          } else {
+            __half2 h = __floats2half2_rn(lo, hi);
+            w[e] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        }
+        o[j] = make_uint4(w[0], w[1], w[2], w[3]);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (n + j < args.N) store_as(args.out, args.out_dt, idx0 + j, v[j]);
+  }
+}
+
 // ---- the kernel ---------------------------------------------------------------------------------------
 template <bool A_MN, bool B_MN, int EPI>
-__global__ void __launch_bounds__(NUM_THREADS, 1)
+__global__ void __launch_bounds__(threads_for(EPI), 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
                const TcArgs args) {
@@ -165,10 +191,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), EPI == EPI_STORE_SCALED ? 8 : 4); }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_fence_init();
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -207,8 +233,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int v = u - args.units_full;
     const int part = v % args.split;
     tile = args.units_full + v / args.split;
-    ks0 = static_cast<int>(static_cast<long long>(kst_total) * part / args.split);
-    ks1 = static_cast<int>(static_cast<long long>(kst_total) * (part + 1) / args.split);
+    if (EPI == EPI_STORE_SCALED) {  // cut between samples
+      ks0 = (args.segs * part / args.split) * args.seg_stages;
+      ks1 = (args.segs * (part + 1) / args.split) * args.seg_stages;
+    } else {
+      ks0 = static_cast<int>(static_cast<long long>(kst_total) * part / args.split);
+      ks1 = static_cast<int>(static_cast<long long>(kst_total) * (part + 1) / args.split);
+    }
     slot = v;
   };
 
@@ -229,6 +260,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const CUtensorMap* mb = second ? &tmB2 : &tmB;
           const int k0 = (second ? ks - args.k_stages : ks) * BK;
           const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
+          if (A_MN && args.prefetch_dist > 0 && ks + args.prefetch_dist < ks1) {
+            // the A slab is shared by few CTAs, so most of its lines come from DRAM: request them early
+            const int kp = k0 + args.prefetch_dist * BK;
+#pragma unroll
+            for (int i = 0; i < BM / 64; ++i) tma_prefetch_2d(ma, m0 + 64 * i, row0 + kp);
+          }
           mbar_expect_tx(full_bar(stage), STAGE_BYTES);
           if (A_MN) {
 #pragma unroll
@@ -260,28 +297,34 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0; uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++it) {
+      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
         int tile, ks0, ks1, slot;
         decode_unit(u, tile, ks0, ks1, slot);
-        const int acc = it % NUM_ACC;
-        const uint32_t acc_phase = (it / NUM_ACC) & 1u;
-        if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, args.status, 2)) { ok = false; break; }
-        tc_fence_after();
-        for (int ks = ks0; ks < ks1; ++ks) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 3)) { ok = false; break; }
+        int ks = ks0;
+        // one accumulator per segment: the whole unit, or one sample for EPI_STORE_SCALED
+        while (ks < ks1 && ok) {
+          const int seg_begin = ks;
+          const int seg_end = (EPI == EPI_STORE_SCALED) ? ks + args.seg_stages : ks1;
+          const int acc = it % NUM_ACC;
+          const uint32_t acc_phase = (it / NUM_ACC) & 1u;
+          if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, args.status, 2)) { ok = false; break; }
           tc_fence_after();
-          const bool second = (EPI == EPI_GRAM) && ks >= args.k_stages;
-          const uint32_t d = tmem_base + (EPI == EPI_GRAM ? (second ? BN : 0) : acc * BN);
-          const bool first_stage = second ? (ks == args.k_stages) : (ks == ks0);
-          const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
+          for (; ks < seg_end; ++ks) {
+            if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 3)) { ok = false; break; }
+            tc_fence_after();
+            const bool second = (EPI == EPI_GRAM) && ks >= args.k_stages;
+            const uint32_t d = tmem_base + (EPI == EPI_GRAM ? (second ? BN : 0) : acc * BN);
+            const bool first_stage = second ? (ks == args.k_stages) : (ks == seg_begin);
+            const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
 #pragma unroll
-          for (int k16 = 0; k16 < BK / UMMA_K; ++k16)
-            tc_mma(d, operand_desc<A_MN>(sa, k16), operand_desc<B_MN>(sb, k16), args.idesc,
-                   (first_stage && k16 == 0) ? 0u : 1u);
-          tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            for (int k16 = 0; k16 < BK / UMMA_K; ++k16)
+              tc_mma(d, operand_desc<A_MN>(sa, k16), operand_desc<B_MN>(sb, k16), args.idesc,
+                     (first_stage && k16 == 0) ? 0u : 1u);
+            tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+          if (ok) { tc_commit(tfull_bar(acc)); ++it; }
         }
-        if (ok) tc_commit(tfull_bar(acc));
       }
       if (!ok) {
         // let MMAs already issued finish before TMEM is released
@@ -291,15 +334,58 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
   } else {
-    // ================= epilogue: warps 2..5, TMEM lane quarter = warp % 4 =================
+    // ================= epilogue: warps 2.., TMEM lane quarter = warp % 4 =================
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     int it = 0;
     bool ok = true;
-    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x, ++it) {
+    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
       int tile, ks0, ks1, slot, b, m0, n0;
       decode_unit(u, tile, ks0, ks1, slot);
       decode(tile, b, m0, n0);
+      const int m = m0 + row;
+      if (EPI == EPI_STORE_SCALED) {
+        // eight warps: two per lane quarter, each owning 128 of the tile's 256 columns in registers
+        const int half = (warp - 2) >> 2;
+        float accr[128];
+#pragma unroll
+        for (int i = 0; i < 128; ++i) accr[i] = 0.f;
+        for (int ks = ks0; ks < ks1 && ok; ks += args.seg_stages, ++it) {
+          const int acc = it % NUM_ACC;
+          const uint32_t acc_phase = (it / NUM_ACC) & 1u;
+          if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, args.status, 4)) { ok = false; break; }
+          tc_fence_after();
+          const float cb = __ldg(args.factors + ks / args.seg_stages);
+          const uint32_t tb = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + half * 128;
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            uint32_t r[32];
+            tc_ld32(tb + c4 * 32, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) accr[c4 * 32 + j] = fmaf(cb, __uint_as_float(r[j]), accr[c4 * 32 + j]);
+          }
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(tempty_bar(acc));
+        }
+        if (!ok) break;
+        if (slot >= 0) {
+          float4* dst = reinterpret_cast<float4*>(args.split_ws + (static_cast<size_t>(slot) * BM + row) * BN + half * 128);
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            dst[j] = make_float4(accr[4 * j], accr[4 * j + 1], accr[4 * j + 2], accr[4 * j + 3]);
+        } else {
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            float v[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = accr[c4 * 32 + j] * args.scale;
+            store_chunk32(args, v, m, n0 + half * 128 + c4 * 32);
+          }
+        }
+        continue;
+      }
       const int acc = it % NUM_ACC;
       const uint32_t acc_phase = (it / NUM_ACC) & 1u;
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, args.status, 4)) { ok = false; break; }
@@ -320,63 +406,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                                          __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
         }
       } else if (EPI == EPI_STORE) {
-        const int m = m0 + row;
-        const size_t esz = dtype_size(args.out_dt);
-        const bool vec_ok = (args.ld_out * esz) % 16 == 0;
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
           uint32_t r[32];
           tc_ld32(tbase + c, r);
           tc_wait_ld();
-          const int n = n0 + c;
-          if (m < args.M && n < args.N) {
-            const size_t idx0 = static_cast<size_t>(m) * args.ld_out + n;
-            float v[32];
+          float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * args.scale;
-            if (args.nk.std != 0.f) {
-              if ((idx0 & 3) == 0) {
-#pragma unroll
-                for (int g = 0; g < 8; ++g) {
-                  float z[4];
-                  noise_group(args.nk, (idx0 >> 2) + g, z);
-                  v[4 * g] += z[0]; v[4 * g + 1] += z[1]; v[4 * g + 2] += z[2]; v[4 * g + 3] += z[3];
-                }
-              } else {
-#pragma unroll 1
-                for (int j = 0; j < 32; ++j) v[j] += noise_at(args.nk, idx0 + j);
-              }
-            }
-            if (n + 32 <= args.N && vec_ok) {
-              if (args.out_dt == FDP_F32) {
-                float4* o = reinterpret_cast<float4*>(reinterpret_cast<float*>(args.out) + idx0);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) o[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-              } else {
-                uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(args.out) + idx0);
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  uint32_t w[4];
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    const float lo = v[8 * j + 2 * e], hi = v[8 * j + 2 * e + 1];
-                    if (args.out_dt == FDP_BF16) {
-                      __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
-                      w[e] = *reinterpret_cast<uint32_t*>(&h);
-                    } else {
-                      __half2 h = __floats2half2_rn(lo, hi);
-                      w[e] = *reinterpret_cast<uint32_t*>(&h);
-                    }
-                  }
-                  o[j] = make_uint4(w[0], w[1], w[2], w[3]);
-                }
-              }
-            } else {
-#pragma unroll 1
-              for (int j = 0; j < 32; ++j)
-                if (n + j < args.N) store_as(args.out, args.out_dt, idx0 + j, v[j]);
-            }
-          }
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * args.scale;
+          store_chunk32(args, v, m, n0 + c);
         }
       } else if (EPI == EPI_SUMSQ) {
         // rows / columns outside the matrix were zero-filled by TMA, so they add nothing
@@ -400,8 +438,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (t < args.T) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const int s = n0 + c + j;
-              const float w = (s >= args.T || s < t) ? 0.f : (s == t ? 1.f : 2.f);
+              const int sidx = n0 + c + j;
+              const float w = (sidx >= args.T || sidx < t) ? 0.f : (sidx == t ? 1.f : 2.f);
               part = fmaf(w * __uint_as_float(p[j]), __uint_as_float(q[j]), part);
             }
           }
@@ -411,7 +449,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
-      if (EPI != EPI_STORE) {
+      ++it;
+      if (EPI == EPI_SUMSQ || EPI == EPI_GRAM) {
         part = warp_sum(part);
         if (lane == 0) red[quarter] = part;
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -569,7 +608,7 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, co
   if (la.split <= 1) { la.split = 1; la.units_full = total; }
   const int units = la.units_full + (total - la.units_full) * la.split;
   const int grid = units < sm_count() ? units : sm_count();
-  tc_gemm_kernel<A_MN, B_MN, EPI><<<grid, NUM_THREADS, SMEM_BYTES, s>>>(a, b, a2, b2, la);
+  tc_gemm_kernel<A_MN, B_MN, EPI><<<grid, threads_for(EPI), SMEM_BYTES, s>>>(a, b, a2, b2, la);
   note_launch();
   return cudaPeekAtLastError() == cudaSuccess ? FDP_OK : (cudaGetLastError(), FDP_ERR_LAUNCH);
 }
@@ -613,7 +652,7 @@ int gram_tiles(int T) {
 // The tensor-core path needs 16-bit inputs, row pitches that are multiples of 16 bytes, and
 // matrices large enough that the 128x256 tile is not mostly padding.
 TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo) {
-  TcPlan p; p.ok = false; p.algo = FDP_NORM_DIRECT; p.ws_bytes = 0; p.nparts = 0;
+  TcPlan p; p.ok = false; p.algo = FDP_NORM_DIRECT; p.ws_bytes = 0; p.nparts = 0; p.scaled_epilogue = false;
   if (dt != FDP_BF16 && dt != FDP_F16) return p;
   if (n_in % 8 != 0 || n_out % 8 != 0 || n_in < 128 || n_out < 128 || T < 64) return p;
   const bool direct_ok = (T % BK == 0);   // a K stage must not run into the next sample's rows
@@ -625,9 +664,15 @@ TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo) {
   if (algo == FDP_NORM_DIRECT && !direct_ok) algo = FDP_NORM_GRAM;
   p.ok = true;
   p.algo = algo;
+  // clip factors applied in the GEMM epilogue (no scaled copy of G) when every 64-row K stage lies
+  // inside one sample and a sample's main loop is long enough to hide the per-sample drain;
+  // FDP_WGRAD_PRESCALE=1 forces the pre-scale pass (for A/B measurements)
+  static const bool force_prescale = [] { const char* e = getenv("FDP_WGRAD_PRESCALE"); return e && e[0] == '1'; }();
+  p.scaled_epilogue = !force_prescale && (T % BK == 0) && T >= 256;
   p.nparts = (algo == FDP_NORM_DIRECT) ? ceil_div(n_out, BM) * ceil_div(n_in, BN) : gram_tiles(T);
-  // the c_b-scaled copy of G, then the parked accumulators of the split-K tail
-  p.ws_bytes = align256(static_cast<size_t>(B) * T * n_out * 2) + split_ws_bytes();
+  // the parked accumulators of the split-K tail, then (pre-scale path only) the c_b-scaled copy of G
+  p.split_bytes = split_ws_bytes();
+  p.ws_bytes = p.split_bytes + (p.scaled_epilogue ? 0 : align256(static_cast<size_t>(B) * T * n_out * 2));
   return p;
 }
 
@@ -669,9 +714,11 @@ int tc_prescale(const void* G, const float* factors, void* Gs, int B, int T, int
   return FDP_OK;
 }
 
-int tc_clipped_wgrad(const void* Gs, const void* X, void* dW, int* dev_status, int B, int T, int n_in,
-                     int n_out, int dt, int out_dt, int layout, float inv_div, NoiseKey nk, cudaStream_t s) {
+int tc_clipped_wgrad(const void* Gs, const void* X, const float* factors, float* split_ws, void* dW,
+                     int* dev_status, int B, int T, int n_in, int n_out, int dt, int out_dt, int layout,
+                     float inv_div, NoiseKey nk, cudaStream_t s) {
   const uint64_t rows = static_cast<uint64_t>(B) * T;
+  const bool scaled = factors != nullptr;  // Gs is then the unscaled G
   CUtensorMap mg, mx;
   if (!make_map(&mg, Gs, rows, n_out, 64, BK, dt) || !make_map(&mx, X, rows, n_in, 64, BK, dt)) return FDP_ERR_LAUNCH;
   TcArgs args{};
@@ -679,25 +726,33 @@ int tc_clipped_wgrad(const void* Gs, const void* X, void* dW, int* dev_status, i
   args.k_stages = static_cast<int>((rows + BK - 1) / BK);
   args.out = dW; args.out_dt = out_dt; args.scale = inv_div; args.nk = nk;
   args.idesc = make_idesc(dt, true, true);
-  // [out,in]: A = Gs (M = n_out), B = X (N = n_in); [in,out]: operands swap roles, no transpose pass
+  if (scaled) { args.factors = factors; args.segs = B; args.seg_stages = T / BK; }
+  static const int prefetch_dist = [] { const char* e = getenv("FDP_TC_PREFETCH"); return e ? atoi(e) : 0; }();
+  args.prefetch_dist = prefetch_dist;
+  // [out,in]: A = G (M = n_out), B = X (N = n_in); [in,out]: operands swap roles, no transpose pass
   const bool oi = (layout == FDP_OUT_IN);
   args.M = oi ? n_out : n_in; args.N = oi ? n_in : n_out; args.ld_out = args.N;
   args.tiles_m = ceil_div(args.M, BM); args.tiles_n = ceil_div(args.N, BN);
   args.tiles_per_batch = args.tiles_m * args.tiles_n;
   // tail wave: split K so the SMs left idle by the tile count get work; parts are parked in the
-  // workspace behind Gs and summed in fixed order by the fix-up kernel (deterministic, no waits)
+  // workspace and summed in fixed order by the fix-up kernel (deterministic, no waits)
   const int total = args.tiles_per_batch, sms = sm_count();
-  const int split = plan_tail_split(total, args.k_stages, sms);
+  int split = plan_tail_split(total, args.k_stages, sms);
+  if (scaled && split > B) split = B;   // the scaled kernel cuts between samples
   int n_split_tiles = 0;
   if (split > 1) {
     n_split_tiles = total <= sms ? total : total % sms;
     args.split = split;
     args.units_full = total - n_split_tiles;
-    args.split_ws = reinterpret_cast<float*>(const_cast<char*>(static_cast<const char*>(Gs)) +
-                                             align256(static_cast<size_t>(rows) * n_out * 2));
+    args.split_ws = split_ws;
   }
-  const int st = oi ? launch<true, true, EPI_STORE>(mg, mx, mg, mx, args, s)
-                    : launch<true, true, EPI_STORE>(mx, mg, mx, mg, args, s);
+  int st;
+  if (scaled)
+    st = oi ? launch<true, true, EPI_STORE_SCALED>(mg, mx, mg, mx, args, s)
+            : launch<true, true, EPI_STORE_SCALED>(mx, mg, mx, mg, args, s);
+  else
+    st = oi ? launch<true, true, EPI_STORE>(mg, mx, mg, mx, args, s)
+            : launch<true, true, EPI_STORE>(mx, mg, mx, mg, args, s);
   if (st != FDP_OK || split <= 1) return st;
   dim3 grid(BM * BN / (256 * 4), n_split_tiles);
   splitk_fixup_kernel<<<grid, 256, 0, s>>>(args.split_ws, args.units_full, split, args.M, args.N, args.tiles_m,
