@@ -194,7 +194,18 @@ def run_native(args, wl):
     Gh = (torch.randn(B, T, n_out, generator=gen) * g_scale).to(dt)
     Wh = (torch.randn(n_out, n_in, generator=gen) * 0.02).to(dt)
     Xh, Gh = Xh.pin_memory(), Gh.pin_memory()
-    X, G, W = Xh.to(dev), Gh.to(dev), Wh.to(dev)
+    pad = int(os.environ.get("FDP_BENCH_PAD", "-1"))
+    if pad >= 0:
+        # X and G carved from one buffer, `pad` bytes apart (how sensitive are the kernels to the
+        # relative placement of the two streams?)
+        nb = Xh.numel() * Xh.element_size()
+        buf = torch.empty(2 * nb + pad + 512, dtype=torch.uint8, device=dev)
+        X = buf[:nb].view(dt).view(Xh.shape)
+        G = buf[nb + pad:nb + pad + Gh.numel() * Gh.element_size()].view(dt).view(Gh.shape)
+        X.copy_(Xh); G.copy_(Gh)
+        W = Wh.to(dev)
+    else:
+        X, G, W = Xh.to(dev), Gh.to(dev), Wh.to(dev)
     step_no = [0]
 
     def step(Xd, Gd):
@@ -321,9 +332,12 @@ def run_native(args, wl):
     # (every rank runs these steps: each holds a collective; only rank 0 reads the phase times)
     if rank == 0:
         lib.fdp_profile_enable(1)
+    # five back-to-back steps, phase times of the last one (read after the loop, so the measured step
+    # ran in the same steady clock/power state as the timed region)
     acc = [[], [], [], []]
-    for _ in range(5):
-        step(X, G)
+    for rep in range(3):
+        for _ in range(5):
+            step(X, G)
         if rank == 0:
             ms = (ctypes.c_float * 4)()
             if lib.fdp_profile_read(ms, 4) == 4:

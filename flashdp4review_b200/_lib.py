@@ -6,7 +6,8 @@ import ctypes
 import os
 
 PKG = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(PKG, "libfdp_b200.so")
+# FDP_B200_LIB points at another build of the same ABI (used to compare builds on one GPU)
+LIB_PATH = os.environ.get("FDP_B200_LIB") or os.path.join(PKG, "libfdp_b200.so")
 
 FDP_OK = 0
 FDP_ERR_ARG, FDP_ERR_DTYPE, FDP_ERR_SHAPE, FDP_ERR_ALIGN = -1, -2, -3, -4

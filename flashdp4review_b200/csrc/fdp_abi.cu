@@ -290,7 +290,7 @@ size_t fdp_layernorm_bwd_workspace_bytes(int B, int T, int d) {
   if (B <= 0 || T <= 0 || d <= 0) return 0;
   const LnPlan pl = ln_plan(T, d, FDP_F32);  // the chunk count does not depend on the dtype
   Carver c(nullptr);
-  c.take<float>(2 * B);                                          // sums of squares
+  c.take<float>(static_cast<size_t>(2) * B * ln_sumsq_parts(d)); // partial sums of squares
   c.take<float>(2 * B);                                          // factors
   c.take<float>(static_cast<size_t>(2) * B * pl.chunks * d);     // partials, both tensors
   return c.off;
@@ -314,7 +314,7 @@ int fdp_layernorm_bwd(const void* dy, const void* x, const void* gamma, const fl
     return FDP_ERR_WORKSPACE;
   const LnPlan pl = ln_plan(T, d, dtype);
   Carver c(workspace);
-  float* sumsq = c.take<float>(2 * B);
+  float* sumsq = c.take<float>(static_cast<size_t>(2) * B * ln_sumsq_parts(d));
   float* factors = c.take<float>(2 * B);
   float* part = c.take<float>(static_cast<size_t>(2) * B * pl.chunks * d);
   float* dg_part = part;
@@ -324,15 +324,10 @@ int fdp_layernorm_bwd(const void* dy, const void* x, const void* gamma, const fl
   const float inv_div = 1.0f / static_cast<float>(div);
   ln_bwd(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, dtype, param_dtype, pl, s);
   ln_psgrad_reduce(part, sumsq, B, pl.chunks, d, s);
-  // norms over d, one per sample and tensor (one partial each)
-  clip_factors(sumsq, 1, B, p->C, p->clamp_value, nullptr, factors, norms_gamma, nullptr, s);
-  if (dbeta != nullptr)
-    clip_factors(sumsq + B, 1, B, p->C, p->clamp_value, nullptr, factors + B, norms_beta, nullptr, s);
-  ln_psgrad_finalize(dg_part, factors, dgamma, B, pl.chunks, d, param_dtype, inv_div,
-                     make_noise_key(p, p->param_id), s);
-  if (dbeta != nullptr)
-    ln_psgrad_finalize(db_part, factors + B, dbeta, B, pl.chunks, d, param_dtype, inv_div,
-                       make_noise_key(p, p->param_id2), s);
+  // norms over d, one per sample and tensor
+  clip_factors_pair(sumsq, ln_sumsq_parts(d), B, p->C, p->clamp_value, factors, norms_gamma, norms_beta, s);
+  ln_psgrad_finalize(part, factors, dgamma, dbeta, B, pl.chunks, d, param_dtype, inv_div,
+                     make_noise_key(p, p->param_id), make_noise_key(p, p->param_id2), s);
   FDP_LAUNCH_OK();
   return FDP_OK;
 }

@@ -15,6 +15,9 @@ void simt_norm_direct(const void* G, const void* X, float* partials, int B, int 
 // sumsq_b = fixed-order sum of partials[b, 0..nparts); norm = sqrt; factor = clip_factor(norm)
 void clip_factors(const float* partials, int nparts, int B, float C, float clamp, float* norms,
                   float* factors, float* norms_out, float* factors_out, cudaStream_t s);
+// the same for 2B entries (two tensors of B samples): factors[2B]; norms go to two outputs
+void clip_factors_pair(const float* partials, int nparts, int B, float C, float clamp, float* factors,
+                       float* norms_out_first, float* norms_out_second, cudaStream_t s);
 // dW = inv_div * sum_{b,t} c_b G[b,t,:]^T X[b,t,:] + noise, stored as out_dt in `layout`
 void simt_clipped_wgrad(const void* G, const void* X, const float* factors, void* dW, int B, int T,
                         int n_in, int n_out, int dt, int out_dt, int layout, float inv_div,
@@ -39,10 +42,13 @@ void ln_fwd(const void* x, const void* gamma, const void* beta, void* y, float* 
 void ln_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,
             void* dx, float* dg_part, float* db_part, int B, int T, int d, int dt, int pdt,
             const LnPlan& pl, cudaStream_t s);
-// reduce partials over chunks -> per-sample grads [B,d] (in place in slot 0) and sums of squares
+// reduce partials over chunks -> per-sample grads [2,B,d] (in place in chunk slot 0) and partial sums
+// of squares sumsq[(tensor*B + b) * ln_sumsq_parts(d) + column block]
+int ln_sumsq_parts(int d);
 void ln_psgrad_reduce(float* part, float* sumsq, int B, int chunks, int d, cudaStream_t s);
-void ln_psgrad_finalize(const float* part, const float* factors, void* out, int B, int chunks,
-                        int d, int out_dt, float inv_div, NoiseKey nk, cudaStream_t s);
+// both tensors in one launch: out0/nk0 for dgamma, out1/nk1 for dbeta (out1 may be null)
+void ln_psgrad_finalize(const float* part, const float* factors, void* out0, void* out1, int B, int chunks,
+                        int d, int out_dt, float inv_div, NoiseKey nk0, NoiseKey nk1, cudaStream_t s);
 
 // ---- tcgen05 / TMEM / TMA kernels (bf16 / fp16, aligned shapes) ---------------------------------
 struct TcPlan {

@@ -6,6 +6,41 @@
 
 namespace fdp {
 
+// VEC adjacent affine parameters starting at column c (a multiple of VEC) as fp32: one or two
+// 16-byte loads when the parameter array is 16-byte aligned, scalar loads otherwise
+template <int VEC>
+__device__ __forceinline__ void load_params(const void* p, int pdt, int c, bool vec_ok, float out[VEC]) {
+  if (vec_ok && VEC >= 4) {
+    if (pdt == FDP_F32) {
+#pragma unroll
+      for (int k = 0; k < VEC / 4; ++k) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(p) + c / 4 + k);
+        out[4 * k] = v.x; out[4 * k + 1] = v.y; out[4 * k + 2] = v.z; out[4 * k + 3] = v.w;
+      }
+    } else {
+      const uint2* q = reinterpret_cast<const uint2*>(reinterpret_cast<const uint16_t*>(p) + c);
+#pragma unroll
+      for (int k = 0; k < VEC / 4; ++k) {
+        const uint2 raw = __ldg(q + k);
+        const uint32_t w[2] = {raw.x, raw.y};
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          if (pdt == FDP_BF16) {
+            const __nv_bfloat162 h = *reinterpret_cast<const __nv_bfloat162*>(&w[e]);
+            out[4 * k + 2 * e] = __bfloat162float(h.x); out[4 * k + 2 * e + 1] = __bfloat162float(h.y);
+          } else {
+            const __half2 h = *reinterpret_cast<const __half2*>(&w[e]);
+            out[4 * k + 2 * e] = __half2float(h.x); out[4 * k + 2 * e + 1] = __half2float(h.y);
+          }
+        }
+      }
+    }
+  } else {
+#pragma unroll
+    for (int v = 0; v < VEC; ++v) out[v] = load_as(p, pdt, c + v);
+  }
+}
+
 // ---------------------------------------------------------------------------------------------
 // forward: one warp per row; mean, biased variance (two-pass), rstd, y = xhat*gamma + beta
 // (flashdp/core/layernorm_clip.py:11-60)
@@ -68,15 +103,18 @@ __global__ void __launch_bounds__(128) ln_fwd_kernel(const Tin* __restrict__ x,
 // async copies (several groups in flight per SM, so HBM latency is covered whatever the occupancy);
 // eight consumer warps take one row each, reduce mean and variance out of shared memory and write y.
 constexpr int LN_MAX_STAGES = 8;
+constexpr int LN_MAX_ROWS_PER_BLOCK = 64;
 constexpr size_t LN_SMEM_BUDGET = 192 * 1024;
-template <typename Tin>
+// NV > 0: a lane keeps its NV vectors of the row, gamma and beta in registers (d <= 32*VEC*NV), so the
+// row is read from shared memory once; NV = 0: generic three-pass loop for longer rows.
+template <typename Tin, int NV>
 __global__ void __launch_bounds__(288) ln_fwd_staged_kernel(const Tin* __restrict__ x,
                                                             const void* __restrict__ gamma,
                                                             const void* __restrict__ beta,
                                                             Tin* __restrict__ y, float* __restrict__ mean,
                                                             float* __restrict__ rstd, int rows, int d,
                                                             float eps, int pdt, int n_stages,
-                                                            int groups_per_block) {
+                                                            int groups_per_block, int pvec_ok) {
   constexpr int VEC = 16 / sizeof(Tin);
   extern __shared__ __align__(128) unsigned char ln_smem[];
   __shared__ __align__(8) unsigned long long bars[2 * LN_MAX_STAGES];
@@ -85,8 +123,10 @@ __global__ void __launch_bounds__(288) ln_fwd_staged_kernel(const Tin* __restric
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t row_bytes = static_cast<uint32_t>(d) * sizeof(Tin);
   const uint32_t stage_bytes = 8 * row_bytes;
-  const int g0 = blockIdx.x * groups_per_block;
-  const int g1 = min(g0 + groups_per_block, (rows + 7) / 8);
+  // groups of 8 rows are dealt round-robin to a grid of two blocks per SM, so every block gets
+  // within one group of the same amount of work
+  const int g0 = blockIdx.x, g1 = (rows + 7) / 8, gstep = gridDim.x;
+  (void)groups_per_block;
   if (threadIdx.x == 0) {
     for (int s = 0; s < n_stages; ++s) { mbar_init(smem_u32(&bars[s]), 1); mbar_init(smem_u32(&bars[LN_MAX_STAGES + s]), 8); }
     abort_flag_s = 0;
@@ -96,7 +136,7 @@ __global__ void __launch_bounds__(288) ln_fwd_staged_kernel(const Tin* __restric
   if (warp == 8) {
     if (lane == 0) {
       int s = 0; uint32_t ph = 0;
-      for (int g = g0; g < g1; ++g) {
+      for (int g = g0; g < g1; g += gstep) {
         if (!mbar_wait(smem_u32(&bars[LN_MAX_STAGES + s]), ph ^ 1u, abort_flag, nullptr, 0)) break;
         const int nrows = min(8, rows - g * 8);
         mbar_expect_tx(smem_u32(&bars[s]), nrows * row_bytes);
@@ -106,10 +146,70 @@ __global__ void __launch_bounds__(288) ln_fwd_staged_kernel(const Tin* __restric
     }
     return;
   }
+  constexpr int NR = NV > 0 ? NV * VEC : 1;
+  float gv[NR], bv[NR];
+  if (NV > 0) {
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int c = (j * 32 + lane) * VEC;
+      if (c < d) {
+        load_params<VEC>(gamma, pdt, c, pvec_ok != 0, gv + j * VEC);
+        load_params<VEC>(beta, pdt, c, pvec_ok != 0, bv + j * VEC);
+      }
+    }
+  }
   int s = 0; uint32_t ph = 0;
-  for (int g = g0; g < g1; ++g) {
+  for (int g = g0; g < g1; g += gstep) {
     if (!mbar_wait(smem_u32(&bars[s]), ph, abort_flag, nullptr, 0)) break;
     const int row = g * 8 + warp;
+    if (NV > 0) {
+      // ---- the row lives in registers ----
+      const Tin* xr = reinterpret_cast<const Tin*>(ln_smem + s * stage_bytes + warp * row_bytes);
+      float xv[NR];
+      float sum = 0.f;
+      if (row < rows) {
+#pragma unroll
+        for (int j = 0; j < NV; ++j) {
+          const int c = (j * 32 + lane) * VEC;
+          if (c < d) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
+            const Tin* e = reinterpret_cast<const Tin*>(&raw);
+#pragma unroll
+            for (int v = 0; v < VEC; ++v) { xv[j * VEC + v] = to_f32<Tin>(e[v]); sum += xv[j * VEC + v]; }
+          }
+        }
+      }
+      // the stage is in registers: give it back before the arithmetic
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bars[LN_MAX_STAGES + s]));
+      if (++s == n_stages) { s = 0; ph ^= 1u; }
+      if (row >= rows) continue;
+      const float mu = warp_sum(sum) / d;
+      float q = 0.f;
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        if ((j * 32 + lane) * VEC < d) {
+#pragma unroll
+          for (int v = 0; v < VEC; ++v) { const float t = xv[j * VEC + v] - mu; q = fmaf(t, t, q); }
+        }
+      }
+      const float rs = 1.0f / sqrtf(warp_sum(q) / d + eps);
+      if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+      Tin* yr = y + static_cast<size_t>(row) * d;
+#pragma unroll
+      for (int j = 0; j < NV; ++j) {
+        const int c = (j * 32 + lane) * VEC;
+        if (c < d) {
+          uint4 outv;
+          Tin* o = reinterpret_cast<Tin*>(&outv);
+#pragma unroll
+          for (int v = 0; v < VEC; ++v)
+            o[v] = from_f32<Tin>(fmaf((xv[j * VEC + v] - mu) * rs, gv[j * VEC + v], bv[j * VEC + v]));
+          *reinterpret_cast<uint4*>(yr + c) = outv;
+        }
+      }
+      continue;
+    }
     if (row < rows) {
       const Tin* xr = reinterpret_cast<const Tin*>(ln_smem + s * stage_bytes + warp * row_bytes);
       float sum = 0.f;
@@ -133,11 +233,13 @@ __global__ void __launch_bounds__(288) ln_fwd_staged_kernel(const Tin* __restric
       for (int c = lane * VEC; c < d; c += 32 * VEC) {
         const uint4 raw = *reinterpret_cast<const uint4*>(xr + c);
         const Tin* e = reinterpret_cast<const Tin*>(&raw);
+        float gq[VEC], bq[VEC];
+        load_params<VEC>(gamma, pdt, c, pvec_ok != 0, gq);
+        load_params<VEC>(beta, pdt, c, pvec_ok != 0, bq);
         uint4 outv;
         Tin* o = reinterpret_cast<Tin*>(&outv);
 #pragma unroll
-        for (int v = 0; v < VEC; ++v)
-          o[v] = from_f32<Tin>((to_f32<Tin>(e[v]) - mu) * rs * load_as(gamma, pdt, c + v) + load_as(beta, pdt, c + v));
+        for (int v = 0; v < VEC; ++v) o[v] = from_f32<Tin>(fmaf((to_f32<Tin>(e[v]) - mu) * rs, gq[v], bq[v]));
         *reinterpret_cast<uint4*>(yr + c) = outv;
       }
     }
@@ -154,18 +256,26 @@ static void ln_fwd_t(const void* x, const void* gamma, const void* beta, void* y
   const size_t stage_bytes = static_cast<size_t>(8) * d * sizeof(Tin);
   if (vec && stage_bytes * 2 <= LN_SMEM_BUDGET) {
     const int groups = ceil_div(rows, 8);
-    // a few row groups per block, one ring stage per group: several blocks share an SM and together
-    // keep most of its shared memory in flight, while the grid still covers the GPU several times
-    int gpb = groups / (148 * 4);
-    if (gpb < 2) gpb = 2;
-    if (gpb > LN_MAX_STAGES) gpb = LN_MAX_STAGES;
-    int n_stages = static_cast<int>(LN_SMEM_BUDGET / stage_bytes);
-    if (n_stages > gpb) n_stages = gpb;
-    static bool done[64];
+    // two resident blocks per SM, each with a ring of up to 96 KiB
+    int n_stages = static_cast<int>((96 * 1024) / stage_bytes);
+    if (n_stages > LN_MAX_STAGES) n_stages = LN_MAX_STAGES;
+    if (n_stages < 2) n_stages = 2;
+    const int grid = groups < 2 * 148 ? groups : 2 * 148;
+    const int gpb = 0;
+    constexpr int NVR = 32 / V;           // register-resident rows: up to 32 columns per lane
+    const bool in_regs = d <= 32 * V * NVR;
+    static bool done[64], done_r[64];
     static std::mutex mu;
-    if (smem_opt_in(done, mu, ln_fwd_staged_kernel<Tin>, LN_SMEM_BUDGET)) {
-      ln_fwd_staged_kernel<Tin><<<ceil_div(groups, gpb), 288, n_stages * stage_bytes, s>>>(
-          (const Tin*)x, gamma, beta, (Tin*)y, mean, rstd, rows, d, eps, pdt, n_stages, gpb);
+    const int pv = aligned16(gamma) && aligned16(beta) ? 1 : 0;
+    if (in_regs && smem_opt_in(done_r, mu, ln_fwd_staged_kernel<Tin, NVR>, LN_SMEM_BUDGET)) {
+      ln_fwd_staged_kernel<Tin, NVR><<<grid, 288, n_stages * stage_bytes, s>>>(
+          (const Tin*)x, gamma, beta, (Tin*)y, mean, rstd, rows, d, eps, pdt, n_stages, gpb, pv);
+      note_launch();
+      return;
+    }
+    if (smem_opt_in(done, mu, ln_fwd_staged_kernel<Tin, 0>, LN_SMEM_BUDGET)) {
+      ln_fwd_staged_kernel<Tin, 0><<<grid, 288, n_stages * stage_bytes, s>>>(
+          (const Tin*)x, gamma, beta, (Tin*)y, mean, rstd, rows, d, eps, pdt, n_stages, gpb, pv);
       note_launch();
       return;
     }
@@ -213,6 +323,7 @@ __global__ void __launch_bounds__(STAGED ? 288 : 256) ln_bwd_kernel(
   __shared__ float2 xch[RG][NWG > 1 ? NWG : 1];
   __shared__ __align__(8) unsigned long long bars[2 * LN_MAX_STAGES];
   __shared__ int abort_flag_s;
+  __shared__ float s_mean[LN_MAX_ROWS_PER_BLOCK], s_rstd[LN_MAX_ROWS_PER_BLOCK];  // this chunk's row statistics
   volatile int* abort_flag = &abort_flag_s;
   const int rg = (threadIdx.x & 255) / TPR, t = threadIdx.x % TPR;
   const int lane = threadIdx.x & 31, wig = (threadIdx.x % TPR) >> 5;
@@ -222,14 +333,17 @@ __global__ void __launch_bounds__(STAGED ? 288 : 256) ln_bwd_kernel(
   const uint32_t row_bytes = static_cast<uint32_t>(d) * sizeof(Tin);
   const uint32_t stage_bytes = 2 * RG * row_bytes;
 
-  if (STAGED) {
-    if (threadIdx.x == 0) {
-      for (int s = 0; s < n_stages; ++s) { mbar_init(smem_u32(&bars[s]), 1); mbar_init(smem_u32(&bars[LN_MAX_STAGES + s]), 8); }
-      abort_flag_s = 0;
-      mbar_fence_init();
-    }
-    __syncthreads();
+  if (STAGED && threadIdx.x == 0) {
+    for (int s = 0; s < n_stages; ++s) { mbar_init(smem_u32(&bars[s]), 1); mbar_init(smem_u32(&bars[LN_MAX_STAGES + s]), 8); }
+    abort_flag_s = 0;
+    mbar_fence_init();
   }
+  // one parallel fetch of the chunk's mean / rstd, so no row waits on a global load of its own
+  if (threadIdx.x < r1 - r0) {
+    s_mean[threadIdx.x] = mean[static_cast<size_t>(b) * T + r0 + threadIdx.x];
+    s_rstd[threadIdx.x] = rstd[static_cast<size_t>(b) * T + r0 + threadIdx.x];
+  }
+  __syncthreads();
 
   float gam[NV * VEC], accg[NV * VEC], accb[NV * VEC];
 #pragma unroll
@@ -275,7 +389,7 @@ __global__ void __launch_bounds__(STAGED ? 288 : 256) ln_bwd_kernel(
       float s1 = 0.f, s2 = 0.f;
       float mu = 0.f, rs = 0.f;
       if (valid) {
-        mu = mean[row]; rs = rstd[row];
+        mu = s_mean[r - r0]; rs = s_rstd[r - r0];
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
           const int c = (j * TPR + t) * VEC;
@@ -383,8 +497,8 @@ LnPlan ln_plan(int T, int d, int dt) {
   pl.cpt = nv_max * vec;
   pl.tpr = 32;
   while (pl.tpr < 256 && pl.tpr * pl.cpt < d) pl.tpr *= 2;
-  // 64-row chunks when that still gives every SM a block; partials are [B, chunks, d]
-  pl.rows_per_block = 32;
+  // partials are [B, chunks, d], one chunk = 64 rows of one sample
+  pl.rows_per_block = 64;
   pl.chunks = ceil_div(T, pl.rows_per_block);
   return pl;
 }
@@ -458,40 +572,51 @@ __global__ void __launch_bounds__(256) ln_psgrad_reduce_kernel(float* __restrict
                                                                float* __restrict__ sumsq, int chunks,
                                                                int d) {
   __shared__ float red[32];
-  float* p = part + static_cast<size_t>(blockIdx.x) * chunks * d;  // blockIdx.x = tensor*B + b
+  // blockIdx.y = tensor*B + b, blockIdx.x = block of 256 columns
+  float* p = part + static_cast<size_t>(blockIdx.y) * chunks * d;
+  const int c = blockIdx.x * 256 + threadIdx.x;
   float sq = 0.f;
-  for (int c = threadIdx.x; c < d; c += 256) {
+  if (c < d) {
     float t = 0.f;
     for (int k = 0; k < chunks; ++k) t += p[static_cast<size_t>(k) * d + c];
     p[c] = t;
-    sq = fmaf(t, t, sq);
+    sq = t * t;
   }
   sq = block_sum(sq, red);
-  if (threadIdx.x == 0) sumsq[blockIdx.x] = sq;
+  if (threadIdx.x == 0) sumsq[blockIdx.y * gridDim.x + blockIdx.x] = sq;
 }
 
+int ln_sumsq_parts(int d) { return ceil_div(d, 256); }
+
 void ln_psgrad_reduce(float* part, float* sumsq, int B, int chunks, int d, cudaStream_t s) {
-  ln_psgrad_reduce_kernel<<<2 * B, 256, 0, s>>>(part, sumsq, chunks, d);
+  dim3 grid(ln_sumsq_parts(d), 2 * B);
+  ln_psgrad_reduce_kernel<<<grid, 256, 0, s>>>(part, sumsq, chunks, d);
   note_launch();
 }
 
 __global__ void __launch_bounds__(256) ln_psgrad_finalize_kernel(const float* __restrict__ part,
                                                                  const float* __restrict__ factors,
-                                                                 void* __restrict__ out, int B,
-                                                                 int chunks, int d, int out_dt,
-                                                                 float inv_div, NoiseKey nk) {
+                                                                 void* __restrict__ out0, void* __restrict__ out1,
+                                                                 int B, int chunks, int d, int out_dt,
+                                                                 float inv_div, NoiseKey nk0, NoiseKey nk1) {
   const int c = blockIdx.x * 256 + threadIdx.x;
-  if (c >= d) return;
+  const int tensor = blockIdx.y;
+  void* out = tensor == 0 ? out0 : out1;
+  if (c >= d || out == nullptr) return;
+  const float* p = part + static_cast<size_t>(tensor) * B * chunks * d;
+  const float* f = factors + tensor * B;
   float acc = 0.f;
-  for (int b = 0; b < B; ++b) acc = fmaf(factors[b], part[static_cast<size_t>(b) * chunks * d + c], acc);
+  for (int b = 0; b < B; ++b) acc = fmaf(f[b], p[static_cast<size_t>(b) * chunks * d + c], acc);
   float v = acc * inv_div;
+  const NoiseKey& nk = tensor == 0 ? nk0 : nk1;
   if (nk.std != 0.f) v += noise_at(nk, c);
   store_as(out, out_dt, c, v);
 }
 
-void ln_psgrad_finalize(const float* part, const float* factors, void* out, int B, int chunks,
-                        int d, int out_dt, float inv_div, NoiseKey nk, cudaStream_t s) {
-  ln_psgrad_finalize_kernel<<<ceil_div(d, 256), 256, 0, s>>>(part, factors, out, B, chunks, d, out_dt, inv_div, nk);
+void ln_psgrad_finalize(const float* part, const float* factors, void* out0, void* out1, int B, int chunks,
+                        int d, int out_dt, float inv_div, NoiseKey nk0, NoiseKey nk1, cudaStream_t s) {
+  dim3 grid(ceil_div(d, 256), 2);
+  ln_psgrad_finalize_kernel<<<grid, 256, 0, s>>>(part, factors, out0, out1, B, chunks, d, out_dt, inv_div, nk0, nk1);
   note_launch();
 }
 

@@ -91,10 +91,12 @@ void simt_norm_direct(const void* G, const void* X, float* partials, int B, int 
 }
 
 // ---- clip factors --------------------------------------------------------------------------------
+// split > 0: entries [split, ..) report their norm to norms_out2[b - split] (two tensors, one launch)
 __global__ void __launch_bounds__(256) clip_factors_kernel(const float* __restrict__ partials,
                                                            int nparts, float C, float clamp,
                                                            float* norms, float* factors,
-                                                           float* norms_out, float* factors_out) {
+                                                           float* norms_out, float* factors_out,
+                                                           int split, float* norms_out2) {
   __shared__ float red[32];
   const int b = blockIdx.x;
   float s = 0.f;
@@ -105,14 +107,25 @@ __global__ void __launch_bounds__(256) clip_factors_kernel(const float* __restri
     const float f = clip_factor(n, C, clamp);
     if (norms) norms[b] = n;
     factors[b] = f;
-    if (norms_out) norms_out[b] = n;
-    if (factors_out) factors_out[b] = f;
+    if (split > 0 && b >= split) {
+      if (norms_out2) norms_out2[b - split] = n;
+    } else {
+      if (norms_out) norms_out[b] = n;
+      if (factors_out) factors_out[b] = f;
+    }
   }
 }
 
 void clip_factors(const float* partials, int nparts, int B, float C, float clamp, float* norms,
                   float* factors, float* norms_out, float* factors_out, cudaStream_t s) {
-  clip_factors_kernel<<<B, 256, 0, s>>>(partials, nparts, C, clamp, norms, factors, norms_out, factors_out);
+  clip_factors_kernel<<<B, 256, 0, s>>>(partials, nparts, C, clamp, norms, factors, norms_out, factors_out, 0, nullptr);
+  note_launch();
+}
+
+void clip_factors_pair(const float* partials, int nparts, int B, float C, float clamp, float* factors,
+                       float* norms_out_first, float* norms_out_second, cudaStream_t s) {
+  clip_factors_kernel<<<2 * B, 256, 0, s>>>(partials, nparts, C, clamp, nullptr, factors, norms_out_first, nullptr, B,
+                                            norms_out_second);
   note_launch();
 }
 
@@ -267,7 +280,7 @@ GstatsPlan gstats_plan(int T, int n_out, int dt) {
   pl.vec = (dt == FDP_F32) ? 4 : 8;
   pl.cols_per_block = 32 * pl.vec;
   pl.col_chunks = ceil_div(n_out, pl.cols_per_block);
-  pl.rows_per_chunk = 64;
+  pl.rows_per_chunk = 128;  // 16 rows per thread: few partials, still thousands of blocks at LLM sizes
   pl.row_chunks = ceil_div(T, pl.rows_per_chunk);
   return pl;
 }
@@ -285,29 +298,38 @@ void gstats(const void* G, float* colsum_part, float* sq_part, int B, int T, int
   note_launch();
 }
 
-// db[o] = inv_div * sum_b c_b * sum_rc colsum_part[b,rc,o] + noise
+// db[o] = inv_div * sum_b c_b * sum_rc colsum_part[b,rc,o] + noise.
+// Block = 32 columns x 8 slices: slice s adds the (b,rc) pairs s, s+8, ... in order, then the eight
+// slice sums are added in order -- many loads in flight, still a fixed summation order.
 __global__ void __launch_bounds__(256) bias_finalize_kernel(const float* __restrict__ colsum_part,
                                                             const float* __restrict__ factors,
                                                             void* __restrict__ db, int B, int n_out,
                                                             int row_chunks, int out_dt,
                                                             float inv_div, NoiseKey nk) {
-  const int o = blockIdx.x * blockDim.x + threadIdx.x;
-  if (o >= n_out) return;
+  __shared__ float part[8][32];
+  const int col = threadIdx.x & 31, sl = threadIdx.x >> 5;
+  const int o = blockIdx.x * 32 + col;
+  const int pairs = B * row_chunks;
   float acc = 0.f;
-  for (int b = 0; b < B; ++b) {
-    float t = 0.f;
-    for (int rc = 0; rc < row_chunks; ++rc)
-      t += colsum_part[(static_cast<size_t>(b) * row_chunks + rc) * n_out + o];
-    acc = fmaf(factors[b], t, acc);
+  if (o < n_out) {
+    for (int p = sl; p < pairs; p += 8)
+      acc = fmaf(factors[p / row_chunks], colsum_part[static_cast<size_t>(p) * n_out + o], acc);
   }
-  float v = acc * inv_div;
-  if (nk.std != 0.f) v += noise_at(nk, o);
-  store_as(db, out_dt, o, v);
+  part[sl][col] = acc;
+  __syncthreads();
+  if (sl == 0 && o < n_out) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += part[k][col];
+    float v = t * inv_div;
+    if (nk.std != 0.f) v += noise_at(nk, o);
+    store_as(db, out_dt, o, v);
+  }
 }
 
 void bias_finalize(const float* colsum_part, const float* factors, void* db, int B, int n_out,
                    int row_chunks, int out_dt, float inv_div, NoiseKey nk, cudaStream_t s) {
-  bias_finalize_kernel<<<ceil_div(n_out, 256), 256, 0, s>>>(colsum_part, factors, db, B, n_out, row_chunks, out_dt, inv_div, nk);
+  bias_finalize_kernel<<<ceil_div(n_out, 32), 256, 0, s>>>(colsum_part, factors, db, B, n_out, row_chunks, out_dt, inv_div, nk);
   note_launch();
 }
 

@@ -62,6 +62,41 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(bar) : "memory");
 }
+// ---- CTA-pair (cta_group::2) helpers: the even CTA of a 2-CTA cluster issues one 256-row MMA for both;
+// loads are per CTA (no multicast), completion is signalled on the leader's mbarrier ------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t local_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t leader_bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1), "r"(leader_bar) : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
 // pull a box into L2 ahead of the shared-memory load that will use it
 __device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
   asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
@@ -163,25 +198,37 @@ __device__ __forceinline__ void store_chunk32(const TcArgs& args, float v[32], i
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------------
-template <bool A_MN, bool B_MN, int EPI>
+// CTAS = 2: a cluster of two CTAs works on one 256x256 tile.  Each CTA loads its 128 rows of A and
+// its 128 columns of B (32 KiB per stage instead of 48, six stages), the even CTA issues
+// tcgen05.mma.cta_group::2 (M = 256) for both, each CTA drains its own 128 accumulator rows.
+template <bool A_MN, bool B_MN, int EPI, int CTAS>
 __global__ void __launch_bounds__(threads_for(EPI), 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
                const TcArgs args) {
+  constexpr int NST = (CTAS == 2) ? 6 : STAGES;          // ring depth
+  constexpr int B_BYTES = B_STAGE_BYTES / CTAS;          // this CTA's share of the B stage
+  constexpr int STG = A_STAGE_BYTES + B_BYTES;
+  constexpr int BN_CTA = BN / CTAS;                      // B columns (rows if K-major) loaded by this CTA
+  constexpr int EPI_WARPS = (EPI == EPI_STORE_SCALED) ? 8 : 4;
+  static_assert(NST * STG == NST * STG, "ring size");
+  static_assert(CTAS == 1 || EPI == EPI_STORE || EPI == EPI_STORE_SCALED, "pairs: store epilogues only");
+  const uint32_t cta_rank = (CTAS == 2) ? cluster_ctarank() : 0u;
+  const bool is_leader = cta_rank == 0;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* gen_base = smem_raw + (base - raw_addr);
-  const uint32_t bar_base = base + STAGES * STAGE_BYTES;
-  uint8_t* bar_gen = gen_base + STAGES * STAGE_BYTES;
+  const uint32_t bar_base = base + NST * STG;
+  uint8_t* bar_gen = gen_base + NST * STG;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
-  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
-  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
-  const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 4);
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * (2 * STAGES + 5));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * (2 * STAGES + 5) + 4);
-  float* red = reinterpret_cast<float*>(bar_gen + 8 * (2 * STAGES + 6));  // 4 floats
+  auto empty_bar = [&](int s) { return bar_base + 8u * (NST + s); };
+  auto tfull_bar = [&](int a) { return bar_base + 8u * (2 * NST + a); };
+  auto tempty_bar = [&](int a) { return bar_base + 8u * (2 * NST + 2 + a); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * NST + 4);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * (2 * NST + 5));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * (2 * NST + 5) + 4);
+  float* red = reinterpret_cast<float*>(bar_gen + 8 * (2 * NST + 6));  // 4 floats
 
   constexpr int NUM_ACC = (EPI == EPI_GRAM) ? 1 : 2;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -190,20 +237,33 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int total_units = args.units_full + (total_tiles - args.units_full) * args.split;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), EPI == EPI_STORE_SCALED ? 8 : 4); }
+    for (int s = 0; s < NST; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), EPI_WARPS * CTAS); }
     mbar_init(drain_bar, 1);
     *abort_flag = 0;
     mbar_fence_init();
   }
+  if (CTAS == 2) {
+    // the peer's barriers must be initialised before anything is signalled across the pair
+    __syncthreads();
+    cluster_sync_all();
+  }
   if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"(TMEM_COLS) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    if (CTAS == 2) {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                   ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"(TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                   ::"r"(smem_u32(const_cast<uint32_t*>(tmem_slot))), "r"(TMEM_COLS) : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // work is dealt to CTAs (or CTA pairs) round-robin
+  const int wid = blockIdx.x / CTAS, wstep = gridDim.x / CTAS;
   const uint32_t tmem_base = *tmem_slot;
 
   // tile -> (batch, m0, n0); EPI_GRAM enumerates the (t-block, s-block) pairs that touch s >= t
@@ -220,9 +280,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       m0 = q * BM; n0 = j * BN;
     } else if (args.n_fastest) {
       n0 = (q % args.tiles_n) * BN;
-      m0 = (q / args.tiles_n) * BM;
+      m0 = (q / args.tiles_n) * (BM * CTAS) + cta_rank * BM;
     } else {
-      m0 = (q % args.tiles_m) * BM;
+      m0 = (q % args.tiles_m) * (BM * CTAS) + cta_rank * BM;
       n0 = (q / args.tiles_m) * BN;
     }
   };
@@ -248,7 +308,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+      for (int u = wid; u < total_units && ok; u += wstep) {
         int tile, ks0, ks1, slot, b, m0, n0;
         decode_unit(u, tile, ks0, ks1, slot);
         decode(tile, b, m0, n0);
@@ -259,32 +319,51 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const CUtensorMap* ma = second ? &tmA2 : &tmA;
           const CUtensorMap* mb = second ? &tmB2 : &tmB;
           const int k0 = (second ? ks - args.k_stages : ks) * BK;
-          const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
+          const uint32_t sa = base + stage * STG, sb = sa + A_STAGE_BYTES;
           if (A_MN && args.prefetch_dist > 0 && ks + args.prefetch_dist < ks1) {
             // the A slab is shared by few CTAs, so most of its lines come from DRAM: request them early
             const int kp = k0 + args.prefetch_dist * BK;
 #pragma unroll
             for (int i = 0; i < BM / 64; ++i) tma_prefetch_2d(ma, m0 + 64 * i, row0 + kp);
           }
-          mbar_expect_tx(full_bar(stage), STAGE_BYTES);
-          if (A_MN) {
+          if (CTAS == 1) {
+            mbar_expect_tx(full_bar(stage), STG);
+            if (A_MN) {
 #pragma unroll
-            for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * (BK * 128), ma, m0 + 64 * i, row0 + k0, full_bar(stage));
-          } else {
-            tma_load_2d(sa, ma, k0, row0 + m0, full_bar(stage));
-          }
-          if (B_MN) {
+              for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * (BK * 128), ma, m0 + 64 * i, row0 + k0, full_bar(stage));
+            } else {
+              tma_load_2d(sa, ma, k0, row0 + m0, full_bar(stage));
+            }
+            if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), mb, n0 + 64 * j, row0 + k0, full_bar(stage));
+              for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), mb, n0 + 64 * j, row0 + k0, full_bar(stage));
+            } else {
+              tma_load_2d(sb, mb, k0, row0 + n0, full_bar(stage));
+            }
           } else {
-            tma_load_2d(sb, mb, k0, row0 + n0, full_bar(stage));
+            // both CTAs' copies complete on the leader's barrier, which expects the bytes of both
+            const uint32_t lbar = mapa_u32(full_bar(stage), 0);
+            if (is_leader) mbar_expect_tx(full_bar(stage), 2 * STG);
+            const int nb0 = n0 + static_cast<int>(cta_rank) * BN_CTA;
+            if (A_MN) {
+#pragma unroll
+              for (int i = 0; i < BM / 64; ++i) tma_load_2d_pair(sa + i * (BK * 128), ma, m0 + 64 * i, row0 + k0, lbar);
+            } else {
+              tma_load_2d_pair(sa, ma, k0, row0 + m0, lbar);
+            }
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BN_CTA / 64; ++j) tma_load_2d_pair(sb + j * (BK * 128), mb, nb0 + 64 * j, row0 + k0, lbar);
+            } else {
+              tma_load_2d_pair(sb, mb, k0, row0 + nb0, lbar);
+            }
           }
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          if (++stage == NST) { stage = 0; phase ^= 1u; }
         }
       }
       if (!ok) {
         // wait (bounded) for the copies already in flight before the CTA may leave
-        for (int s = 0; s < STAGES; ++s) {
+        for (int s = 0; s < NST; ++s) {
           const long long t0 = clock64();
           const uint32_t ph = (s < stage) ? phase : (phase ^ 1u);
           while (!mbar_try(full_bar(s), ph) && clock64() - t0 < WAIT_LIMIT_CYCLES / 8) {}
@@ -292,12 +371,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
     }
   } else if (warp == 1) {
-    // ================= MMA issuer =================
-    if (lane == 0) {
+    // ================= MMA issuer (the leader CTA of a pair issues for both) =================
+    if (lane == 0 && is_leader) {
       int stage = 0; uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+      for (int u = wid; u < total_units && ok; u += wstep) {
         int tile, ks0, ks1, slot;
         decode_unit(u, tile, ks0, ks1, slot);
         int ks = ks0;
@@ -315,20 +394,39 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const bool second = (EPI == EPI_GRAM) && ks >= args.k_stages;
             const uint32_t d = tmem_base + (EPI == EPI_GRAM ? (second ? BN : 0) : acc * BN);
             const bool first_stage = second ? (ks == args.k_stages) : (ks == seg_begin);
-            const uint32_t sa = base + stage * STAGE_BYTES, sb = sa + A_STAGE_BYTES;
+            const uint32_t sa = base + stage * STG, sb = sa + A_STAGE_BYTES;
 #pragma unroll
-            for (int k16 = 0; k16 < BK / UMMA_K; ++k16)
-              tc_mma(d, operand_desc<A_MN>(sa, k16), operand_desc<B_MN>(sb, k16), args.idesc,
-                     (first_stage && k16 == 0) ? 0u : 1u);
-            tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+            for (int k16 = 0; k16 < BK / UMMA_K; ++k16) {
+              if (CTAS == 1)
+                tc_mma(d, operand_desc<A_MN>(sa, k16), operand_desc<B_MN>(sb, k16), args.idesc,
+                       (first_stage && k16 == 0) ? 0u : 1u);
+              else
+                tc_mma_pair(d, operand_desc<A_MN>(sa, k16), operand_desc<B_MN>(sb, k16), args.idesc,
+                            (first_stage && k16 == 0) ? 0u : 1u);
+            }
+            // frees the stage (in both CTAs of a pair) once these MMAs have read it
+            if (CTAS == 1) {
+              tc_commit(empty_bar(stage));
+            } else {
+              tc_commit_pair(empty_bar(stage));
+              tc_commit_pair(mapa_u32(empty_bar(stage), 1));
+            }
+            if (++stage == NST) { stage = 0; phase ^= 1u; }
           }
-          if (ok) { tc_commit(tfull_bar(acc)); ++it; }
+          if (ok) {
+            if (CTAS == 1) {
+              tc_commit(tfull_bar(acc));
+            } else {
+              tc_commit_pair(tfull_bar(acc));
+              tc_commit_pair(mapa_u32(tfull_bar(acc), 1));
+            }
+            ++it;
+          }
         }
       }
       if (!ok) {
         // let MMAs already issued finish before TMEM is released
-        tc_commit(drain_bar);
+        if (CTAS == 1) tc_commit(drain_bar); else tc_commit_pair(drain_bar);
         const long long t0 = clock64();
         while (!mbar_try(drain_bar, 0) && clock64() - t0 < WAIT_LIMIT_CYCLES / 8) {}
       }
@@ -339,7 +437,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int row = quarter * 32 + lane;
     int it = 0;
     bool ok = true;
-    for (int u = blockIdx.x; u < total_units && ok; u += gridDim.x) {
+    for (int u = wid; u < total_units && ok; u += wstep) {
       int tile, ks0, ks1, slot, b, m0, n0;
       decode_unit(u, tile, ks0, ks1, slot);
       decode(tile, b, m0, n0);
@@ -367,11 +465,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(tempty_bar(acc));
+          if (lane == 0) {
+            if (CTAS == 1 || is_leader) mbar_arrive(tempty_bar(acc));
+            else mbar_arrive_cluster(mapa_u32(tempty_bar(acc), 0));
+          }
         }
         if (!ok) break;
         if (slot >= 0) {
-          float4* dst = reinterpret_cast<float4*>(args.split_ws + (static_cast<size_t>(slot) * BM + row) * BN + half * 128);
+          float4* dst = reinterpret_cast<float4*>(args.split_ws + ((static_cast<size_t>(slot) * CTAS + cta_rank) * BM + row) * BN + half * 128);
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             dst[j] = make_float4(accr[4 * j], accr[4 * j + 1], accr[4 * j + 2], accr[4 * j + 3]);
@@ -394,7 +495,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       float part = 0.f;
       if (EPI == EPI_STORE && slot >= 0) {
         // K-split unit: park the raw accumulator; the fix-up kernel adds the parts in fixed order
-        float4* dst = reinterpret_cast<float4*>(args.split_ws + (static_cast<size_t>(slot) * BM + row) * BN);
+        float4* dst = reinterpret_cast<float4*>(args.split_ws + ((static_cast<size_t>(slot) * CTAS + cta_rank) * BM + row) * BN);
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
           uint32_t r[32];
@@ -445,10 +546,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
       }
-      // accumulator drained: hand it back to the MMA warp
+      // accumulator drained: hand it back to the MMA warp (of the leader CTA)
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      if (lane == 0) {
+        if (CTAS == 1 || is_leader) mbar_arrive(tempty_bar(acc));
+        else mbar_arrive_cluster(mapa_u32(tempty_bar(acc), 0));
+      }
       ++it;
       if (EPI == EPI_SUMSQ || EPI == EPI_GRAM) {
         part = warp_sum(part);
@@ -464,20 +568,24 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   __syncwarp();
   tc_fence_before();
   __syncthreads();
+  if (CTAS == 2) cluster_sync_all();  // neither CTA leaves (or frees TMEM) while its peer may still signal it
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    if (CTAS == 2)
+      asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+    else
+      asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
 // ---- split-K fix-up: out = scale * (part_0 + part_1 + ...) + noise for the tiles of the tail wave ------
 __global__ void __launch_bounds__(256) splitk_fixup_kernel(const float* __restrict__ ws, int first_tile, int split,
-                                                           int M, int N, int tiles_m, int tiles_n, int n_fastest,
+                                                           int tile_rows, int M, int N, int tiles_m, int tiles_n, int n_fastest,
                                                            void* __restrict__ out, int out_dt, long long ld_out,
                                                            float scale, NoiseKey nk) {
   const int t = blockIdx.y;  // index among the split tiles
   const int q = first_tile + t;
-  const int m0 = (n_fastest ? q / tiles_n : q % tiles_m) * BM;
+  const int m0 = (n_fastest ? q / tiles_n : q % tiles_m) * tile_rows;
   const int n0 = (n_fastest ? q % tiles_n : q / tiles_m) * BN;
   const int e = (blockIdx.x * 256 + threadIdx.x) * 4;  // element of the tile, 4 adjacent columns
   const int row = e / BN, col = e % BN;
@@ -485,7 +593,7 @@ __global__ void __launch_bounds__(256) splitk_fixup_kernel(const float* __restri
   if (m >= M || n >= N) return;
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   for (int p = 0; p < split; ++p) {
-    const float4 v = *reinterpret_cast<const float4*>(ws + (static_cast<size_t>(t * split + p) * BM + row) * BN + col);
+    const float4 v = *reinterpret_cast<const float4*>(ws + (static_cast<size_t>(t * split + p) * tile_rows + row) * BN + col);
     acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
   }
   float v[4] = {acc.x * scale, acc.y * scale, acc.z * scale, acc.w * scale};
@@ -557,7 +665,7 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, ui
   return r == CUDA_SUCCESS;
 }
 
-uint32_t make_idesc(int dt, bool a_mn, bool b_mn) {
+uint32_t make_idesc(int dt, bool a_mn, bool b_mn, int ctas = 1) {
   uint32_t d = 0;
   d |= 1u << 4;                                   // accumulator format: F32
   d |= (dt == FDP_BF16 ? 1u : 0u) << 7;           // A format
@@ -565,7 +673,7 @@ uint32_t make_idesc(int dt, bool a_mn, bool b_mn) {
   d |= (a_mn ? 1u : 0u) << 15;                    // A major: 1 = MN-major
   d |= (b_mn ? 1u : 0u) << 16;                    // B major
   d |= static_cast<uint32_t>(BN >> 3) << 17;      // N
-  d |= static_cast<uint32_t>(BM >> 4) << 24;      // M
+  d |= static_cast<uint32_t>((BM * ctas) >> 4) << 24;  // M (256 for a CTA pair)
   return d;
 }
 
@@ -584,33 +692,43 @@ int sm_count() {
   return cache[dev];
 }
 
-template <bool A_MN, bool B_MN, int EPI>
+template <bool A_MN, bool B_MN, int EPI, int CTAS = 1>
 int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, const CUtensorMap& b2,
            const TcArgs& args, cudaStream_t s) {
-  // the opt-in to >48 KiB of dynamic shared memory is per device
   static std::mutex mu;
   static bool done[64];
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return FDP_ERR_LAUNCH; }
-  {
-    std::lock_guard<std::mutex> lk(mu);
-    if (!done[dev]) {
-      if (cudaFuncSetAttribute(tc_gemm_kernel<A_MN, B_MN, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               SMEM_BYTES) != cudaSuccess) {
-        cudaGetLastError();
-        return FDP_ERR_LAUNCH;
-      }
-      done[dev] = true;
-    }
-  }
+  if (!smem_opt_in(done, mu, tc_gemm_kernel<A_MN, B_MN, EPI, CTAS>, SMEM_BYTES)) return FDP_ERR_LAUNCH;
   TcArgs la = args;
   const int total = la.batch * la.tiles_per_batch;
   if (la.split <= 1) { la.split = 1; la.units_full = total; }
   const int units = la.units_full + (total - la.units_full) * la.split;
-  const int grid = units < sm_count() ? units : sm_count();
-  tc_gemm_kernel<A_MN, B_MN, EPI><<<grid, threads_for(EPI), SMEM_BYTES, s>>>(a, b, a2, b2, la);
+  const int workers = sm_count() / CTAS;   // CTAs, or CTA pairs
+  const int grid = CTAS * (units < workers ? units : workers);
+  if (CTAS == 1) {
+    tc_gemm_kernel<A_MN, B_MN, EPI, CTAS><<<grid, threads_for(EPI), SMEM_BYTES, s>>>(a, b, a2, b2, la);
+  } else {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(threads_for(EPI));
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, tc_gemm_kernel<A_MN, B_MN, EPI, CTAS>, a, b, a2, b2, la) != cudaSuccess) {
+      cudaGetLastError();
+      return FDP_ERR_LAUNCH;
+    }
+  }
   note_launch();
   return cudaPeekAtLastError() == cudaSuccess ? FDP_OK : (cudaGetLastError(), FDP_ERR_LAUNCH);
+}
+
+// CTA pairs (cta_group::2) for the store-epilogue GEMMs unless FDP_TC_CTAS=1
+int ctas_per_tile() {
+  static const int v = [] { const char* e = getenv("FDP_TC_CTAS"); return (e && e[0] == '1') ? 1 : 2; }();
+  return v;
 }
 
 // K-split of the tail wave: `rem` tiles left after the full waves are cut into s parts each so that
@@ -637,6 +755,7 @@ int plan_tail_split(int total_tiles, int k_stages, int sms) {
   }
   return best_s;
 }
+// up to 2*SMs parked 128-row accumulators (a CTA pair parks two per slot)
 size_t split_ws_bytes() { return static_cast<size_t>(2) * sm_count() * BM * BN * sizeof(float); }
 size_t align256(size_t n) { return (n + 255) & ~static_cast<size_t>(255); }
 
@@ -725,38 +844,39 @@ int tc_clipped_wgrad(const void* Gs, const void* X, const float* factors, float*
   args.batch = 1; args.batch_rows = 0; args.status = dev_status;
   args.k_stages = static_cast<int>((rows + BK - 1) / BK);
   args.out = dW; args.out_dt = out_dt; args.scale = inv_div; args.nk = nk;
-  args.idesc = make_idesc(dt, true, true);
+  const int ctas = ctas_per_tile();
+  args.idesc = make_idesc(dt, true, true, ctas);
   if (scaled) { args.factors = factors; args.segs = B; args.seg_stages = T / BK; }
   static const int prefetch_dist = [] { const char* e = getenv("FDP_TC_PREFETCH"); return e ? atoi(e) : 0; }();
   args.prefetch_dist = prefetch_dist;
   // [out,in]: A = G (M = n_out), B = X (N = n_in); [in,out]: operands swap roles, no transpose pass
   const bool oi = (layout == FDP_OUT_IN);
   args.M = oi ? n_out : n_in; args.N = oi ? n_in : n_out; args.ld_out = args.N;
-  args.tiles_m = ceil_div(args.M, BM); args.tiles_n = ceil_div(args.N, BN);
+  args.tiles_m = ceil_div(args.M, BM * ctas); args.tiles_n = ceil_div(args.N, BN);
   args.tiles_per_batch = args.tiles_m * args.tiles_n;
   // tail wave: split K so the SMs left idle by the tile count get work; parts are parked in the
   // workspace and summed in fixed order by the fix-up kernel (deterministic, no waits)
-  const int total = args.tiles_per_batch, sms = sm_count();
-  int split = plan_tail_split(total, args.k_stages, sms);
+  const int total = args.tiles_per_batch, workers = sm_count() / ctas;
+  int split = plan_tail_split(total, args.k_stages, workers);
   if (scaled && split > B) split = B;   // the scaled kernel cuts between samples
   int n_split_tiles = 0;
   if (split > 1) {
-    n_split_tiles = total <= sms ? total : total % sms;
+    n_split_tiles = total <= workers ? total : total % workers;
     args.split = split;
     args.units_full = total - n_split_tiles;
     args.split_ws = split_ws;
   }
   int st;
-  if (scaled)
-    st = oi ? launch<true, true, EPI_STORE_SCALED>(mg, mx, mg, mx, args, s)
-            : launch<true, true, EPI_STORE_SCALED>(mx, mg, mx, mg, args, s);
-  else
-    st = oi ? launch<true, true, EPI_STORE>(mg, mx, mg, mx, args, s)
-            : launch<true, true, EPI_STORE>(mx, mg, mx, mg, args, s);
+#define FDP_WGRAD_LAUNCH(EPI_, CT_) (oi ? launch<true, true, EPI_, CT_>(mg, mx, mg, mx, args, s) \
+                                        : launch<true, true, EPI_, CT_>(mx, mg, mx, mg, args, s))
+  if (scaled) st = ctas == 2 ? FDP_WGRAD_LAUNCH(EPI_STORE_SCALED, 2) : FDP_WGRAD_LAUNCH(EPI_STORE_SCALED, 1);
+  else st = ctas == 2 ? FDP_WGRAD_LAUNCH(EPI_STORE, 2) : FDP_WGRAD_LAUNCH(EPI_STORE, 1);
+#undef FDP_WGRAD_LAUNCH
   if (st != FDP_OK || split <= 1) return st;
-  dim3 grid(BM * BN / (256 * 4), n_split_tiles);
-  splitk_fixup_kernel<<<grid, 256, 0, s>>>(args.split_ws, args.units_full, split, args.M, args.N, args.tiles_m,
-                                           args.tiles_n, args.n_fastest, dW, out_dt, args.ld_out, inv_div, nk);
+  dim3 grid(BM * ctas * BN / (256 * 4), n_split_tiles);
+  splitk_fixup_kernel<<<grid, 256, 0, s>>>(args.split_ws, args.units_full, split, BM * ctas, args.M, args.N,
+                                           args.tiles_m, args.tiles_n, args.n_fastest, dW, out_dt, args.ld_out,
+                                           inv_div, nk);
   note_launch();
   return FDP_OK;
 }
@@ -768,11 +888,12 @@ bool tc_dgrad_ok(int rows, int n_in, int n_out, int dt) {
 int tc_dgrad(const void* G, const void* W, void* dX, int* dev_status, int rows, int n_in, int n_out,
              int dt, int w_layout, cudaStream_t s) {
   CUtensorMap mg, mw;
+  const int ctas = ctas_per_tile();
   if (!make_map(&mg, G, rows, n_out, BK, BM, dt)) return FDP_ERR_LAUNCH;
   TcArgs args{};
   args.batch = 1; args.batch_rows = 0; args.status = dev_status;
   args.M = rows; args.N = n_in; args.ld_out = n_in;
-  args.tiles_m = ceil_div(rows, BM); args.tiles_n = ceil_div(n_in, BN);
+  args.tiles_m = ceil_div(rows, BM * ctas); args.tiles_n = ceil_div(n_in, BN);
   args.tiles_per_batch = args.tiles_m * args.tiles_n;
   args.k_stages = ceil_div(n_out, BK);
   // G is streamed once: CTAs that run together cover a band of rows times all of n_in, so the
@@ -781,12 +902,15 @@ int tc_dgrad(const void* G, const void* W, void* dX, int* dev_status, int rows, 
   args.out = dX; args.out_dt = dt; args.scale = 1.0f; args.nk = NoiseKey{};
   if (w_layout == FDP_OUT_IN) {  // W [n_out, n_in]: rows are K, N contiguous
     if (!make_map(&mw, W, n_out, n_in, 64, BK, dt)) return FDP_ERR_LAUNCH;
-    args.idesc = make_idesc(dt, false, true);
-    return launch<false, true, EPI_STORE>(mg, mw, mg, mw, args, s);
+    args.idesc = make_idesc(dt, false, true, ctas);
+    return ctas == 2 ? launch<false, true, EPI_STORE, 2>(mg, mw, mg, mw, args, s)
+                     : launch<false, true, EPI_STORE, 1>(mg, mw, mg, mw, args, s);
   }
-  if (!make_map(&mw, W, n_in, n_out, BK, BN, dt)) return FDP_ERR_LAUNCH;  // W [n_in, n_out]: K contiguous
-  args.idesc = make_idesc(dt, false, false);
-  return launch<false, false, EPI_STORE>(mg, mw, mg, mw, args, s);
+  // W [n_in, n_out]: K contiguous; a CTA of a pair loads half of the 256 B rows
+  if (!make_map(&mw, W, n_in, n_out, BK, BN / ctas, dt)) return FDP_ERR_LAUNCH;
+  args.idesc = make_idesc(dt, false, false, ctas);
+  return ctas == 2 ? launch<false, false, EPI_STORE, 2>(mg, mw, mg, mw, args, s)
+                   : launch<false, false, EPI_STORE, 1>(mg, mw, mg, mw, args, s);
 }
 
 }  // namespace fdp
