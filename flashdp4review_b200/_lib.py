@@ -48,7 +48,7 @@ SIGNATURES = {
     "fdp_bias_grad_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 5 +
                              [ctypes.POINTER(DPParams), c_void_p]),
     "fdp_linear_dgrad_workspace_bytes": (c_size_t, [c_int] * 4),
-    "fdp_linear_dgrad": (c_int, [c_void_p, c_void_p, c_void_p] + [c_int] * 5 +
+    "fdp_linear_dgrad": (c_int, [c_void_p, c_void_p, c_void_p] + [c_int] * 6 +
                          [c_void_p, c_size_t, c_void_p]),
     "fdp_layernorm_fwd": (c_int, [c_void_p] * 6 + [c_int, c_int, c_float, c_int, c_int, c_void_p]),
     "fdp_layernorm_bwd_workspace_bytes": (c_size_t, [c_int] * 3),

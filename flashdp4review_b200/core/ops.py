@@ -165,9 +165,10 @@ def linear_bias_grad_clip(grad_output, C, clamp_value):
 # ------------------------------------------------------------------------------------------------
 # input gradient
 # ------------------------------------------------------------------------------------------------
-def linear_input_grad(grad_output, weight, w_layout="out_in"):
+def linear_input_grad(grad_output, weight, w_layout="out_in", out_dtype=None):
     """grad_output @ weight (nn.Linear, weight [out,in]) or grad_output @ weight.t() (Conv1D,
-    weight [in,out]) -- flashdp/layers/linear.py:62-67, transformers_conv1d.py:70-75."""
+    weight [in,out]) -- flashdp/layers/linear.py:62-67, transformers_conv1d.py:70-75.
+    `out_dtype` (default: grad_output's) lets the kernel write the dtype autograd wants directly."""
     lib = _lib.load()
     _require_cuda(grad_output, weight)
     G = grad_output.contiguous()
@@ -175,10 +176,11 @@ def linear_input_grad(grad_output, weight, w_layout="out_in"):
     n_out = G.shape[-1]
     n_in = W.shape[1] if w_layout == "out_in" else W.shape[0]
     rows = G.numel() // n_out
-    dX = torch.empty(G.shape[:-1] + (n_in,), dtype=G.dtype, device=G.device)
+    out_dtype = out_dtype or G.dtype
+    dX = torch.empty(G.shape[:-1] + (n_in,), dtype=out_dtype, device=G.device)
     ws = _workspace(lib.fdp_linear_dgrad_workspace_bytes(rows, n_in, n_out, _dt(G.dtype)), G.device)
     with torch.cuda.device(G.device):
-        st = lib.fdp_linear_dgrad(_ptr(G), _ptr(W), _ptr(dX), rows, n_in, n_out, _dt(G.dtype),
+        st = lib.fdp_linear_dgrad(_ptr(G), _ptr(W), _ptr(dX), rows, n_in, n_out, _dt(G.dtype), _dt(out_dtype),
                                   _lib.FDP_OUT_IN if w_layout == "out_in" else _lib.FDP_IN_OUT,
                                   _ptr(ws), ws.numel(), _stream(G.device))
     _lib.check(st, "fdp_linear_dgrad")

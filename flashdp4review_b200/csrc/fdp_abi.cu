@@ -250,12 +250,12 @@ size_t fdp_linear_dgrad_workspace_bytes(int rows, int n_in, int n_out, int dtype
 }
 
 int fdp_linear_dgrad(const void* G, const void* W, void* dX, int rows, int n_in, int n_out,
-                     int dtype, int w_layout, void* workspace, size_t workspace_bytes,
+                     int dtype, int out_dtype, int w_layout, void* workspace, size_t workspace_bytes,
                      fdp_stream_t stream) {
   if (G == nullptr || W == nullptr || dX == nullptr) return FDP_ERR_ARG;
   if (rows <= 0 || n_in <= 0 || n_out <= 0) return FDP_ERR_ARG;
   if (w_layout != FDP_OUT_IN && w_layout != FDP_IN_OUT) return FDP_ERR_ARG;
-  if (!valid_dtype(dtype)) return FDP_ERR_DTYPE;
+  if (!valid_dtype(dtype) || !valid_dtype(out_dtype)) return FDP_ERR_DTYPE;
   int st = current_device_ok();
   if (st != FDP_OK) return st;
   if (workspace == nullptr || workspace_bytes < 256 || !aligned16(workspace)) return FDP_ERR_WORKSPACE;
@@ -263,9 +263,9 @@ int fdp_linear_dgrad(const void* G, const void* W, void* dX, int rows, int n_in,
   int* status = static_cast<int*>(workspace);
   FDP_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), s));
   if (tc_dgrad_ok(rows, n_in, n_out, dtype) && aligned16(G) && aligned16(W) && aligned16(dX)) {
-    if ((st = tc_dgrad(G, W, dX, status, rows, n_in, n_out, dtype, w_layout, s)) != FDP_OK) return st;
+    if ((st = tc_dgrad(G, W, dX, status, rows, n_in, n_out, dtype, out_dtype, w_layout, s)) != FDP_OK) return st;
   } else {
-    simt_dgrad(G, W, dX, rows, n_in, n_out, dtype, w_layout, s);
+    simt_dgrad(G, W, dX, rows, n_in, n_out, dtype, out_dtype, w_layout, s);
   }
   FDP_LAUNCH_OK();
   return FDP_OK;

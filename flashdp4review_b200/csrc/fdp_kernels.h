@@ -24,7 +24,7 @@ void simt_clipped_wgrad(const void* G, const void* X, const float* factors, void
                         NoiseKey nk, cudaStream_t s);
 // dX[rows,n_in] = G[rows,n_out] * W (W [n_out,n_in] if w_layout==FDP_OUT_IN else [n_in,n_out]^T)
 void simt_dgrad(const void* G, const void* W, void* dX, int rows, int n_in, int n_out, int dt,
-                int w_layout, cudaStream_t s);
+                int out_dt, int w_layout, cudaStream_t s);
 
 // ---- bias gradient (HBM-bound; G read once) ----------------------------------------------------
 struct GstatsPlan { int vec, cols_per_block, col_chunks, rows_per_chunk, row_chunks; };
@@ -72,6 +72,6 @@ int tc_clipped_wgrad(const void* Gs, const void* X, const float* factors, float*
                      float inv_div, NoiseKey nk, cudaStream_t s);
 bool tc_dgrad_ok(int rows, int n_in, int n_out, int dt);
 int tc_dgrad(const void* G, const void* W, void* dX, int* dev_status, int rows, int n_in, int n_out,
-             int dt, int w_layout, cudaStream_t s);
+             int dt, int out_dt, int w_layout, cudaStream_t s);
 
 }  // namespace fdp

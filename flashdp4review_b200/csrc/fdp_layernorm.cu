@@ -114,7 +114,7 @@ __global__ void __launch_bounds__(288) ln_fwd_staged_kernel(const Tin* __restric
                                                             Tin* __restrict__ y, float* __restrict__ mean,
                                                             float* __restrict__ rstd, int rows, int d,
                                                             float eps, int pdt, int n_stages,
-                                                            int groups_per_block, int pvec_ok) {
+                                                            int pvec_ok) {
   constexpr int VEC = 16 / sizeof(Tin);
   extern __shared__ __align__(128) unsigned char ln_smem[];
   __shared__ __align__(8) unsigned long long bars[2 * LN_MAX_STAGES];
@@ -126,7 +126,6 @@ __global__ void __launch_bounds__(288) ln_fwd_staged_kernel(const Tin* __restric
   // groups of 8 rows are dealt round-robin to a grid of two blocks per SM, so every block gets
   // within one group of the same amount of work
   const int g0 = blockIdx.x, g1 = (rows + 7) / 8, gstep = gridDim.x;
-  (void)groups_per_block;
   if (threadIdx.x == 0) {
     for (int s = 0; s < n_stages; ++s) { mbar_init(smem_u32(&bars[s]), 1); mbar_init(smem_u32(&bars[LN_MAX_STAGES + s]), 8); }
     abort_flag_s = 0;
@@ -261,7 +260,6 @@ static void ln_fwd_t(const void* x, const void* gamma, const void* beta, void* y
     if (n_stages > LN_MAX_STAGES) n_stages = LN_MAX_STAGES;
     if (n_stages < 2) n_stages = 2;
     const int grid = groups < 2 * 148 ? groups : 2 * 148;
-    const int gpb = 0;
     constexpr int NVR = 32 / V;           // register-resident rows: up to 32 columns per lane
     const bool in_regs = d <= 32 * V * NVR;
     static bool done[64], done_r[64];
@@ -269,13 +267,13 @@ static void ln_fwd_t(const void* x, const void* gamma, const void* beta, void* y
     const int pv = aligned16(gamma) && aligned16(beta) ? 1 : 0;
     if (in_regs && smem_opt_in(done_r, mu, ln_fwd_staged_kernel<Tin, NVR>, LN_SMEM_BUDGET)) {
       ln_fwd_staged_kernel<Tin, NVR><<<grid, 288, n_stages * stage_bytes, s>>>(
-          (const Tin*)x, gamma, beta, (Tin*)y, mean, rstd, rows, d, eps, pdt, n_stages, gpb, pv);
+          (const Tin*)x, gamma, beta, (Tin*)y, mean, rstd, rows, d, eps, pdt, n_stages, pv);
       note_launch();
       return;
     }
     if (smem_opt_in(done, mu, ln_fwd_staged_kernel<Tin, 0>, LN_SMEM_BUDGET)) {
       ln_fwd_staged_kernel<Tin, 0><<<grid, 288, n_stages * stage_bytes, s>>>(
-          (const Tin*)x, gamma, beta, (Tin*)y, mean, rstd, rows, d, eps, pdt, n_stages, gpb, pv);
+          (const Tin*)x, gamma, beta, (Tin*)y, mean, rstd, rows, d, eps, pdt, n_stages, pv);
       note_launch();
       return;
     }
@@ -493,7 +491,9 @@ LnPlan ln_plan(int T, int d, int dt) {
   const int V = 16 / static_cast<int>(dtype_size(dt));
   pl.vec = (d % V == 0);
   const int vec = pl.vec ? V : 1;
-  const int nv_max = pl.vec ? (32 / V) : 32;  // 32 columns per thread at most
+  // columns per thread: 32 (16-bit) or 16 (fp32 up to d = 4096, so a ring stage stays 32 KiB)
+  int nv_max = pl.vec ? (32 / V) : 32;
+  if (pl.vec && dt == FDP_F32 && d <= 4096) nv_max = 4;
   pl.cpt = nv_max * vec;
   pl.tpr = 32;
   while (pl.tpr < 256 && pl.tpr * pl.cpt < d) pl.tpr *= 2;
@@ -553,7 +553,8 @@ void ln_bwd(const void* dy, const void* x, const void* gamma, const float* mean,
             const LnPlan& pl, cudaStream_t s) {
   const bool vec = pl.vec && aligned16(dy) && aligned16(x) && (dx == nullptr || aligned16(dx));
   if (dt == FDP_F32) {
-    if (vec) ln_bwd_launch<float, 4, 8>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s);
+    if (vec && pl.cpt == 16) ln_bwd_launch<float, 4, 4>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s);
+    else if (vec) ln_bwd_launch<float, 4, 8>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s);
     else ln_bwd_launch<float, 1, 32>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s);
   } else if (dt == FDP_BF16) {
     if (vec) ln_bwd_launch<__nv_bfloat16, 8, 4>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s);

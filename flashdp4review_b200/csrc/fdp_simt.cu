@@ -173,8 +173,8 @@ void simt_clipped_wgrad(const void* G, const void* X, const float* factors, void
 template <typename Tin>
 __global__ void __launch_bounds__(256) simt_dgrad_kernel(const Tin* __restrict__ G,
                                                          const Tin* __restrict__ W,
-                                                         Tin* __restrict__ dX, int rows, int n_in,
-                                                         int n_out, int w_layout) {
+                                                         void* __restrict__ dX, int out_dt, int rows,
+                                                         int n_in, int n_out, int w_layout) {
   float acc[4][4] = {};
   const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
   // A(k=o, m=r) = G[r*n_out + o];  B(k=o, n=i) = W[o*n_in + i] (OUT_IN) or W[i*n_out + o] (IN_OUT)
@@ -188,20 +188,20 @@ __global__ void __launch_bounds__(256) simt_dgrad_kernel(const Tin* __restrict__
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int n = n0 + tx * 4 + j;
-      if (n < n_in) dX[static_cast<size_t>(m) * n_in + n] = from_f32<Tin>(acc[i][j]);
+      if (n < n_in) store_as(dX, out_dt, static_cast<size_t>(m) * n_in + n, acc[i][j]);
     }
   }
 }
 
 void simt_dgrad(const void* G, const void* W, void* dX, int rows, int n_in, int n_out, int dt,
-                int w_layout, cudaStream_t s) {
+                int out_dt, int w_layout, cudaStream_t s) {
   dim3 grid(ceil_div(n_in, TN), ceil_div(rows, TM));
   if (dt == FDP_F32)
-    simt_dgrad_kernel<float><<<grid, 256, 0, s>>>((const float*)G, (const float*)W, (float*)dX, rows, n_in, n_out, w_layout);
+    simt_dgrad_kernel<float><<<grid, 256, 0, s>>>((const float*)G, (const float*)W, dX, out_dt, rows, n_in, n_out, w_layout);
   else if (dt == FDP_BF16)
-    simt_dgrad_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)G, (const __nv_bfloat16*)W, (__nv_bfloat16*)dX, rows, n_in, n_out, w_layout);
+    simt_dgrad_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)G, (const __nv_bfloat16*)W, dX, out_dt, rows, n_in, n_out, w_layout);
   else
-    simt_dgrad_kernel<__half><<<grid, 256, 0, s>>>((const __half*)G, (const __half*)W, (__half*)dX, rows, n_in, n_out, w_layout);
+    simt_dgrad_kernel<__half><<<grid, 256, 0, s>>>((const __half*)G, (const __half*)W, dX, out_dt, rows, n_in, n_out, w_layout);
   note_launch();
 }
 

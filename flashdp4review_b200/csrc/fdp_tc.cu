@@ -54,6 +54,11 @@ struct TcArgs {
   int segs, seg_stages;
   // producer prefetches the A operand's boxes of stage ks + prefetch_dist into L2 (0 = off)
   int prefetch_dist;
+  // EPI_GRAM: per sample `gram_full` tiles need all 256 s-columns and `gram_half` tiles (the t-block is
+  // the lower half of the s-block) only columns 128..255, done with an N = 128 MMA (idesc_half).
+  // Tiles are numbered full tiles of all samples first, then the half tiles.
+  int gram_full, gram_half;
+  uint32_t idesc_half;
 };
 
 // ---- PTX wrappers (mbarrier helpers live in fdp_async.cuh) --------------------------------------------
@@ -266,25 +271,45 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int wid = blockIdx.x / CTAS, wstep = gridDim.x / CTAS;
   const uint32_t tmem_base = *tmem_slot;
 
-  // tile -> (batch, m0, n0); EPI_GRAM enumerates the (t-block, s-block) pairs that touch s >= t
-  auto decode = [&](int tile, int& b, int& m0, int& n0) {
-    b = tile / args.tiles_per_batch;
-    int q = tile - b * args.tiles_per_batch;
+  // tile -> (batch, m0, n0, half).  EPI_GRAM: tiles [0, batch*gram_full) are the full (t-block, s-block)
+  // pairs with t-block <= 2*s-block, the rest are the half tiles t-block = 2*s-block + 1
+  auto decode = [&](int tile, int& b, int& m0, int& n0, int& half) {
+    half = 0;
     if (EPI == EPI_GRAM) {
-      int j = 0;
-      while (true) {
-        const int cnt = min(2 * j + 2, args.tiles_m);
-        if (q < cnt) break;
-        q -= cnt; ++j;
+      const int nfull = args.batch * args.gram_full;
+      if (tile < nfull) {
+        b = tile / args.gram_full;
+        int q = tile - b * args.gram_full;
+        int j = 0;
+        while (true) {
+          const int cnt = min(2 * j + 1, args.tiles_m);
+          if (q < cnt) break;
+          q -= cnt; ++j;
+        }
+        m0 = q * BM; n0 = j * BN;
+      } else {
+        const int h = tile - nfull;
+        b = h / args.gram_half;
+        const int j = h - b * args.gram_half;
+        m0 = (2 * j + 1) * BM; n0 = j * BN; half = 1;
       }
-      m0 = q * BM; n0 = j * BN;
-    } else if (args.n_fastest) {
+      return;
+    }
+    b = tile / args.tiles_per_batch;
+    const int q = tile - b * args.tiles_per_batch;
+    if (args.n_fastest) {
       n0 = (q % args.tiles_n) * BN;
       m0 = (q / args.tiles_n) * (BM * CTAS) + cta_rank * BM;
     } else {
       m0 = (q % args.tiles_m) * (BM * CTAS) + cta_rank * BM;
       n0 = (q / args.tiles_m) * BN;
     }
+  };
+  // k-th work unit of this CTA (pair).  EPI_GRAM deals the units out in snake order -- forward on even
+  // rounds, backward on odd ones -- so the cheaper half tiles at the end of the list even out the load.
+  auto unit_of_round = [&](int k) {
+    if (EPI == EPI_GRAM && (k & 1)) return (wstep - 1 - wid) + k * wstep;
+    return wid + k * wstep;
   };
 
   // work unit -> tile, K-stage range, slot in split_ws (-1: whole tile, normal epilogue)
@@ -308,10 +333,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
-      for (int u = wid; u < total_units && ok; u += wstep) {
-        int tile, ks0, ks1, slot, b, m0, n0;
+      for (int round = 0; ok; ++round) {
+        const int u = unit_of_round(round);
+        if (u >= total_units) break;
+        int tile, ks0, ks1, slot, b, m0, n0, half;
         decode_unit(u, tile, ks0, ks1, slot);
-        decode(tile, b, m0, n0);
+        decode(tile, b, m0, n0, half);
         const int row0 = b * args.batch_rows;
         for (int ks = ks0; ks < ks1; ++ks) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 1)) { ok = false; break; }
@@ -376,9 +403,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0; uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int u = wid; u < total_units && ok; u += wstep) {
-        int tile, ks0, ks1, slot;
+      for (int round = 0; ok; ++round) {
+        const int u = unit_of_round(round);
+        if (u >= total_units) break;
+        int tile, ks0, ks1, slot, tb, tm0, tn0, half;
         decode_unit(u, tile, ks0, ks1, slot);
+        decode(tile, tb, tm0, tn0, half);
+        // a half tile multiplies by the upper 128 rows of the B stage only (N = 128)
+        const uint32_t idesc = half ? args.idesc_half : args.idesc;
+        const uint32_t b_off = half ? 128u * 128u : 0u;
         int ks = ks0;
         // one accumulator per segment: the whole unit, or one sample for EPI_STORE_SCALED
         while (ks < ks1 && ok) {
@@ -398,10 +431,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
             for (int k16 = 0; k16 < BK / UMMA_K; ++k16) {
               if (CTAS == 1)
-                tc_mma(d, operand_desc<A_MN>(sa, k16), operand_desc<B_MN>(sb, k16), args.idesc,
+                tc_mma(d, operand_desc<A_MN>(sa, k16), operand_desc<B_MN>(sb + b_off, k16), idesc,
                        (first_stage && k16 == 0) ? 0u : 1u);
               else
-                tc_mma_pair(d, operand_desc<A_MN>(sa, k16), operand_desc<B_MN>(sb, k16), args.idesc,
+                tc_mma_pair(d, operand_desc<A_MN>(sa, k16), operand_desc<B_MN>(sb, k16), idesc,
                             (first_stage && k16 == 0) ? 0u : 1u);
             }
             // frees the stage (in both CTAs of a pair) once these MMAs have read it
@@ -437,10 +470,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int row = quarter * 32 + lane;
     int it = 0;
     bool ok = true;
-    for (int u = wid; u < total_units && ok; u += wstep) {
-      int tile, ks0, ks1, slot, b, m0, n0;
+    for (int round = 0; ok; ++round) {
+      const int u = unit_of_round(round);
+      if (u >= total_units) break;
+      int tile, ks0, ks1, slot, b, m0, n0, half;
       decode_unit(u, tile, ks0, ks1, slot);
-      decode(tile, b, m0, n0);
+      decode(tile, b, m0, n0, half);
       const int m = m0 + row;
       if (EPI == EPI_STORE_SCALED) {
         // eight warps: two per lane quarter, each owning 128 of the tile's 256 columns in registers
@@ -530,8 +565,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       } else {
         // weight 2 above the diagonal, 1 on it, 0 below it and outside the sample
         const int t = m0 + row;
+        const int ncols = half ? BN / 2 : BN;       // a half tile holds s-columns 128..255 in columns 0..127
+        const int s_base = n0 + (half ? BN / 2 : 0);
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = 0; c < ncols; c += 32) {
           uint32_t p[32], q[32];
           tc_ld32(tbase + c, p);
           tc_ld32(tbase + BN + c, q);
@@ -539,7 +576,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           if (t < args.T) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const int sidx = n0 + c + j;
+              const int sidx = s_base + c + j;
               const float w = (sidx >= args.T || sidx < t) ? 0.f : (sidx == t ? 1.f : 2.f);
               part = fmaf(w * __uint_as_float(p[j]), __uint_as_float(q[j]), part);
             }
@@ -558,7 +595,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         part = warp_sum(part);
         if (lane == 0) red[quarter] = part;
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (warp == 2 && lane == 0) args.partials[tile] = (red[0] + red[1]) + (red[2] + red[3]);
+        if (warp == 2 && lane == 0) {
+          int pslot = tile;  // EPI_SUMSQ: tiles are numbered sample by sample
+          if (EPI == EPI_GRAM) {
+            const int nfull = args.batch * args.gram_full, per = args.gram_full + args.gram_half;
+            pslot = tile < nfull ? b * per + (tile - b * args.gram_full)
+                                 : b * per + args.gram_full + (tile - nfull - b * args.gram_half);
+          }
+          args.partials[pslot] = (red[0] + red[1]) + (red[2] + red[3]);
+        }
         asm volatile("bar.sync 1, 128;" ::: "memory");
       }
     }
@@ -665,28 +710,34 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, ui
   return r == CUDA_SUCCESS;
 }
 
-uint32_t make_idesc(int dt, bool a_mn, bool b_mn, int ctas = 1) {
+uint32_t make_idesc(int dt, bool a_mn, bool b_mn, int ctas = 1, int n = BN) {
   uint32_t d = 0;
   d |= 1u << 4;                                   // accumulator format: F32
   d |= (dt == FDP_BF16 ? 1u : 0u) << 7;           // A format
   d |= (dt == FDP_BF16 ? 1u : 0u) << 10;          // B format
   d |= (a_mn ? 1u : 0u) << 15;                    // A major: 1 = MN-major
   d |= (b_mn ? 1u : 0u) << 16;                    // B major
-  d |= static_cast<uint32_t>(BN >> 3) << 17;      // N
+  d |= static_cast<uint32_t>(n >> 3) << 17;       // N
   d |= static_cast<uint32_t>((BM * ctas) >> 4) << 24;  // M (256 for a CTA pair)
   return d;
 }
 
+// SMs the persistent GEMM grids may occupy.  FDP_TC_RESERVE_SMS=n leaves n SMs free, e.g. for the
+// NCCL kernels of a data-parallel job: a persistent CTA holds a whole SM's shared memory, so a
+// collective launched beside it cannot start until SMs are free.
 int sm_count() {
   static std::mutex mu;
   static int cache[64];
   static bool have[64];
+  static const int reserve = [] { const char* e = getenv("FDP_TC_RESERVE_SMS"); return e ? atoi(e) : 0; }();
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return 148; }
   std::lock_guard<std::mutex> lk(mu);
   if (!have[dev]) {
     int n = 148;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) { cudaGetLastError(); n = 148; }
+    if (reserve > 0 && n - reserve >= 16) n -= reserve;
+    n &= ~1;  // CTA pairs
     cache[dev] = n; have[dev] = true;
   }
   return cache[dev];
@@ -816,6 +867,10 @@ int tc_norms(const void* G, const void* X, float* partials, int* dev_status, int
   args.M = T; args.N = T;
   args.tiles_m = ceil_div(T, BM); args.tiles_n = ceil_div(T, BN);
   args.tiles_per_batch = gram_tiles(T);
+  args.gram_half = 0;
+  for (int j = 0; j < args.tiles_n; ++j) args.gram_half += (2 * j + 1 < args.tiles_m) ? 1 : 0;
+  args.gram_full = args.tiles_per_batch - args.gram_half;
+  args.idesc_half = make_idesc(dt, false, false, 1, BN / 2);
   args.k_stages = ceil_div(n_out, BK); args.k_stages2 = ceil_div(n_in, BK);
   args.idesc = make_idesc(dt, false, false);
   return launch<false, false, EPI_GRAM>(a, b, a2, b2, args, s);
@@ -886,7 +941,7 @@ bool tc_dgrad_ok(int rows, int n_in, int n_out, int dt) {
 }
 
 int tc_dgrad(const void* G, const void* W, void* dX, int* dev_status, int rows, int n_in, int n_out,
-             int dt, int w_layout, cudaStream_t s) {
+             int dt, int out_dt, int w_layout, cudaStream_t s) {
   CUtensorMap mg, mw;
   const int ctas = ctas_per_tile();
   if (!make_map(&mg, G, rows, n_out, BK, BM, dt)) return FDP_ERR_LAUNCH;
@@ -899,7 +954,7 @@ int tc_dgrad(const void* G, const void* W, void* dX, int* dev_status, int rows, 
   // G is streamed once: CTAs that run together cover a band of rows times all of n_in, so the
   // band of G and the whole of W stay in L2 (walking along M first would re-read G per n-tile)
   args.n_fastest = 1;
-  args.out = dX; args.out_dt = dt; args.scale = 1.0f; args.nk = NoiseKey{};
+  args.out = dX; args.out_dt = out_dt; args.scale = 1.0f; args.nk = NoiseKey{};
   if (w_layout == FDP_OUT_IN) {  // W [n_out, n_in]: rows are K, N contiguous
     if (!make_map(&mw, W, n_out, n_in, 64, BK, dt)) return FDP_ERR_LAUNCH;
     args.idesc = make_idesc(dt, false, true, ctas);

@@ -25,6 +25,7 @@ class _DPLinearFunc(Function):
         w = weight if dt is None else weight.to(dt)
         ctx.save_for_backward(x, weight, bias, w if dt is not None else None)
         ctx.layer = layer
+        ctx.input_dtype = input.dtype
         output = x @ w.t()
         if bias is not None:
             output += bias if dt is None else bias.to(dt)
@@ -42,7 +43,7 @@ class _DPLinearFunc(Function):
 
         if ctx.needs_input_grad[0]:
             if runtime.input_grad_impl() == "native":
-                grad_input = ops.linear_input_grad(g3, w_for_dx, "out_in")
+                grad_input = ops.linear_input_grad(g3, w_for_dx, "out_in", out_dtype=ctx.input_dtype)
             else:
                 grad_input = g3 @ w_for_dx.to(g3.dtype)
             grad_input = grad_input.reshape(input.shape)

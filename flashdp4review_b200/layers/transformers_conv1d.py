@@ -42,6 +42,7 @@ class _DPConv1DFunc(Function):
         w = weight if dt is None else weight.to(dt)
         ctx.save_for_backward(bias, x, weight, w if dt is not None else None)
         ctx.layer = layer
+        ctx.input_dtype = input.dtype
         return x @ w + (bias if dt is None else bias.to(dt))
 
     @staticmethod
@@ -67,7 +68,7 @@ class _DPConv1DFunc(Function):
 
         if ctx.needs_input_grad[1]:
             if runtime.input_grad_impl() == "native":
-                grad_input = ops.linear_input_grad(g3, w_for_dx, "in_out")
+                grad_input = ops.linear_input_grad(g3, w_for_dx, "in_out", out_dtype=ctx.input_dtype)
             else:
                 grad_input = g3 @ w_for_dx.to(g3.dtype).t()
             grad_input = grad_input.reshape(input.shape)

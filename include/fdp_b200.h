@@ -136,11 +136,12 @@ int fdp_bias_grad_static(const void* G, void* db, float* norms_out, float* facto
 /* ---- input gradient ---------------------------------------------------------------------------
  * `grad_output @ weight` of flashdp/layers/linear.py:62-67 (w_layout FDP_OUT_IN, W [n_out,n_in]) and
  * `grad_output @ weight.t()` of flashdp/layers/transformers_conv1d.py:70-75 (FDP_IN_OUT, W [n_in,n_out]).
- *   G [rows,n_out], dX [rows,n_in], all in `dtype`.
+ *   G [rows,n_out] and W in `dtype`; dX [rows,n_in] in `out_dtype` (e.g. fp32 when the layer input was
+ *   fp32 under bf16 autocast, which saves the cast pass autograd would otherwise add).
  */
 size_t fdp_linear_dgrad_workspace_bytes(int rows, int n_in, int n_out, int dtype);
 int fdp_linear_dgrad(const void* G, const void* W, void* dX, int rows, int n_in, int n_out,
-                     int dtype, int w_layout, void* workspace, size_t workspace_bytes,
+                     int dtype, int out_dtype, int w_layout, void* workspace, size_t workspace_bytes,
                      fdp_stream_t stream);
 
 /* ---- LayerNorm ----------------------------------------------------------------------------------

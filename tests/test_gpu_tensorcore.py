@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 
 # (B, T, n_in, n_out): full tiles, partial tiles in M / N / K, T not a multiple of the tile
 SHAPES = [(2, 128, 256, 128), (3, 64, 136, 200), (2, 256, 512, 384), (1, 192, 768, 1024),
-          (4, 320, 264, 520), (2, 1024, 256, 256)]
+          (4, 320, 264, 520), (2, 1024, 256, 256), (2, 512, 256, 128), (1, 768, 128, 256), (5, 448, 384, 640)]
 
 
 @pytest.mark.parametrize("algo", ["direct", "gram", "auto"])
@@ -97,3 +97,41 @@ def test_no_bounded_wait_ran_out():
                               torch.cuda.current_stream().cuda_stream)
     assert st == 0
     assert lib.fdp_device_status(ws.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
+
+
+_VARIANT_CHILD = r"""
+import sys, torch, numpy as np
+sys.path.insert(0, %r)
+from oracle import dp_oracle as O
+from flashdp4review_b200.core import ops
+dev = torch.device("cuda:0")
+worst = 0.0
+for shape in [(2, 256, 512, 384), (3, 320, 264, 520), (2, 1024, 256, 256)]:
+    B, T, n_in, n_out = shape
+    X, G, W = O.make_linear_inputs(B, T, n_in, n_out, 1e-3, seed=sum(shape), dtype=torch.bfloat16)
+    G[0] *= 40.0
+    for layout in ("out_in", "in_out"):
+        dW, norms, _ = ops.dp_linear_weight_grad(X.to(dev), G.to(dev), 1e-2, 1.0, layout=layout, return_norms=True)
+        want, wn = O.linear_weight_grad(G, X, 1e-2, 1.0, layout=layout)
+        worst = max(worst, float(np.abs(dW.float().cpu().numpy() - want).max() / np.abs(want).max()),
+                    float((np.abs(norms.cpu().numpy() - wn) / wn).max()))
+    dX = ops.linear_input_grad(G.to(dev), W.to(dev), "out_in")
+    wdx = G.double().numpy() @ W.double().numpy()
+    worst = max(worst, float(np.abs(dX.float().cpu().numpy() - wdx).max() / np.abs(wdx).max()))
+torch.cuda.synchronize()
+print("WORST", worst)
+"""
+
+
+@pytest.mark.parametrize("env", [{"FDP_TC_CTAS": "1"}, {"FDP_WGRAD_PRESCALE": "1"},
+                                 {"FDP_TC_CTAS": "1", "FDP_WGRAD_PRESCALE": "1"}, {"FDP_TC_RESERVE_SMS": "16"}])
+def test_kernel_variants_selected_by_environment(env):
+    """Single-CTA tiles, the pre-scale path and a reduced grid are chosen once per process, so each
+    is exercised in a child process and checked against the oracle at the bf16 tolerance."""
+    import os, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, "-c", _VARIANT_CHILD % root], env={**os.environ, **env},
+                       capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    worst = float(r.stdout.strip().split("WORST")[-1])
+    assert worst < 1e-2, worst
