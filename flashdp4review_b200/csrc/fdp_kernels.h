@@ -35,7 +35,7 @@ void bias_finalize(const float* colsum_part, const float* factors, void* db, int
                    int row_chunks, int out_dt, float inv_div, NoiseKey nk, cudaStream_t s);
 
 // ---- LayerNorm -----------------------------------------------------------------------------------
-struct LnPlan { int tpr, cpt, rows_per_block, chunks; bool vec; };
+struct LnPlan { int tpr, cpt, cw, rows_per_block, chunks; bool vec; };
 LnPlan ln_plan(int T, int d, int dt);
 void ln_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
             int rows, int d, float eps, int dt, int pdt, cudaStream_t s);

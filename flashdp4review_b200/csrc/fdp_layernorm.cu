@@ -296,7 +296,7 @@ void ln_fwd(const void* x, const void* gamma, const void* beta, void* y, float* 
 }
 
 // ---------------------------------------------------------------------------------------------
-// backward.  A block of 256 threads is RG = 256/TPR row groups of TPR threads; a row group walks
+// backward.  A block of CW consumer threads (256 or 512) is RG = CW/TPR row groups of TPR threads; a row group walks
 // rows of one chunk of one sample, each thread owning NV vectors of VEC columns (vector j at
 // column (j*TPR + t)*VEC).  Per row: xhat, wdy = gamma*dy, the two row means, dx
 // (flashdp/core/layernorm_clip.py:95-103); per thread: running sums of dy*xhat and dy over the
@@ -306,13 +306,13 @@ void ln_fwd(const void* x, const void* gamma, const void* beta, void* y, float* 
 // STAGED: a ninth warp streams the rows of x and dy into a shared-memory ring with bulk async
 // copies (one stage = the RG rows the row groups work on at once), so several stages are in flight
 // per SM whatever the register-limited occupancy; the row groups read their row from the ring.
-template <typename Tin, int VEC, int NV, int TPR, bool STAGED>
-__global__ void __launch_bounds__(STAGED ? 288 : 256) ln_bwd_kernel(
+template <typename Tin, int VEC, int NV, int TPR, bool STAGED, int CW>
+__global__ void __launch_bounds__(STAGED ? CW + 32 : CW) ln_bwd_kernel(
     const Tin* __restrict__ dy, const Tin* __restrict__ x, const void* __restrict__ gamma,
     const float* __restrict__ mean, const float* __restrict__ rstd, Tin* __restrict__ dx,
     float* __restrict__ dg_part, float* __restrict__ db_part, int T, int d, int pdt,
     int rows_per_block, int chunks, int n_stages) {
-  constexpr int RG = 256 / TPR;
+  constexpr int RG = CW / TPR;
   constexpr int NWG = TPR / 32;  // warps per row group
   // dynamic shared memory: the ring (STAGED), reused at the end as [RG][TPR*NV*VEC] floats for the
   // cross-group sum
@@ -323,7 +323,7 @@ __global__ void __launch_bounds__(STAGED ? 288 : 256) ln_bwd_kernel(
   __shared__ int abort_flag_s;
   __shared__ float s_mean[LN_MAX_ROWS_PER_BLOCK], s_rstd[LN_MAX_ROWS_PER_BLOCK];  // this chunk's row statistics
   volatile int* abort_flag = &abort_flag_s;
-  const int rg = (threadIdx.x & 255) / TPR, t = threadIdx.x % TPR;
+  const int rg = (threadIdx.x % CW) / TPR, t = threadIdx.x % TPR;
   const int lane = threadIdx.x & 31, wig = (threadIdx.x % TPR) >> 5;
   const int b = blockIdx.y, chunk = blockIdx.x;
   const int r0 = chunk * rows_per_block, r1 = min(T, r0 + rows_per_block);
@@ -332,7 +332,7 @@ __global__ void __launch_bounds__(STAGED ? 288 : 256) ln_bwd_kernel(
   const uint32_t stage_bytes = 2 * RG * row_bytes;
 
   if (STAGED && threadIdx.x == 0) {
-    for (int s = 0; s < n_stages; ++s) { mbar_init(smem_u32(&bars[s]), 1); mbar_init(smem_u32(&bars[LN_MAX_STAGES + s]), 8); }
+    for (int s = 0; s < n_stages; ++s) { mbar_init(smem_u32(&bars[s]), 1); mbar_init(smem_u32(&bars[LN_MAX_STAGES + s]), CW / 32); }
     abort_flag_s = 0;
     mbar_fence_init();
   }
@@ -354,9 +354,9 @@ __global__ void __launch_bounds__(STAGED ? 288 : 256) ln_bwd_kernel(
     }
   const float inv_d = 1.0f / d;
 
-  if (STAGED && threadIdx.x >= 256) {
+  if (STAGED && threadIdx.x >= CW) {
     // ---- producer warp ----
-    if (threadIdx.x == 256) {
+    if (threadIdx.x == CW) {
       int s = 0; uint32_t ph = 0;
       for (int it = 0; it < n_iter; ++it) {
         if (!mbar_wait(smem_u32(&bars[LN_MAX_STAGES + s]), ph ^ 1u, abort_flag, nullptr, 0)) break;
@@ -466,7 +466,7 @@ __global__ void __launch_bounds__(STAGED ? 288 : 256) ln_bwd_kernel(
 #pragma unroll
   for (int which = 0; which < 2; ++which) {
     __syncthreads();
-    if (threadIdx.x < 256) {
+    if (threadIdx.x < CW) {
 #pragma unroll
       for (int j = 0; j < NV; ++j)
 #pragma unroll
@@ -475,8 +475,8 @@ __global__ void __launch_bounds__(STAGED ? 288 : 256) ln_bwd_kernel(
     }
     __syncthreads();
     float* dst = outp[which] + (static_cast<size_t>(b) * chunks + chunk) * d;
-    if (threadIdx.x < 256) {
-      for (int c = threadIdx.x; c < d; c += 256) {
+    if (threadIdx.x < CW) {
+      for (int c = threadIdx.x; c < d; c += CW) {
         float tot = 0.f;
 #pragma unroll
         for (int g = 0; g < RG; ++g) tot += sm[g * CPG + c];
@@ -491,9 +491,11 @@ LnPlan ln_plan(int T, int d, int dt) {
   const int V = 16 / static_cast<int>(dtype_size(dt));
   pl.vec = (d % V == 0);
   const int vec = pl.vec ? V : 1;
-  // columns per thread: 32 (16-bit) or 16 (fp32 up to d = 4096, so a ring stage stays 32 KiB)
+  // Vector path up to d = 4096: 16 columns per thread and 512 consumer threads (16 warps hide the
+  // latency of the row arithmetic; about 100 registers each).  Otherwise 32 columns, 256 threads.
   int nv_max = pl.vec ? (32 / V) : 32;
-  if (pl.vec && dt == FDP_F32 && d <= 4096) nv_max = 4;
+  pl.cw = 256;
+  if (pl.vec && d <= 4096) { nv_max = 16 / V; pl.cw = 512; }
   pl.cpt = nv_max * vec;
   pl.tpr = 32;
   while (pl.tpr < 256 && pl.tpr * pl.cpt < d) pl.tpr *= 2;
@@ -503,42 +505,42 @@ LnPlan ln_plan(int T, int d, int dt) {
   return pl;
 }
 
-template <typename Tin, int VEC, int NV, int TPRV, bool STAGED>
+template <typename Tin, int VEC, int NV, int TPRV, bool STAGED, int CW>
 static bool ln_bwd_launch_one(const void* dy, const void* x, const void* gamma, const float* mean,
                               const float* rstd, void* dx, float* dg_part, float* db_part, int B, int T,
                               int d, int pdt, const LnPlan& pl, int n_stages, cudaStream_t s) {
   dim3 grid(pl.chunks, B);
-  constexpr int RG = 256 / TPRV;
-  const size_t reduce_bytes = static_cast<size_t>(256) * NV * VEC * sizeof(float);
+  constexpr int RG = CW / TPRV;
+  const size_t reduce_bytes = static_cast<size_t>(CW) * NV * VEC * sizeof(float);
   const size_t stage_bytes = static_cast<size_t>(2) * RG * d * sizeof(Tin);
   size_t smem = reduce_bytes;
   if (STAGED && n_stages * stage_bytes > smem) smem = n_stages * stage_bytes;
   static bool done[64];
   static std::mutex mu;
-  if (smem > 48 * 1024 && !smem_opt_in(done, mu, ln_bwd_kernel<Tin, VEC, NV, TPRV, STAGED>, LN_SMEM_BUDGET)) return false;
-  ln_bwd_kernel<Tin, VEC, NV, TPRV, STAGED><<<grid, STAGED ? 288 : 256, smem, s>>>(
+  if (smem > 48 * 1024 && !smem_opt_in(done, mu, ln_bwd_kernel<Tin, VEC, NV, TPRV, STAGED, CW>, LN_SMEM_BUDGET)) return false;
+  ln_bwd_kernel<Tin, VEC, NV, TPRV, STAGED, CW><<<grid, STAGED ? CW + 32 : CW, smem, s>>>(
       (const Tin*)dy, (const Tin*)x, gamma, mean, rstd, (Tin*)dx, dg_part, db_part, T, d, pdt,
       pl.rows_per_block, pl.chunks, n_stages);
   note_launch();
   return true;
 }
 
-template <typename Tin, int VEC, int NV>
+template <typename Tin, int VEC, int NV, int CW>
 static void ln_bwd_launch(const void* dy, const void* x, const void* gamma, const float* mean,
                           const float* rstd, void* dx, float* dg_part, float* db_part, int B, int T,
                           int d, int pdt, const LnPlan& pl, cudaStream_t s) {
-  // ring of up to 3 stages (two blocks then share an SM); needs 16-byte rows, i.e. the vector path
-  const size_t stage_bytes = static_cast<size_t>(2) * (256 / pl.tpr) * d * sizeof(Tin);
+  // ring of up to 3 stages of at most 96 KiB in total; needs 16-byte rows, i.e. the vector path
+  const size_t stage_bytes = static_cast<size_t>(2) * (CW / pl.tpr) * d * sizeof(Tin);
   int n_stages = static_cast<int>((96 * 1024) / stage_bytes);
   if (n_stages > 3) n_stages = 3;
-  const int n_iter = ceil_div(pl.rows_per_block, 256 / pl.tpr);
+  const int n_iter = ceil_div(pl.rows_per_block, CW / pl.tpr);
   if (n_stages > n_iter) n_stages = n_iter;
   const bool staged = VEC > 1 && n_stages >= 2;
-#define FDP_LN_CASE(TPRV)                                                                                    \
-  if (staged && ln_bwd_launch_one<Tin, VEC, NV, TPRV, (VEC > 1)>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, \
-                                                                 T, d, pdt, pl, n_stages, s))                  \
-    return;                                                                                                  \
-  ln_bwd_launch_one<Tin, VEC, NV, TPRV, false>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, 0, s)
+#define FDP_LN_CASE(TPRV)                                                                                      \
+  if (staged && ln_bwd_launch_one<Tin, VEC, NV, TPRV, (VEC > 1), CW>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, \
+                                                                     B, T, d, pdt, pl, n_stages, s))                 \
+    return;                                                                                                    \
+  ln_bwd_launch_one<Tin, VEC, NV, TPRV, false, CW>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, 0, s)
   switch (pl.tpr) {
     case 32: FDP_LN_CASE(32); break;
     case 64: FDP_LN_CASE(64); break;
@@ -552,17 +554,21 @@ void ln_bwd(const void* dy, const void* x, const void* gamma, const float* mean,
             void* dx, float* dg_part, float* db_part, int B, int T, int d, int dt, int pdt,
             const LnPlan& pl, cudaStream_t s) {
   const bool vec = pl.vec && aligned16(dy) && aligned16(x) && (dx == nullptr || aligned16(dx));
+#define FDP_LN_ARGS dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s
   if (dt == FDP_F32) {
-    if (vec && pl.cpt == 16) ln_bwd_launch<float, 4, 4>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s);
-    else if (vec) ln_bwd_launch<float, 4, 8>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s);
-    else ln_bwd_launch<float, 1, 32>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s);
+    if (vec && pl.cw == 512) ln_bwd_launch<float, 4, 4, 512>(FDP_LN_ARGS);
+    else if (vec) ln_bwd_launch<float, 4, 8, 256>(FDP_LN_ARGS);
+    else ln_bwd_launch<float, 1, 32, 256>(FDP_LN_ARGS);
   } else if (dt == FDP_BF16) {
-    if (vec) ln_bwd_launch<__nv_bfloat16, 8, 4>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s);
-    else ln_bwd_launch<__nv_bfloat16, 1, 32>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s);
+    if (vec && pl.cw == 512) ln_bwd_launch<__nv_bfloat16, 8, 2, 512>(FDP_LN_ARGS);
+    else if (vec) ln_bwd_launch<__nv_bfloat16, 8, 4, 256>(FDP_LN_ARGS);
+    else ln_bwd_launch<__nv_bfloat16, 1, 32, 256>(FDP_LN_ARGS);
   } else {
-    if (vec) ln_bwd_launch<__half, 8, 4>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s);
-    else ln_bwd_launch<__half, 1, 32>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, pdt, pl, s);
+    if (vec && pl.cw == 512) ln_bwd_launch<__half, 8, 2, 512>(FDP_LN_ARGS);
+    else if (vec) ln_bwd_launch<__half, 8, 4, 256>(FDP_LN_ARGS);
+    else ln_bwd_launch<__half, 1, 32, 256>(FDP_LN_ARGS);
   }
+#undef FDP_LN_ARGS
 }
 
 // ---------------------------------------------------------------------------------------------

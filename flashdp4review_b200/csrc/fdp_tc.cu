@@ -56,9 +56,13 @@ struct TcArgs {
   int prefetch_dist;
   // EPI_GRAM: per sample `gram_full` tiles need all 256 s-columns and `gram_half` tiles (the t-block is
   // the lower half of the s-block) only columns 128..255, done with an N = 128 MMA (idesc_half).
-  // Tiles are numbered full tiles of all samples first, then the half tiles.
+  // Tiles are numbered sample by sample: the sample's full tiles, then its half tiles.  A work unit is
+  // one full tile or two half tiles, so all units cost the same and round-robin dealing is balanced.
   int gram_full, gram_half;
   uint32_t idesc_half;
+  // store GEMMs: tiles are walked in groups of m_group tile rows (0 = plain order), so that the CTAs
+  // running together cover a squarer patch of the output and re-read less of the operands
+  int m_group;
 };
 
 // ---- PTX wrappers (mbarrier helpers live in fdp_async.cuh) --------------------------------------------
@@ -239,7 +243,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_tiles = args.batch * args.tiles_per_batch;
   const int kst_total = args.k_stages + (EPI == EPI_GRAM ? args.k_stages2 : 0);
-  const int total_units = args.units_full + (total_tiles - args.units_full) * args.split;
+  const int total_units = (EPI == EPI_GRAM)
+      ? args.batch * (args.gram_full + (args.gram_half + 1) / 2)
+      : args.units_full + (total_tiles - args.units_full) * args.split;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NST; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -271,15 +277,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int wid = blockIdx.x / CTAS, wstep = gridDim.x / CTAS;
   const uint32_t tmem_base = *tmem_slot;
 
-  // tile -> (batch, m0, n0, half).  EPI_GRAM: tiles [0, batch*gram_full) are the full (t-block, s-block)
-  // pairs with t-block <= 2*s-block, the rest are the half tiles t-block = 2*s-block + 1
+  // tile -> (batch, m0, n0, half).  EPI_GRAM: per sample the full (t-block, s-block) pairs with
+  // t-block <= 2*s-block, then the half tiles t-block = 2*s-block + 1
   auto decode = [&](int tile, int& b, int& m0, int& n0, int& half) {
     half = 0;
+    b = tile / args.tiles_per_batch;
+    int q = tile - b * args.tiles_per_batch;
     if (EPI == EPI_GRAM) {
-      const int nfull = args.batch * args.gram_full;
-      if (tile < nfull) {
-        b = tile / args.gram_full;
-        int q = tile - b * args.gram_full;
+      if (q < args.gram_full) {
         int j = 0;
         while (true) {
           const int cnt = min(2 * j + 1, args.tiles_m);
@@ -288,28 +293,33 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
         m0 = q * BM; n0 = j * BN;
       } else {
-        const int h = tile - nfull;
-        b = h / args.gram_half;
-        const int j = h - b * args.gram_half;
+        const int j = q - args.gram_full;
         m0 = (2 * j + 1) * BM; n0 = j * BN; half = 1;
       }
       return;
     }
-    b = tile / args.tiles_per_batch;
-    const int q = tile - b * args.tiles_per_batch;
+    int mi, ni;
     if (args.n_fastest) {
-      n0 = (q % args.tiles_n) * BN;
-      m0 = (q / args.tiles_n) * (BM * CTAS) + cta_rank * BM;
+      ni = q % args.tiles_n; mi = q / args.tiles_n;
+    } else if (args.m_group > 0) {
+      const int per_group = args.m_group * args.tiles_n;
+      const int g = q / per_group, r = q - g * per_group;
+      const int gm = min(args.m_group, args.tiles_m - g * args.m_group);
+      mi = g * args.m_group + r % gm; ni = r / gm;
     } else {
-      m0 = (q % args.tiles_m) * (BM * CTAS) + cta_rank * BM;
-      n0 = (q / args.tiles_m) * BN;
+      mi = q % args.tiles_m; ni = q / args.tiles_m;
     }
+    m0 = mi * (BM * CTAS) + cta_rank * BM;
+    n0 = ni * BN;
   };
-  // k-th work unit of this CTA (pair).  EPI_GRAM deals the units out in snake order -- forward on even
-  // rounds, backward on odd ones -- so the cheaper half tiles at the end of the list even out the load.
-  auto unit_of_round = [&](int k) {
-    if (EPI == EPI_GRAM && (k & 1)) return (wstep - 1 - wid) + k * wstep;
-    return wid + k * wstep;
+  // EPI_GRAM: unit u -> its sub-tile `sub` (of nsub) in the sample-by-sample tile numbering
+  const int gram_ups = args.gram_full + (args.gram_half + 1) / 2;   // units per sample
+  auto gram_unit = [&](int u, int sub, int& nsub, int& tile) {
+    const int b = u / gram_ups, lu = u - b * gram_ups;
+    if (lu < args.gram_full) { nsub = 1; tile = b * args.tiles_per_batch + lu; return; }
+    const int h0 = 2 * (lu - args.gram_full);
+    nsub = min(2, args.gram_half - h0);
+    tile = b * args.tiles_per_batch + args.gram_full + h0 + sub;
   };
 
   // work unit -> tile, K-stage range, slot in split_ws (-1: whole tile, normal epilogue)
@@ -333,11 +343,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
-      for (int round = 0; ok; ++round) {
-        const int u = unit_of_round(round);
+      int nsub = 1;
+      for (int round = 0, sub = 0; ok; (++sub >= nsub) ? (void)(sub = 0, ++round) : (void)0) {
+        const int u = wid + round * wstep;
         if (u >= total_units) break;
         int tile, ks0, ks1, slot, b, m0, n0, half;
-        decode_unit(u, tile, ks0, ks1, slot);
+        if (EPI == EPI_GRAM) { gram_unit(u, sub, nsub, tile); ks0 = 0; ks1 = kst_total; slot = -1; }
+        else decode_unit(u, tile, ks0, ks1, slot);
         decode(tile, b, m0, n0, half);
         const int row0 = b * args.batch_rows;
         for (int ks = ks0; ks < ks1; ++ks) {
@@ -403,11 +415,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0; uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int round = 0; ok; ++round) {
-        const int u = unit_of_round(round);
+      int nsub = 1;
+      for (int round = 0, sub = 0; ok; (++sub >= nsub) ? (void)(sub = 0, ++round) : (void)0) {
+        const int u = wid + round * wstep;
         if (u >= total_units) break;
         int tile, ks0, ks1, slot, tb, tm0, tn0, half;
-        decode_unit(u, tile, ks0, ks1, slot);
+        if (EPI == EPI_GRAM) { gram_unit(u, sub, nsub, tile); ks0 = 0; ks1 = kst_total; slot = -1; }
+        else decode_unit(u, tile, ks0, ks1, slot);
         decode(tile, tb, tm0, tn0, half);
         // a half tile multiplies by the upper 128 rows of the B stage only (N = 128)
         const uint32_t idesc = half ? args.idesc_half : args.idesc;
@@ -470,11 +484,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int row = quarter * 32 + lane;
     int it = 0;
     bool ok = true;
-    for (int round = 0; ok; ++round) {
-      const int u = unit_of_round(round);
+    int nsub = 1;
+    for (int round = 0, sub = 0; ok; (++sub >= nsub) ? (void)(sub = 0, ++round) : (void)0) {
+      const int u = wid + round * wstep;
       if (u >= total_units) break;
       int tile, ks0, ks1, slot, b, m0, n0, half;
-      decode_unit(u, tile, ks0, ks1, slot);
+      if (EPI == EPI_GRAM) { gram_unit(u, sub, nsub, tile); ks0 = 0; ks1 = kst_total; slot = -1; }
+      else decode_unit(u, tile, ks0, ks1, slot);
       decode(tile, b, m0, n0, half);
       const int m = m0 + row;
       if (EPI == EPI_STORE_SCALED) {
@@ -596,12 +612,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (lane == 0) red[quarter] = part;
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp == 2 && lane == 0) {
-          int pslot = tile;  // EPI_SUMSQ: tiles are numbered sample by sample
-          if (EPI == EPI_GRAM) {
-            const int nfull = args.batch * args.gram_full, per = args.gram_full + args.gram_half;
-            pslot = tile < nfull ? b * per + (tile - b * args.gram_full)
-                                 : b * per + args.gram_full + (tile - nfull - b * args.gram_half);
-          }
+          const int pslot = tile;  // tiles are numbered sample by sample
           args.partials[pslot] = (red[0] + red[1]) + (red[2] + red[3]);
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -626,12 +637,23 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 // ---- split-K fix-up: out = scale * (part_0 + part_1 + ...) + noise for the tiles of the tail wave ------
 __global__ void __launch_bounds__(256) splitk_fixup_kernel(const float* __restrict__ ws, int first_tile, int split,
                                                            int tile_rows, int M, int N, int tiles_m, int tiles_n, int n_fastest,
+                                                           int m_group,
                                                            void* __restrict__ out, int out_dt, long long ld_out,
                                                            float scale, NoiseKey nk) {
   const int t = blockIdx.y;  // index among the split tiles
   const int q = first_tile + t;
-  const int m0 = (n_fastest ? q / tiles_n : q % tiles_m) * tile_rows;
-  const int n0 = (n_fastest ? q % tiles_n : q / tiles_m) * BN;
+  int mi, ni;  // the tile order of tc_gemm_kernel's decode
+  if (n_fastest) {
+    ni = q % tiles_n; mi = q / tiles_n;
+  } else if (m_group > 0) {
+    const int per_group = m_group * tiles_n;
+    const int g = q / per_group, r = q - g * per_group;
+    const int gm = min(m_group, tiles_m - g * m_group);
+    mi = g * m_group + r % gm; ni = r / gm;
+  } else {
+    mi = q % tiles_m; ni = q / tiles_m;
+  }
+  const int m0 = mi * tile_rows, n0 = ni * BN;
   const int e = (blockIdx.x * 256 + threadIdx.x) * 4;  // element of the tile, 4 adjacent columns
   const int row = e / BN, col = e % BN;
   const int m = m0 + row, n = n0 + col;
@@ -752,7 +774,8 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, co
   TcArgs la = args;
   const int total = la.batch * la.tiles_per_batch;
   if (la.split <= 1) { la.split = 1; la.units_full = total; }
-  const int units = la.units_full + (total - la.units_full) * la.split;
+  int units = la.units_full + (total - la.units_full) * la.split;
+  if (EPI == EPI_GRAM) units = la.batch * (la.gram_full + (la.gram_half + 1) / 2);
   const int workers = sm_count() / CTAS;   // CTAs, or CTA pairs
   const int grid = CTAS * (units < workers ? units : workers);
   if (CTAS == 1) {
@@ -909,6 +932,8 @@ int tc_clipped_wgrad(const void* Gs, const void* X, const float* factors, float*
   args.M = oi ? n_out : n_in; args.N = oi ? n_in : n_out; args.ld_out = args.N;
   args.tiles_m = ceil_div(args.M, BM * ctas); args.tiles_n = ceil_div(args.N, BN);
   args.tiles_per_batch = args.tiles_m * args.tiles_n;
+  static const int m_group = [] { const char* e = getenv("FDP_TC_MGROUP"); return e ? atoi(e) : 8; }();
+  args.m_group = m_group;
   // tail wave: split K so the SMs left idle by the tile count get work; parts are parked in the
   // workspace and summed in fixed order by the fix-up kernel (deterministic, no waits)
   const int total = args.tiles_per_batch, workers = sm_count() / ctas;
@@ -930,8 +955,8 @@ int tc_clipped_wgrad(const void* Gs, const void* X, const float* factors, float*
   if (st != FDP_OK || split <= 1) return st;
   dim3 grid(BM * ctas * BN / (256 * 4), n_split_tiles);
   splitk_fixup_kernel<<<grid, 256, 0, s>>>(args.split_ws, args.units_full, split, BM * ctas, args.M, args.N,
-                                           args.tiles_m, args.tiles_n, args.n_fastest, dW, out_dt, args.ld_out,
-                                           inv_div, nk);
+                                           args.tiles_m, args.tiles_n, args.n_fastest, args.m_group, dW, out_dt,
+                                           args.ld_out, inv_div, nk);
   note_launch();
   return FDP_OK;
 }

@@ -71,7 +71,11 @@ class DPGradReducer:
         bucket = [p for p in self.buckets[i] if p.grad is not None]
         if not bucket:
             return
-        flat = torch.cat([(p.grad * self._scale(p, self.world)).reshape(-1) for p in bucket])
+        parts = []
+        for p in bucket:
+            sc = self._scale(p, self.world)
+            parts.append((p.grad if sc == 1.0 else p.grad * sc).reshape(-1))
+        flat = torch.cat(parts)
         work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
         self._inflight[i] = (work, flat, bucket)
 
