@@ -50,6 +50,8 @@ SIGNATURES = {
     "fdp_linear_dgrad_workspace_bytes": (c_size_t, [c_int] * 4),
     "fdp_linear_dgrad": (c_int, [c_void_p, c_void_p, c_void_p] + [c_int] * 6 +
                          [c_void_p, c_size_t, c_void_p]),
+    "fdp_linear_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p] + [c_int] * 6 +
+                       [c_void_p, c_size_t, c_void_p]),
     "fdp_layernorm_fwd": (c_int, [c_void_p] * 6 + [c_int, c_int, c_float, c_int, c_int, c_void_p]),
     "fdp_layernorm_bwd_workspace_bytes": (c_size_t, [c_int] * 3),
     "fdp_layernorm_bwd": (c_int, [c_void_p] * 10 + [c_int] * 5 +

@@ -187,6 +187,28 @@ def linear_input_grad(grad_output, weight, w_layout="out_in", out_dtype=None):
     return dX
 
 
+def linear_forward(input, weight, bias=None, w_layout="out_in", out_dtype=None):
+    """input @ weight.t() + bias (nn.Linear, weight [out,in]) or input @ weight + bias (Conv1D, weight
+    [in,out]) -- flashdp/layers/linear.py:41-46, transformers_conv1d.py:40-43."""
+    lib = _lib.load()
+    _require_cuda(input, weight, bias)
+    X = input.contiguous()
+    W = weight.to(X.dtype).contiguous()
+    b = None if bias is None else bias.to(X.dtype).contiguous()
+    n_in = X.shape[-1]
+    n_out = W.shape[0] if w_layout == "out_in" else W.shape[1]
+    rows = X.numel() // n_in
+    out_dtype = out_dtype or X.dtype
+    Y = torch.empty(X.shape[:-1] + (n_out,), dtype=out_dtype, device=X.device)
+    ws = _workspace(lib.fdp_linear_dgrad_workspace_bytes(rows, n_out, n_in, _dt(X.dtype)), X.device)
+    with torch.cuda.device(X.device):
+        st = lib.fdp_linear_fwd(_ptr(X), _ptr(W), _ptr(b), _ptr(Y), rows, n_in, n_out, _dt(X.dtype), _dt(out_dtype),
+                                _lib.FDP_OUT_IN if w_layout == "out_in" else _lib.FDP_IN_OUT,
+                                _ptr(ws), ws.numel(), _stream(X.device))
+    _lib.check(st, "fdp_linear_fwd")
+    return Y
+
+
 # ------------------------------------------------------------------------------------------------
 # LayerNorm
 # ------------------------------------------------------------------------------------------------

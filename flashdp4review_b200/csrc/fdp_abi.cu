@@ -271,6 +271,30 @@ int fdp_linear_dgrad(const void* G, const void* W, void* dX, int rows, int n_in,
   return FDP_OK;
 }
 
+// ---- forward --------------------------------------------------------------------------------------------
+int fdp_linear_fwd(const void* X, const void* W, const void* bias, void* Y, int rows, int n_in, int n_out,
+                   int dtype, int out_dtype, int w_layout, void* workspace, size_t workspace_bytes,
+                   fdp_stream_t stream) {
+  if (X == nullptr || W == nullptr || Y == nullptr) return FDP_ERR_ARG;
+  if (rows <= 0 || n_in <= 0 || n_out <= 0) return FDP_ERR_ARG;
+  if (w_layout != FDP_OUT_IN && w_layout != FDP_IN_OUT) return FDP_ERR_ARG;
+  if (!valid_dtype(dtype) || !valid_dtype(out_dtype)) return FDP_ERR_DTYPE;
+  int st = current_device_ok();
+  if (st != FDP_OK) return st;
+  if (workspace == nullptr || workspace_bytes < 256 || !aligned16(workspace)) return FDP_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  int* status = static_cast<int*>(workspace);
+  FDP_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), s));
+  // same shape rules as the input gradient with the roles of n_in and n_out exchanged
+  if (tc_dgrad_ok(rows, n_out, n_in, dtype) && aligned16(X) && aligned16(W) && aligned16(Y)) {
+    if ((st = tc_fwd(X, W, bias, Y, status, rows, n_in, n_out, dtype, out_dtype, w_layout, s)) != FDP_OK) return st;
+  } else {
+    simt_fwd(X, W, bias, Y, rows, n_in, n_out, dtype, out_dtype, w_layout, s);
+  }
+  FDP_LAUNCH_OK();
+  return FDP_OK;
+}
+
 // ---- LayerNorm ------------------------------------------------------------------------------------------
 int fdp_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean,
                       float* rstd, int rows, int d, float eps, int dtype, int param_dtype,

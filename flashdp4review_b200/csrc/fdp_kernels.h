@@ -26,6 +26,10 @@ void simt_clipped_wgrad(const void* G, const void* X, const float* factors, void
 void simt_dgrad(const void* G, const void* W, void* dX, int rows, int n_in, int n_out, int dt,
                 int out_dt, int w_layout, cudaStream_t s);
 
+// Y[rows,n_out] = X[rows,n_in] * W^T (+ bias); W [n_out,n_in] if w_layout==FDP_OUT_IN else [n_in,n_out]
+void simt_fwd(const void* X, const void* W, const void* bias, void* Y, int rows, int n_in, int n_out, int dt,
+              int out_dt, int w_layout, cudaStream_t s);
+
 // ---- bias gradient (HBM-bound; G read once) ----------------------------------------------------
 struct GstatsPlan { int vec, cols_per_block, col_chunks, rows_per_chunk, row_chunks; };
 GstatsPlan gstats_plan(int T, int n_out, int dt);
@@ -71,6 +75,8 @@ int tc_clipped_wgrad(const void* Gs, const void* X, const float* factors, float*
                      int* dev_status, int B, int T, int n_in, int n_out, int dt, int out_dt, int layout,
                      float inv_div, NoiseKey nk, cudaStream_t s);
 bool tc_dgrad_ok(int rows, int n_in, int n_out, int dt);
+int tc_fwd(const void* X, const void* W, const void* bias, void* Y, int* dev_status, int rows, int n_in,
+           int n_out, int dt, int out_dt, int w_layout, cudaStream_t s);
 int tc_dgrad(const void* G, const void* W, void* dX, int* dev_status, int rows, int n_in, int n_out,
              int dt, int out_dt, int w_layout, cudaStream_t s);
 

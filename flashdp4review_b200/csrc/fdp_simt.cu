@@ -205,6 +205,42 @@ void simt_dgrad(const void* G, const void* W, void* dX, int rows, int n_in, int 
   note_launch();
 }
 
+// ---- forward: Y[r,o] = sum_i X[r,i] W(i,o) + bias[o] ---------------------------------------------
+template <typename Tin>
+__global__ void __launch_bounds__(256) simt_fwd_kernel(const Tin* __restrict__ X, const Tin* __restrict__ W,
+                                                       const Tin* __restrict__ bias, void* __restrict__ Y,
+                                                       int out_dt, int rows, int n_in, int n_out, int w_layout) {
+  float acc[4][4] = {};
+  const int m0 = blockIdx.y * TM, n0 = blockIdx.x * TN;
+  // A(k=i, m=r) = X[r*n_in + i];  B(k=i, n=o) = W[o*n_in + i] (OUT_IN) or W[i*n_out + o] (IN_OUT)
+  const long sBk = (w_layout == FDP_OUT_IN) ? 1 : n_out, sBn = (w_layout == FDP_OUT_IN) ? n_in : 1;
+  simt_tile<Tin, false>(X, 1, n_in, W, sBk, sBn, n_in, rows, n_out, m0, n0, nullptr, 1, acc);
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= rows) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < n_out)
+        store_as(Y, out_dt, static_cast<size_t>(m) * n_out + n, acc[i][j] + (bias ? to_f32<Tin>(bias[n]) : 0.f));
+    }
+  }
+}
+
+void simt_fwd(const void* X, const void* W, const void* bias, void* Y, int rows, int n_in, int n_out, int dt,
+              int out_dt, int w_layout, cudaStream_t s) {
+  dim3 grid(ceil_div(n_out, TN), ceil_div(rows, TM));
+  if (dt == FDP_F32)
+    simt_fwd_kernel<float><<<grid, 256, 0, s>>>((const float*)X, (const float*)W, (const float*)bias, Y, out_dt, rows, n_in, n_out, w_layout);
+  else if (dt == FDP_BF16)
+    simt_fwd_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)X, (const __nv_bfloat16*)W, (const __nv_bfloat16*)bias, Y, out_dt, rows, n_in, n_out, w_layout);
+  else
+    simt_fwd_kernel<__half><<<grid, 256, 0, s>>>((const __half*)X, (const __half*)W, (const __half*)bias, Y, out_dt, rows, n_in, n_out, w_layout);
+  note_launch();
+}
+
 // ---- bias gradient statistics: one read of G -> per-sample sum of squares + column sums ---------
 // Block = 32 column-threads x 8 row-threads.  A column-thread owns VEC adjacent columns (one
 // 16-byte load per row); the 8 row-threads stride over the rows of the chunk.  Partials are

@@ -60,6 +60,8 @@ struct TcArgs {
   // one full tile or two half tiles, so all units cost the same and round-robin dealing is balanced.
   int gram_full, gram_half;
   uint32_t idesc_half;
+  // store epilogue: optional bias[N] (same 16-bit type as the operands) added to every row
+  const void* bias; int bias_dt;
   // store GEMMs: tiles are walked in groups of m_group tile rows (0 = plain order), so that the CTAs
   // running together cover a squarer patch of the output and re-read less of the operands
   int m_group;
@@ -161,6 +163,11 @@ __device__ __forceinline__ uint64_t operand_desc(uint32_t stage_base, int k16) {
 __device__ __forceinline__ void store_chunk32(const TcArgs& args, float v[32], int m, int n) {
   if (m >= args.M || n >= args.N) return;
   const size_t idx0 = static_cast<size_t>(m) * args.ld_out + n;
+  if (args.bias != nullptr) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j)
+      if (n + j < args.N) v[j] += load_as(args.bias, args.bias_dt, n + j);
+  }
   if (args.nk.std != 0.f) {
     if ((idx0 & 3) == 0) {
 #pragma unroll
@@ -991,6 +998,34 @@ int tc_dgrad(const void* G, const void* W, void* dX, int* dev_status, int rows, 
   args.idesc = make_idesc(dt, false, false, ctas);
   return ctas == 2 ? launch<false, false, EPI_STORE, 2>(mg, mw, mg, mw, args, s)
                    : launch<false, false, EPI_STORE, 1>(mg, mw, mg, mw, args, s);
+}
+
+// forward: A = X [rows, n_in] K-major; B = W, K-major for [n_out, n_in] (Linear), MN-major for
+// [n_in, n_out] (Conv1D); bias added in the epilogue
+int tc_fwd(const void* X, const void* W, const void* bias, void* Y, int* dev_status, int rows, int n_in,
+           int n_out, int dt, int out_dt, int w_layout, cudaStream_t s) {
+  CUtensorMap mx, mw;
+  const int ctas = ctas_per_tile();
+  if (!make_map(&mx, X, rows, n_in, BK, BM, dt)) return FDP_ERR_LAUNCH;
+  TcArgs args{};
+  args.batch = 1; args.batch_rows = 0; args.status = dev_status;
+  args.M = rows; args.N = n_out; args.ld_out = n_out;
+  args.tiles_m = ceil_div(rows, BM * ctas); args.tiles_n = ceil_div(n_out, BN);
+  args.tiles_per_batch = args.tiles_m * args.tiles_n;
+  args.k_stages = ceil_div(n_in, BK);
+  args.n_fastest = 1;  // X is streamed once, W stays in L2
+  args.out = Y; args.out_dt = out_dt; args.scale = 1.0f; args.nk = NoiseKey{};
+  args.bias = bias; args.bias_dt = dt;
+  if (w_layout == FDP_OUT_IN) {  // W [n_out, n_in]: K contiguous
+    if (!make_map(&mw, W, n_out, n_in, BK, BN / ctas, dt)) return FDP_ERR_LAUNCH;
+    args.idesc = make_idesc(dt, false, false, ctas);
+    return ctas == 2 ? launch<false, false, EPI_STORE, 2>(mx, mw, mx, mw, args, s)
+                     : launch<false, false, EPI_STORE, 1>(mx, mw, mx, mw, args, s);
+  }
+  if (!make_map(&mw, W, n_in, n_out, 64, BK, dt)) return FDP_ERR_LAUNCH;  // W [n_in, n_out]: N contiguous
+  args.idesc = make_idesc(dt, false, true, ctas);
+  return ctas == 2 ? launch<false, true, EPI_STORE, 2>(mx, mw, mx, mw, args, s)
+                   : launch<false, true, EPI_STORE, 1>(mx, mw, mx, mw, args, s);
 }
 
 }  // namespace fdp

@@ -26,6 +26,8 @@ class _DPLinearFunc(Function):
         ctx.save_for_backward(x, weight, bias, w if dt is not None else None)
         ctx.layer = layer
         ctx.input_dtype = input.dtype
+        if runtime.input_grad_impl() == "native" and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16):
+            return ops.linear_forward(x, w, bias, "out_in")     # library GEMM, bias added in its epilogue
         output = x @ w.t()
         if bias is not None:
             output += bias if dt is None else bias.to(dt)

@@ -43,6 +43,8 @@ class _DPConv1DFunc(Function):
         ctx.save_for_backward(bias, x, weight, w if dt is not None else None)
         ctx.layer = layer
         ctx.input_dtype = input.dtype
+        if runtime.input_grad_impl() == "native" and x.is_cuda and x.dtype in (torch.bfloat16, torch.float16):
+            return ops.linear_forward(x, w, bias, "in_out")     # library GEMM, bias added in its epilogue
         return x @ w + (bias if dt is None else bias.to(dt))
 
     @staticmethod

@@ -55,6 +55,10 @@ def data_parallel():
 
 
 def set_input_grad_impl(name: str):
+    """Which GEMMs the DP layers use beside the DP kernels: "library" = cuBLAS through torch, as the
+    reference does (flashdp/layers/linear.py:43, :62-67); "native" = this package's own tcgen05 GEMMs
+    for the input gradient (any dtype) and, for bf16/fp16, the forward product with the bias added in
+    the epilogue."""
     if name not in ("library", "native"):
         raise ValueError("input_grad_impl must be 'library' or 'native'")
     _run.input_grad_impl = name

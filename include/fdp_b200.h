@@ -144,6 +144,16 @@ int fdp_linear_dgrad(const void* G, const void* W, void* dX, int rows, int n_in,
                      int dtype, int out_dtype, int w_layout, void* workspace, size_t workspace_bytes,
                      fdp_stream_t stream);
 
+/* ---- forward -----------------------------------------------------------------------------------
+ * `input @ weight.t() + bias` of flashdp/layers/linear.py:41-46 (w_layout FDP_OUT_IN, W [n_out,n_in]) and
+ * `input @ weight + bias` of flashdp/layers/transformers_conv1d.py:40-43 (FDP_IN_OUT, W [n_in,n_out]).
+ *   X [rows,n_in] and W in `dtype`; bias [n_out] in `dtype` or NULL; Y [rows,n_out] in `out_dtype`.
+ * The workspace is that of fdp_linear_dgrad (the status word).
+ */
+int fdp_linear_fwd(const void* X, const void* W, const void* bias, void* Y, int rows, int n_in, int n_out,
+                   int dtype, int out_dtype, int w_layout, void* workspace, size_t workspace_bytes,
+                   fdp_stream_t stream);
+
 /* ---- LayerNorm ----------------------------------------------------------------------------------
  * fdp_layernorm_fwd: layernorm_fwd_fused(input, weight, bias, eps) (flashdp/core/layernorm_clip.py:201-239):
  *   x,y [rows,d] in `dtype`; gamma,beta [d] in `param_dtype`; mean,rstd float[rows].

@@ -1,0 +1,26 @@
+"""Shape fuzzing of the weight-gradient entry point with hypothesis: arbitrary small shapes straddle
+the boundary between the generic kernels and the tensor-core kernels (row pitch multiple of 16 bytes,
+at least 128 features, T >= 64) and the boundaries of the 128x256x64 tiles."""
+import numpy as np
+import pytest
+import torch
+from hypothesis import given, settings, strategies as st, HealthCheck
+
+from oracle import dp_oracle as O
+from gpu_util import TOL, check_wgrad
+
+pytestmark = pytest.mark.gpu
+
+dims = st.sampled_from([8, 24, 64, 120, 128, 136, 192, 256, 264, 320, 384, 520])
+
+
+@settings(max_examples=30, deadline=None, suppress_health_check=list(HealthCheck), derandomize=True)
+@given(B=st.integers(1, 5), T=st.sampled_from([1, 7, 33, 64, 96, 128, 130, 192, 256, 320]), n_in=dims, n_out=dims,
+       dtype=st.sampled_from([torch.float32, torch.bfloat16, torch.float16]),
+       layout=st.sampled_from(["out_in", "in_out"]), C=st.sampled_from([1e-3, 0.05, 1.0, 1e6]),
+       clamp=st.sampled_from([0.25, 1.0]))
+def test_wgrad_fuzz(B, T, n_in, n_out, dtype, layout, C, clamp):
+    X, G, _ = O.make_linear_inputs(B, T, n_in, n_out, 2e-2, seed=B * 1000 + T + n_in + n_out, dtype=dtype)
+    if B > 1:
+        G[0] *= 25.0
+    check_wgrad(X, G, C, clamp, dtype, layout=layout)

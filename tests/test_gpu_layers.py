@@ -142,6 +142,38 @@ def test_autocast_bf16_gives_fp32_param_grads():
     assert rel_err(lin.weight.grad.cpu().numpy(), want) < 1e-2
 
 
+def test_native_gemms_bf16_layer_matches_oracle():
+    """With set_input_grad_impl("native") forward, input gradient and DP gradients all come from the library."""
+    import flashdp4review_b200 as fdp
+    from flashdp4review_b200 import _lib
+    fdp.set_input_grad_impl("native")
+    try:
+        X, G, W = O.make_linear_inputs(4, 128, 256, 384, 1e-2, seed=33, dtype=torch.bfloat16)
+        for kind in ("linear", "conv1d"):
+            if kind == "linear":
+                layer = fdp.DPLinear(256, 384, C=0.1, noise_multiplier=0.0).to(dev()).to(torch.bfloat16)
+                with torch.no_grad():
+                    layer.weight.copy_(W)
+                    layer.bias.copy_(torch.linspace(-1, 1, 384))
+            else:
+                layer = fdp.DPConv1D(384, 256, C=0.1, noise_multiplier=0.0).to(dev()).to(torch.bfloat16)
+                with torch.no_grad():
+                    layer.weight.copy_(W.t())
+                    layer.bias.copy_(torch.linspace(-1, 1, 384))
+            x = X.to(dev()).requires_grad_(True)
+            n0 = _lib.load().fdp_launch_count()
+            y = layer(x)
+            y.backward(G.to(dev()))
+            assert _lib.load().fdp_launch_count() - n0 >= 8          # forward, dX, wgrad and bias kernels ran
+            bias = layer.bias.detach().double().cpu().numpy()
+            assert rel_err(y.detach().float().cpu().numpy(), X.double().numpy() @ W.double().numpy().T + bias) < 1e-2
+            assert rel_err(x.grad.float().cpu().numpy(), G.double().numpy() @ W.double().numpy()) < 1e-2
+            want, _ = O.linear_weight_grad(G, X, 0.1, 1.0, layout="out_in" if kind == "linear" else "in_out")
+            assert rel_err(layer.weight.grad.float().cpu().numpy(), want) < 1e-2
+    finally:
+        fdp.set_input_grad_impl("library")
+
+
 def test_wrapped_model_trains_one_step():
     import flashdp4review_b200 as fdp
     torch.manual_seed(0)
@@ -156,3 +188,38 @@ def test_wrapped_model_trains_one_step():
     loss.backward()
     assert all(p.grad is not None and torch.isfinite(p.grad).all() for p in model.parameters())
     opt.step()
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 1e-5), (torch.bfloat16, 1e-2)])
+def test_batch_sharding_equals_single_rank(dtype, tol):
+    """Data-parallel semantics without a collective: two 'ranks' each run the DP backward on half of
+    the batch (divisor and noise std of the global batch, each drawing its share of the noise); the
+    SUM of their gradients must equal the single-rank gradient of the whole batch -- the clipped
+    part to tolerance, the noise part exactly (same Philox stream, disjoint element groups)."""
+    from flashdp4review_b200.core import ops
+    B, T, n_in, n_out, world = 8, 128, 256, 384, 2
+    X, G, _ = O.make_linear_inputs(B, T, n_in, n_out, 1e-2, seed=17, dtype=dtype)
+    G[2] *= 20.0
+    Xd, Gd = X.to(dev()), G.to(dev())
+    std = ops.noise_std(1.5, B)
+    for std_ in (0.0, std):
+        full_ns = ops.NoiseSpec(std=std_, seed=5, param_id=3, step=9)
+        want = ops.dp_linear_weight_grad(Xd, Gd, 0.05, 1.0, noise=full_ns, out_dtype=torch.float32)
+        want_b = ops.dp_bias_grad(Gd, 0.05, 1.0, noise=full_ns, out_dtype=torch.float32)
+        acc = torch.zeros_like(want)
+        acc_b = torch.zeros_like(want_b)
+        half = B // world
+        for r in range(world):
+            ns = ops.NoiseSpec(std=std_, seed=5, param_id=3, step=9, rank=r, world=world)
+            sl = slice(r * half, (r + 1) * half)
+            acc += ops.dp_linear_weight_grad(Xd[sl], Gd[sl], 0.05, 1.0, batch_divisor=B, noise=ns,
+                                             out_dtype=torch.float32)
+            acc_b += ops.dp_bias_grad(Gd[sl], 0.05, 1.0, batch_divisor=B, noise=ns, out_dtype=torch.float32)
+        assert rel_err(acc.cpu().numpy(), want.cpu().numpy()) < tol
+        assert rel_err(acc_b.cpu().numpy(), want_b.cpu().numpy()) < tol
+    # noise alone: the shards' draws add up to the single-rank draw bit for bit
+    Z = torch.zeros_like(Gd)
+    one = ops.dp_linear_weight_grad(Xd, Z, 1.0, 1.0, noise=ops.NoiseSpec(std, 5, 3, 0, 9), out_dtype=torch.float32)
+    two = sum(ops.dp_linear_weight_grad(Xd[:4], Z[:4], 1.0, 1.0, batch_divisor=B, out_dtype=torch.float32,
+                                        noise=ops.NoiseSpec(std, 5, 3, 0, 9, r, 2)) for r in range(2))
+    assert torch.equal(one, two)

@@ -132,6 +132,21 @@ def test_input_grad(layout, dtype, ops):
     assert rel_err(dX.float().cpu().numpy(), want) < TOL[dtype]
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("layout", ["out_in", "in_out"])
+@pytest.mark.parametrize("shape", [(3, 37, 72, 40), (2, 128, 256, 384), (1, 200, 136, 328)])
+def test_forward_gemm(shape, layout, dtype, ops):
+    B, T, n_in, n_out = shape
+    X, _, W = O.make_linear_inputs(B, T, n_in, n_out, 1e-1, seed=21, dtype=dtype)
+    bias = (torch.linspace(-0.5, 0.5, n_out)).to(dtype)
+    Wd = W if layout == "out_in" else W.t().contiguous()
+    for b in (None, bias):
+        Y = ops.linear_forward(X.to(dev()), Wd.to(dev()), None if b is None else b.to(dev()), layout)
+        want = X.double().numpy() @ W.double().numpy().T + (0 if b is None else b.double().numpy())
+        assert Y.shape == (B, T, n_out)
+        assert rel_err(Y.float().cpu().numpy(), want) < TOL[dtype]
+
+
 # ---- noise ---------------------------------------------------------------------------------------
 def _noise_only(ops, n_out, n_in, std, seed, pid, step, rank=0, world=1, layout="out_in", dtype=torch.float32):
     X = torch.zeros(2, 4, n_in, device=dev(), dtype=dtype)
