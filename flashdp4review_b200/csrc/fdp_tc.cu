@@ -1,13 +1,17 @@
 // Tensor-core path for bf16 / fp16: one persistent, warp-specialised GEMM kernel template built
 // on TMA (cp.async.bulk.tensor, 128-byte swizzle) -> shared-memory ring -> tcgen05.mma with fp32
-// accumulators in TMEM -> tcgen05.ld epilogue.  Instances:
-//   wgrad   A,B MN-major   dW = scale * Gs^T X + noise        (K = B*T, Gs = c_b-scaled G)
-//   direct  A,B MN-major   per-sample ||G_b^T X_b||_F^2 tiles, squared in the epilogue, not stored
-//   gram    A,B K-major    sum_{t,s} (G_b G_b^T)_{ts} (X_b X_b^T)_{ts}, two accumulators in TMEM
-//   dgrad   A K-major, B MN- or K-major   dX = G W
-// Roles in a CTA of 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner,
-// warps 2-5 = epilogue (one TMEM lane quarter each).  Every mbarrier wait is bounded: when one
-// runs out the CTA records a code in the status word, drains and leaves.
+// accumulators in TMEM -> tcgen05.ld epilogue.  Instances (A major, B major, epilogue, CTAs per tile):
+//   wgrad   MN, MN, STORE_SCALED, 2   dW = scale * sum_b c_b G_b^T X_b + noise; every sample's K segment has
+//                                     its own TMEM accumulator, added times c_b into registers
+//           MN, MN, STORE, 2          same from a pre-scaled copy of G (T not a multiple of 64, or short T)
+//   direct  MN, MN, SUMSQ, 1          per-sample ||G_b^T X_b||_F^2: tile squared in the epilogue, never stored
+//   gram    K,  K,  GRAM, 1           sum_{t,s} (G_b G_b^T)_{ts} (X_b X_b^T)_{ts}, two accumulators in TMEM
+//   dgrad   K,  MN or K, STORE, 2     dX = G W
+//   forward K,  K or MN, STORE, 2     Y = X W^T + bias
+// Roles in a CTA: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2-5 (2-9 for
+// STORE_SCALED) = epilogue, each on the TMEM lane quarter warp % 4.  With two CTAs per tile the
+// even CTA of a 2-CTA cluster issues tcgen05.mma.cta_group::2 for both.  Every mbarrier wait is
+// bounded: when one runs out the CTA records a code in the status word, drains and leaves.
 // No TMA load here uses cluster multicast.
 #include <cuda.h>
 #include <cstdlib>
@@ -52,8 +56,6 @@ struct TcArgs {
   // EPI_STORE_SCALED: K is `segs` segments (samples) of `seg_stages` stages; factors[seg] scales each
   const float* factors;
   int segs, seg_stages;
-  // producer prefetches the A operand's boxes of stage ks + prefetch_dist into L2 (0 = off)
-  int prefetch_dist;
   // EPI_GRAM: per sample `gram_full` tiles need all 256 s-columns and `gram_half` tiles (the t-block is
   // the lower half of the s-block) only columns 128..255, done with an N = 128 MMA (idesc_half).
   // Tiles are numbered sample by sample: the sample's full tiles, then its half tiles.  A work unit is
@@ -107,11 +109,6 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t tmem_d, uint64_t desc_a, ui
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-// pull a box into L2 ahead of the shared-memory load that will use it
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int c0, int c1) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];"
-               ::"l"(reinterpret_cast<uint64_t>(map)), "r"(c0), "r"(c1) : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -366,12 +363,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const CUtensorMap* mb = second ? &tmB2 : &tmB;
           const int k0 = (second ? ks - args.k_stages : ks) * BK;
           const uint32_t sa = base + stage * STG, sb = sa + A_STAGE_BYTES;
-          if (A_MN && args.prefetch_dist > 0 && ks + args.prefetch_dist < ks1) {
-            // the A slab is shared by few CTAs, so most of its lines come from DRAM: request them early
-            const int kp = k0 + args.prefetch_dist * BK;
-#pragma unroll
-            for (int i = 0; i < BM / 64; ++i) tma_prefetch_2d(ma, m0 + 64 * i, row0 + kp);
-          }
           if (CTAS == 1) {
             mbar_expect_tx(full_bar(stage), STG);
             if (A_MN) {
@@ -932,8 +923,6 @@ int tc_clipped_wgrad(const void* Gs, const void* X, const float* factors, float*
   const int ctas = ctas_per_tile();
   args.idesc = make_idesc(dt, true, true, ctas);
   if (scaled) { args.factors = factors; args.segs = B; args.seg_stages = T / BK; }
-  static const int prefetch_dist = [] { const char* e = getenv("FDP_TC_PREFETCH"); return e ? atoi(e) : 0; }();
-  args.prefetch_dist = prefetch_dist;
   // [out,in]: A = G (M = n_out), B = X (N = n_in); [in,out]: operands swap roles, no transpose pass
   const bool oi = (layout == FDP_OUT_IN);
   args.M = oi ? n_out : n_in; args.N = oi ? n_in : n_out; args.ld_out = args.N;
