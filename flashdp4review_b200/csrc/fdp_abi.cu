@@ -235,10 +235,8 @@ int fdp_bias_grad(const void* G, void* db, float* norms_out, float* factors_out,
   // mean over the B*T rows (flashdp/core/linear_clip.py:122)
   const float inv_div = 1.0f / (static_cast<float>(div) * static_cast<float>(T));
   gstats(G, colsum_part, sq_part, B, T, n_out, in_dtype, pl, s);
-  clip_factors(sq_part, pl.row_chunks * pl.col_chunks, B, p->C, p->clamp_value, nullptr, factors,
-               norms_out, factors_out, s);
-  bias_finalize(colsum_part, factors, db, B, n_out, pl.row_chunks, out_dtype, inv_div,
-                make_noise_key(p, p->param_id), s);
+  bias_clip_finalize(colsum_part, sq_part, pl.row_chunks * pl.col_chunks, p->C, p->clamp_value, factors, norms_out,
+                     factors_out, db, B, n_out, pl.row_chunks, out_dtype, inv_div, make_noise_key(p, p->param_id), s);
   FDP_LAUNCH_OK();
   return FDP_OK;
 }
@@ -348,10 +346,10 @@ int fdp_layernorm_bwd(const void* dy, const void* x, const void* gamma, const fl
   const float inv_div = 1.0f / static_cast<float>(div);
   ln_bwd(dy, x, gamma, mean, rstd, dx, dg_part, db_part, B, T, d, dtype, param_dtype, pl, s);
   ln_psgrad_reduce(part, sumsq, B, pl.chunks, d, s);
-  // norms over d, one per sample and tensor
-  clip_factors_pair(sumsq, ln_sumsq_parts(d), B, p->C, p->clamp_value, factors, norms_gamma, norms_beta, s);
-  ln_psgrad_finalize(part, factors, dgamma, dbeta, B, pl.chunks, d, param_dtype, inv_div,
-                     make_noise_key(p, p->param_id), make_noise_key(p, p->param_id2), s);
+  // norms over d (one per sample and tensor), clip factors, mean over the batch, noise
+  ln_clip_finalize(part, sumsq, ln_sumsq_parts(d), p->C, p->clamp_value, factors, norms_gamma, norms_beta, dgamma,
+                   dbeta, B, pl.chunks, d, param_dtype, inv_div, make_noise_key(p, p->param_id),
+                   make_noise_key(p, p->param_id2), s);
   FDP_LAUNCH_OK();
   return FDP_OK;
 }

@@ -37,6 +37,10 @@ void gstats(const void* G, float* colsum_part, float* sq_part, int B, int T, int
             const GstatsPlan& pl, cudaStream_t s);
 void bias_finalize(const float* colsum_part, const float* factors, void* db, int B, int n_out,
                    int row_chunks, int out_dt, float inv_div, NoiseKey nk, cudaStream_t s);
+// clip factors from sq_part[B, nparts] and the finalisation in one launch (two for very large B)
+void bias_clip_finalize(const float* colsum_part, const float* sq_part, int nparts, float C, float clamp,
+                        float* factors_ws, float* norms_out, float* factors_out, void* db, int B, int n_out,
+                        int row_chunks, int out_dt, float inv_div, NoiseKey nk, cudaStream_t s);
 
 // ---- LayerNorm -----------------------------------------------------------------------------------
 struct LnPlan { int tpr, cpt, cw, rows_per_block, chunks; bool vec; };
@@ -53,6 +57,10 @@ void ln_psgrad_reduce(float* part, float* sumsq, int B, int chunks, int d, cudaS
 // both tensors in one launch: out0/nk0 for dgamma, out1/nk1 for dbeta (out1 may be null)
 void ln_psgrad_finalize(const float* part, const float* factors, void* out0, void* out1, int B, int chunks,
                         int d, int out_dt, float inv_div, NoiseKey nk0, NoiseKey nk1, cudaStream_t s);
+// clip factors from sumsq[2B, nparts] and the finalisation of both tensors in one launch
+void ln_clip_finalize(const float* part, const float* sumsq, int nparts, float C, float clamp, float* factors_ws,
+                      float* norms0, float* norms1, void* out0, void* out1, int B, int chunks, int d, int out_dt,
+                      float inv_div, NoiseKey nk0, NoiseKey nk1, cudaStream_t s);
 
 // ---- tcgen05 / TMEM / TMA kernels (bf16 / fp16, aligned shapes) ---------------------------------
 struct TcPlan {

@@ -248,10 +248,92 @@ __global__ void __launch_bounds__(288) ln_fwd_staged_kernel(const Tin* __restric
   }
 }
 
+// Direct forward for rows that fit a warp's registers (d <= 32 columns per lane): one warp per row,
+// grid-stride, the row held as the raw 16-byte vectors it was loaded as (values are re-converted in
+// each of the three passes, which keeps the kernel near 48 registers and ~40 warps resident per SM --
+// the kernel is bound by instruction issue, so resident warps matter more than anything else);
+// gamma and beta sit in shared memory as fp32.
+template <typename Tin, int NV>
+__global__ void __launch_bounds__(256, 4) ln_fwd_rows_kernel(const Tin* __restrict__ x,
+                                                             const void* __restrict__ gamma,
+                                                             const void* __restrict__ beta,
+                                                             Tin* __restrict__ y, float* __restrict__ mean,
+                                                             float* __restrict__ rstd, int rows, int d,
+                                                             float eps, int pdt) {
+  constexpr int VEC = 16 / sizeof(Tin);
+  extern __shared__ __align__(16) float ln_params[];   // gamma[d], beta[d]
+  for (int c = threadIdx.x; c < d; c += 256) {
+    ln_params[c] = load_as(gamma, pdt, c);
+    ln_params[d + c] = load_as(beta, pdt, c);
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int nwarps = gridDim.x * 8;
+  const float inv_d = 1.0f / d;
+  for (int row = blockIdx.x * 8 + (threadIdx.x >> 5); row < rows; row += nwarps) {
+    const Tin* xr = x + static_cast<size_t>(row) * d;
+    uint4 raw[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int c = (j * 32 + lane) * VEC;
+      raw[j] = (c < d) ? __ldg(reinterpret_cast<const uint4*>(xr + c)) : make_uint4(0, 0, 0, 0);
+    }
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const Tin* e = reinterpret_cast<const Tin*>(&raw[j]);
+#pragma unroll
+      for (int v = 0; v < VEC; ++v) sum += to_f32<Tin>(e[v]);     // padding vectors are zero
+    }
+    const float mu = warp_sum(sum) * inv_d;
+    float q = 0.f;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      if ((j * 32 + lane) * VEC < d) {
+        const Tin* e = reinterpret_cast<const Tin*>(&raw[j]);
+#pragma unroll
+        for (int v = 0; v < VEC; ++v) { const float t = to_f32<Tin>(e[v]) - mu; q = fmaf(t, t, q); }
+      }
+    }
+    const float rs = 1.0f / sqrtf(warp_sum(q) * inv_d + eps);
+    if (lane == 0) { mean[row] = mu; rstd[row] = rs; }
+    Tin* yr = y + static_cast<size_t>(row) * d;
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int c = (j * 32 + lane) * VEC;
+      if (c < d) {
+        const Tin* e = reinterpret_cast<const Tin*>(&raw[j]);
+        uint4 outv;
+        Tin* o = reinterpret_cast<Tin*>(&outv);
+#pragma unroll
+        for (int v4 = 0; v4 < VEC / 4; ++v4) {
+          const float4 g = *reinterpret_cast<const float4*>(ln_params + c + 4 * v4);
+          const float4 b = *reinterpret_cast<const float4*>(ln_params + d + c + 4 * v4);
+          o[4 * v4 + 0] = from_f32<Tin>(fmaf((to_f32<Tin>(e[4 * v4 + 0]) - mu) * rs, g.x, b.x));
+          o[4 * v4 + 1] = from_f32<Tin>(fmaf((to_f32<Tin>(e[4 * v4 + 1]) - mu) * rs, g.y, b.y));
+          o[4 * v4 + 2] = from_f32<Tin>(fmaf((to_f32<Tin>(e[4 * v4 + 2]) - mu) * rs, g.z, b.z));
+          o[4 * v4 + 3] = from_f32<Tin>(fmaf((to_f32<Tin>(e[4 * v4 + 3]) - mu) * rs, g.w, b.w));
+        }
+        *reinterpret_cast<uint4*>(yr + c) = outv;
+      }
+    }
+  }
+}
+
 template <typename Tin>
 static void ln_fwd_t(const void* x, const void* gamma, const void* beta, void* y, float* mean,
                      float* rstd, int rows, int d, float eps, int pdt, bool vec, cudaStream_t s) {
   constexpr int V = 16 / sizeof(Tin);
+  if (vec && d <= 1024 && d % 4 == 0) {
+    // rows of up to 32 columns per lane: registers only, as many resident warps as possible
+    constexpr int NVR = 32 / V;
+    int grid = ceil_div(rows, 8);
+    if (grid > 148 * 8) grid = 148 * 8;
+    ln_fwd_rows_kernel<Tin, NVR><<<grid, 256, static_cast<size_t>(2) * d * sizeof(float), s>>>(
+        (const Tin*)x, gamma, beta, (Tin*)y, mean, rstd, rows, d, eps, pdt);
+    note_launch();
+    return;
+  }
   const size_t stage_bytes = static_cast<size_t>(8) * d * sizeof(Tin);
   if (vec && stage_bytes * 2 <= LN_SMEM_BUDGET) {
     const int groups = ceil_div(rows, 8);
@@ -437,7 +519,7 @@ __global__ void __launch_bounds__(STAGED ? CW + 32 : CW) ln_bwd_kernel(
         asm volatile("bar.sync %0, %1;" ::"r"(1 + rg), "r"(TPR) : "memory");
       }
       if (dx != nullptr) {
-        const float c1 = s1 * inv_d, c2 = s2 * inv_d;
+        const float a1 = -(s1 * inv_d) * rs, a2 = -(s2 * inv_d) * rs;
         Tin* dxr = dx + row * d;
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
@@ -449,11 +531,11 @@ __global__ void __launch_bounds__(STAGED ? CW + 32 : CW) ln_bwd_kernel(
 #pragma unroll
             for (int v = 0; v < VEC; ++v) {
               const int i = j * VEC + v;
-              o[v] = from_f32<Tin>((wd[i] - (xh[i] * c1 + c2)) * rs);
+              o[v] = from_f32<Tin>(fmaf(xh[i], a1, fmaf(wd[i], rs, a2)));   // (wd - (xhat*c1 + c2)) * rs
             }
             *reinterpret_cast<uint4*>(dxr + c) = outv;
           } else {
-            dxr[c] = from_f32<Tin>((wd[j] - (xh[j] * c1 + c2)) * rs);
+            dxr[c] = from_f32<Tin>(fmaf(xh[j], a1, fmaf(wd[j], rs, a2)));
           }
         }
       }
@@ -625,6 +707,51 @@ void ln_psgrad_finalize(const float* part, const float* factors, void* out0, voi
   dim3 grid(ceil_div(d, 256), 2);
   ln_psgrad_finalize_kernel<<<grid, 256, 0, s>>>(part, factors, out0, out1, B, chunks, d, out_dt, inv_div, nk0, nk1);
   note_launch();
+}
+
+__global__ void __launch_bounds__(256) ln_clip_finalize_kernel(
+    const float* __restrict__ part, const float* __restrict__ sumsq, int nparts, float C, float clamp,
+    float* __restrict__ norms0, float* __restrict__ norms1, void* __restrict__ out0, void* __restrict__ out1,
+    int B, int chunks, int d, int out_dt, float inv_div, NoiseKey nk0, NoiseKey nk1) {
+  extern __shared__ float s_fac[];  // [B] factors of this block's tensor
+  const int tensor = blockIdx.y;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  for (int b = w; b < B; b += 8) {
+    float sq = 0.f;
+    for (int i = lane; i < nparts; i += 32) sq += sumsq[static_cast<size_t>(tensor * B + b) * nparts + i];
+    sq = warp_sum(sq);
+    if (lane == 0) {
+      const float n = sqrtf(fmaxf(sq, 0.f));
+      s_fac[b] = clip_factor(n, C, clamp);
+      float* no = tensor == 0 ? norms0 : norms1;
+      if (blockIdx.x == 0 && no != nullptr) no[b] = n;
+    }
+  }
+  __syncthreads();
+  const int c = blockIdx.x * 256 + threadIdx.x;
+  void* out = tensor == 0 ? out0 : out1;
+  if (c >= d || out == nullptr) return;
+  const float* p = part + static_cast<size_t>(tensor) * B * chunks * d;
+  float acc = 0.f;
+  for (int b = 0; b < B; ++b) acc = fmaf(s_fac[b], p[static_cast<size_t>(b) * chunks * d + c], acc);
+  float v = acc * inv_div;
+  const NoiseKey& nk = tensor == 0 ? nk0 : nk1;
+  if (nk.std != 0.f) v += noise_at(nk, c);
+  store_as(out, out_dt, c, v);
+}
+
+void ln_clip_finalize(const float* part, const float* sumsq, int nparts, float C, float clamp, float* factors_ws,
+                      float* norms0, float* norms1, void* out0, void* out1, int B, int chunks, int d, int out_dt,
+                      float inv_div, NoiseKey nk0, NoiseKey nk1, cudaStream_t s) {
+  if (static_cast<size_t>(B) * sizeof(float) <= 32 * 1024) {
+    dim3 grid(ceil_div(d, 256), 2);
+    ln_clip_finalize_kernel<<<grid, 256, B * sizeof(float), s>>>(part, sumsq, nparts, C, clamp, norms0, norms1, out0,
+                                                                 out1, B, chunks, d, out_dt, inv_div, nk0, nk1);
+    note_launch();
+    return;
+  }
+  clip_factors_pair(sumsq, nparts, B, C, clamp, factors_ws, norms0, norms1, s);
+  ln_psgrad_finalize(part, factors_ws, out0, out1, B, chunks, d, out_dt, inv_div, nk0, nk1, s);
 }
 
 }  // namespace fdp

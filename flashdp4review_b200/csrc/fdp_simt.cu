@@ -369,4 +369,61 @@ void bias_finalize(const float* colsum_part, const float* factors, void* db, int
   note_launch();
 }
 
+// The same with the clip factors computed in the kernel (one launch less): every block derives the
+// B factors from the sum-of-squares partials in the same fixed order (warp w takes samples w, w+8, ...),
+// block 0 also reports norms and factors.
+__global__ void __launch_bounds__(256) bias_finalize_fused_kernel(
+    const float* __restrict__ colsum_part, const float* __restrict__ sq_part, int nparts, float C, float clamp,
+    float* __restrict__ norms_out, float* __restrict__ factors_out, void* __restrict__ db, int B, int n_out,
+    int row_chunks, int out_dt, float inv_div, NoiseKey nk) {
+  extern __shared__ float s_fac[];  // [B]
+  __shared__ float part[8][32];
+  const int col = threadIdx.x & 31, sl = threadIdx.x >> 5;
+  for (int b = sl; b < B; b += 8) {
+    float sq = 0.f;
+    for (int i = col; i < nparts; i += 32) sq += sq_part[static_cast<size_t>(b) * nparts + i];
+    sq = warp_sum(sq);
+    if (col == 0) {
+      const float n = sqrtf(fmaxf(sq, 0.f));
+      const float f = clip_factor(n, C, clamp);
+      s_fac[b] = f;
+      if (blockIdx.x == 0) {
+        if (norms_out) norms_out[b] = n;
+        if (factors_out) factors_out[b] = f;
+      }
+    }
+  }
+  __syncthreads();
+  const int o = blockIdx.x * 32 + col;
+  const int pairs = B * row_chunks;
+  float acc = 0.f;
+  if (o < n_out) {
+    for (int p = sl; p < pairs; p += 8)
+      acc = fmaf(s_fac[p / row_chunks], colsum_part[static_cast<size_t>(p) * n_out + o], acc);
+  }
+  part[sl][col] = acc;
+  __syncthreads();
+  if (sl == 0 && o < n_out) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) t += part[k][col];
+    float v = t * inv_div;
+    if (nk.std != 0.f) v += noise_at(nk, o);
+    store_as(db, out_dt, o, v);
+  }
+}
+
+void bias_clip_finalize(const float* colsum_part, const float* sq_part, int nparts, float C, float clamp,
+                        float* factors_ws, float* norms_out, float* factors_out, void* db, int B, int n_out,
+                        int row_chunks, int out_dt, float inv_div, NoiseKey nk, cudaStream_t s) {
+  if (static_cast<size_t>(B) * sizeof(float) <= 32 * 1024) {
+    bias_finalize_fused_kernel<<<ceil_div(n_out, 32), 256, B * sizeof(float), s>>>(
+        colsum_part, sq_part, nparts, C, clamp, norms_out, factors_out, db, B, n_out, row_chunks, out_dt, inv_div, nk);
+    note_launch();
+    return;
+  }
+  clip_factors(sq_part, nparts, B, C, clamp, nullptr, factors_ws, norms_out, factors_out, s);
+  bias_finalize(colsum_part, factors_ws, db, B, n_out, row_chunks, out_dt, inv_div, nk, s);
+}
+
 }  // namespace fdp

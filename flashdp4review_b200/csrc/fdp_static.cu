@@ -84,10 +84,8 @@ extern "C" int fdp_bias_grad_static(const void* G, void* db, float* norms_out, f
   const int div = p->batch_divisor > 0 ? p->batch_divisor : B;
   const float inv_div = 1.0f / (static_cast<float>(div) * static_cast<float>(T));
   gstats(G, colsum_part, sq_part, B, T, n_out, in_dtype, pl, s);
-  clip_factors(sq_part, pl.row_chunks * pl.col_chunks, B, p->C, p->clamp_value, nullptr, factors, norms_out,
-               factors_out, s);
-  bias_finalize(colsum_part, factors, db, B, n_out, pl.row_chunks, out_dtype, inv_div,
-                make_noise_key(p, p->param_id), s);
+  bias_clip_finalize(colsum_part, sq_part, pl.row_chunks * pl.col_chunks, p->C, p->clamp_value, factors, norms_out,
+                     factors_out, db, B, n_out, pl.row_chunks, out_dtype, inv_div, make_noise_key(p, p->param_id), s);
   FDP_LAUNCH_OK();
   return FDP_OK;
 }
