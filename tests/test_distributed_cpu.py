@@ -20,8 +20,6 @@ def _worker(rank, world, port, overlap, results):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
-        import flashdp4review_b200 as fdp
-        from flashdp4review_b200 import runtime
         from flashdp4review_b200.distributed import DPGradReducer, init_data_parallel
         from flashdp4review_b200.layers._common import dp_scalars
         from flashdp4review_b200.layers.utils import DPParameter

@@ -1,13 +1,12 @@
 """Shape fuzzing of the weight-gradient entry point with hypothesis: arbitrary small shapes straddle
 the boundary between the generic kernels and the tensor-core kernels (row pitch multiple of 16 bytes,
 at least 128 features, T >= 64) and the boundaries of the 128x256x64 tiles."""
-import numpy as np
 import pytest
 import torch
 from hypothesis import given, settings, strategies as st, HealthCheck
 
 from oracle import dp_oracle as O
-from gpu_util import TOL, check_wgrad
+from gpu_util import check_wgrad
 
 pytestmark = pytest.mark.gpu
 

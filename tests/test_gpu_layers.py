@@ -1,6 +1,5 @@
 """DPLinear / DPConv1D / DPLayerNorm against the fixtures made by the reference's own autograd
 Functions (noise_multiplier = 0), plus the behaviours that differ from the reference by design."""
-import numpy as np
 import pytest
 import torch
 import torch.nn as nn

@@ -6,7 +6,7 @@ import torch
 
 from oracle import dp_oracle as O
 from conftest import rel_err, norm_err
-from gpu_util import TOL, dev, check_wgrad
+from gpu_util import dev, check_wgrad
 
 pytestmark = pytest.mark.gpu
 

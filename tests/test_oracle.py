@@ -2,8 +2,6 @@
 import math
 
 import numpy as np
-import pytest
-import torch
 
 from oracle import dp_oracle as O
 from conftest import rel_err, norm_err
