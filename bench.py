@@ -210,7 +210,7 @@ def run_native(args, wl):
 
     def step(Xd, Gd):
         step_no[0] += 1
-        noise = ops.NoiseSpec(std=ops.noise_std(1.0, B * world), seed=1234, param_id=1, step=step_no[0],
+        noise = ops.NoiseSpec(std=ops.noise_std(args.sigma, B * world), seed=1234, param_id=1, step=step_no[0],
                               rank=rank, world=world)
         dW = ops.dp_linear_weight_grad(Xd, Gd, 1.0, 1.0, batch_divisor=B * world, noise=noise,
                                        out_dtype=torch.float32, norm_algo=args.norm_algo)
@@ -368,7 +368,7 @@ def run_native(args, wl):
                 "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": dtn, "data": "synthetic",
                 "config": {"workload": args.workload, "B_per_gpu": B, "T": T, "in": n_in, "out": n_out,
-                           "C": 1.0, "noise_multiplier": 1.0, "bias": False, "grad_dtype": "f32",
+                           "C": 1.0, "noise_multiplier": args.sigma, "bias": False, "grad_dtype": "f32",
                            "flops_per_step_per_gpu": flops_bwd(B, T, n_in, n_out),
                            "l2": ("inputs (X, G: %.0f MB) larger than the 126 MB L2" % (h2d / 1e6)) if flush is None
                            else "L2 overwritten by a 256 MB fill between steps",
@@ -560,6 +560,7 @@ def main():
     ap.add_argument("--micro-batch", type=int, default=8, help="gpt2_medium: samples per GPU and step")
     ap.add_argument("--no-dp", action="store_true", help="gpt2_medium: leave the model unwrapped (context only)")
     ap.add_argument("--norm-algo", default="auto", choices=["auto", "direct", "gram"])
+    ap.add_argument("--sigma", type=float, default=1.0, help="noise_multiplier of the DP-Linear workloads")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work for cpu_baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
