@@ -157,7 +157,8 @@ __device__ __forceinline__ uint64_t operand_desc(uint32_t stage_base, int k16) {
 }
 
 // Finish 32 adjacent output columns of row m starting at column n: add the noise, convert, store.
-__device__ __forceinline__ void store_chunk32(const TcArgs& args, float v[32], int m, int n) {
+__device__ __forceinline__ void store_chunk32(const TcArgs& args, float v[32], int m, int n,
+                                              bool add_noise = true) {
   if (m >= args.M || n >= args.N) return;
   const size_t idx0 = static_cast<size_t>(m) * args.ld_out + n;
   if (args.bias != nullptr) {
@@ -165,7 +166,7 @@ __device__ __forceinline__ void store_chunk32(const TcArgs& args, float v[32], i
     for (int j = 0; j < 32; ++j)
       if (n + j < args.N) v[j] += load_as(args.bias, args.bias_dt, n + j);
   }
-  if (args.nk.std != 0.f) {
+  if (add_noise && args.nk.std != 0.f) {
     if ((idx0 & 3) == 0) {
 #pragma unroll
       for (int g = 0; g < 8; ++g) {
@@ -208,6 +209,23 @@ __device__ __forceinline__ void store_chunk32(const TcArgs& args, float v[32], i
     for (int j = 0; j < 32; ++j)
       if (n + j < args.N) store_as(args.out, args.out_dt, idx0 + j, v[j]);
   }
+}
+
+// accr[4g .. 4g+3] += z * f with g known only at run time: a switch keeps every index static, so
+// the 128 accumulators stay in registers.
+__device__ __forceinline__ void add_group(float (&accr)[128], int g, const float z[4], float f) {
+#define FDP_ADD_GROUP(G) case G: accr[4 * G] = fmaf(z[0], f, accr[4 * G]); accr[4 * G + 1] = fmaf(z[1], f, accr[4 * G + 1]); \
+    accr[4 * G + 2] = fmaf(z[2], f, accr[4 * G + 2]); accr[4 * G + 3] = fmaf(z[3], f, accr[4 * G + 3]); break;
+  switch (g) {
+    FDP_ADD_GROUP(0) FDP_ADD_GROUP(1) FDP_ADD_GROUP(2) FDP_ADD_GROUP(3) FDP_ADD_GROUP(4) FDP_ADD_GROUP(5)
+    FDP_ADD_GROUP(6) FDP_ADD_GROUP(7) FDP_ADD_GROUP(8) FDP_ADD_GROUP(9) FDP_ADD_GROUP(10) FDP_ADD_GROUP(11)
+    FDP_ADD_GROUP(12) FDP_ADD_GROUP(13) FDP_ADD_GROUP(14) FDP_ADD_GROUP(15) FDP_ADD_GROUP(16) FDP_ADD_GROUP(17)
+    FDP_ADD_GROUP(18) FDP_ADD_GROUP(19) FDP_ADD_GROUP(20) FDP_ADD_GROUP(21) FDP_ADD_GROUP(22) FDP_ADD_GROUP(23)
+    FDP_ADD_GROUP(24) FDP_ADD_GROUP(25) FDP_ADD_GROUP(26) FDP_ADD_GROUP(27) FDP_ADD_GROUP(28) FDP_ADD_GROUP(29)
+    FDP_ADD_GROUP(30) FDP_ADD_GROUP(31)
+    default: break;
+  }
+#undef FDP_ADD_GROUP
 }
 
 // ---- the kernel ---------------------------------------------------------------------------------------
@@ -497,6 +515,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         float accr[128];
 #pragma unroll
         for (int i = 0; i < 128; ++i) accr[i] = 0.f;
+        // Whole tiles take their Gaussian noise into the accumulators a few element groups per
+        // sample segment, in the time these warps would otherwise wait for the next segment's
+        // MMAs; K-split parts stay noise-free (the fix-up kernel adds the noise once per tile).
+        const bool pre_noise = slot < 0 && args.nk.std != 0.f && (args.ld_out & 3) == 0 && m < args.M;
+        const uint64_t g0 = (static_cast<uint64_t>(m) * args.ld_out + n0 + half * 128) >> 2;
+        const float unscale = 1.f / args.scale;
+        const int nseg = (ks1 - ks0 + args.seg_stages - 1) / args.seg_stages;
+        int ng = 0, seg = 0;
         for (int ks = ks0; ks < ks1 && ok; ks += args.seg_stages, ++it) {
           const int acc = it % NUM_ACC;
           const uint32_t acc_phase = (it / NUM_ACC) & 1u;
@@ -518,6 +544,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             if (CTAS == 1 || is_leader) mbar_arrive(tempty_bar(acc));
             else mbar_arrive_cluster(mapa_u32(tempty_bar(acc), 0));
           }
+          ++seg;
+          if (pre_noise) {
+            const int target = (32 * seg) / nseg;
+            for (; ng < target; ++ng) {
+              float z[4];
+              noise_group(args.nk, g0 + ng, z);
+              add_group(accr, ng, z, unscale);
+            }
+          }
         }
         if (!ok) break;
         if (slot >= 0) {
@@ -531,7 +566,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             float v[32];
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = accr[c4 * 32 + j] * args.scale;
-            store_chunk32(args, v, m, n0 + half * 128 + c4 * 32);
+            store_chunk32(args, v, m, n0 + half * 128 + c4 * 32, !pre_noise);
           }
         }
         continue;
