@@ -130,6 +130,22 @@ def bmtm_clip(tensor1, tensor2, clip_args=None):
     return dp_linear_weight_grad(tensor2, tensor1, C, clamp, batch_divisor=1)
 
 
+def bmm_clip(tensor1, tensor2, clip_args=None):
+    """`bmm_clip(tensor1=(B,M,K), tensor2=(B,K,N), clip_args=[C, clamp])` -> sum_b clip(t1_b t2_b)
+    (flashdp/core/bmm_clip_loop.py:150-162; exported by flashdp.core, called by no layer).  The
+    library contracts over the shared leading axis of both operands, so tensor1 is laid out as
+    (B,K,M) first -- one extra pass over tensor1."""
+    return bmtm_clip(tensor1.transpose(1, 2).contiguous(), tensor2, clip_args)
+
+
+def mm_clip(mat1, mat2, clip_args=None):
+    """Per-token clipping: `mm_clip(mat1=(M,K), mat2=(K,N))` -> sum_k clip(a_k b_k^T), each outer
+    product of column k of mat1 and row k of mat2 clipped by its own Frobenius norm
+    ||a_k|| * ||b_k|| (flashdp/core/mm_clip_loop.py:127-139; called by no layer).  Every k is a
+    sample with a single row, which the library handles as a short sequence."""
+    return bmtm_clip(mat1.t().contiguous().unsqueeze(1), mat2.contiguous().unsqueeze(1), clip_args)
+
+
 # ------------------------------------------------------------------------------------------------
 # bias gradient
 # ------------------------------------------------------------------------------------------------

@@ -52,11 +52,13 @@ int check_params(const fdp_dp_params* p) {
 struct WgradWs {
   int* status; float* norms; float* factors; float* partials; void* tc_extra;
   size_t bytes; int nparts; TcPlan tc;
+  bool short_seq;   // norms by the small Gram kernel (T < SHORT_SEQ unless the caller asked for the direct norm)
 };
 WgradWs wgrad_ws(void* base, int B, int T, int n_in, int n_out, int dt, int norm_algo) {
   WgradWs w;
   w.tc = tc_plan(B, T, n_in, n_out, dt, norm_algo);
-  w.nparts = w.tc.ok ? w.tc.nparts : simt_norm_tiles(n_in, n_out);
+  w.short_seq = T < SHORT_SEQ && norm_algo != FDP_NORM_DIRECT;
+  w.nparts = w.tc.ok ? w.tc.nparts : (w.short_seq ? 1 : simt_norm_tiles(n_in, n_out));
   Carver c(base);
   w.status = c.take<int>(64);
   w.norms = c.take<float>(B);
@@ -175,7 +177,9 @@ int fdp_linear_wgrad(const void* G, const void* X, void* dW, float* norms_out, f
   FDP_CUDA_OK(cudaMemsetAsync(w.status, 0, sizeof(int), s));
 
   prof_mark(0, s);
-  if (w.tc.ok) {
+  if (w.short_seq) {
+    simt_norm_gram_small(G, X, w.partials, B, T, n_in, n_out, in_dtype, s);
+  } else if (w.tc.ok) {
     if ((st = tc_norms(G, X, w.partials, w.status, B, T, n_in, n_out, in_dtype, w.tc, s)) != FDP_OK) return st;
   } else {
     simt_norm_direct(G, X, w.partials, B, T, n_in, n_out, in_dtype, s);

@@ -12,6 +12,10 @@ int simt_norm_tiles(int n_in, int n_out);
 // partials[b*ntiles + tile] = sum of squares of one 64x64 tile of G_b^T X_b
 void simt_norm_direct(const void* G, const void* X, float* partials, int B, int T, int n_in,
                       int n_out, int dt, cudaStream_t s);
+// short sequences (T < SHORT_SEQ): sumsq[b] = ||G_b^T X_b||_F^2 through the T x T Gram matrices
+constexpr int SHORT_SEQ = 64;
+void simt_norm_gram_small(const void* G, const void* X, float* sumsq, int B, int T, int n_in, int n_out,
+                          int dt, cudaStream_t s);
 // sumsq_b = fixed-order sum of partials[b, 0..nparts); norm = sqrt; factor = clip_factor(norm)
 void clip_factors(const float* partials, int nparts, int B, float C, float clamp, float* norms,
                   float* factors, float* norms_out, float* factors_out, cudaStream_t s);
@@ -70,6 +74,7 @@ struct TcPlan {
   size_t split_bytes;
   int nparts;       // norm partials per sample
   bool scaled_epilogue;  // clip factors applied per sample in the GEMM epilogue, no pre-scale pass
+  bool short_seq;        // T < SHORT_SEQ: norms by simt_norm_gram_small, clipped sum over the pre-scaled G
 };
 TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo);
 int tc_norms(const void* G, const void* X, float* partials, int* dev_status, int B, int T, int n_in,

@@ -90,6 +90,88 @@ void simt_norm_direct(const void* G, const void* X, float* partials, int B, int 
   note_launch();
 }
 
+// ---- per-sample norm for short sequences (T < 64), through the T x T Gram matrices ---------------
+//   ||G_b^T X_b||_F^2 = sum_{t,s} (G_b G_b^T)[t,s] * (X_b X_b^T)[t,s]
+// costs T^2 (in + out) multiply-adds per sample instead of T * in * out; for T = 1 (2-D layer
+// inputs) it is the rank-one identity ||g||^2 ||x||^2 and one read of G and X.  One block per
+// sample.  The (t,s) plane is cut into 4x4 blocks, one per thread group; a group's `cs` lanes
+// split the 64 columns of a staged chunk and combine by shuffles, so short sequences still use
+// whole warps.  Rows t >= T of the staged chunk are zero and add nothing.
+constexpr int GS_COLS = 64, GS_PITCH = 68;   // chunk columns; floats per staged column (T padded, 16-byte rows)
+
+template <typename Tin>
+__device__ __forceinline__ void gram_small_accumulate(const Tin* __restrict__ Mb, int T, int n, int tb,
+                                                      int cs, float (*tile)[GS_PITCH], float acc[4][4]) {
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  const int blk = tid / cs, part = tid % cs;
+  const int bt = blk / tb, bs = blk % tb;
+  const bool active = blk < tb * tb;
+  const int tp = tb * 4;
+  for (int c0 = 0; c0 < n; c0 += GS_COLS) {
+    __syncthreads();
+    for (int i = tid; i < tp * GS_COLS; i += nthreads) {
+      const int t = i / GS_COLS, c = i % GS_COLS;
+      tile[c][t] = (t < T && c0 + c < n) ? to_f32<Tin>(Mb[static_cast<size_t>(t) * n + c0 + c]) : 0.f;
+    }
+    __syncthreads();
+    if (active) {
+      for (int c = part; c < GS_COLS; c += cs) {
+        const float4 a = *reinterpret_cast<const float4*>(&tile[c][bt * 4]);
+        const float4 b = *reinterpret_cast<const float4*>(&tile[c][bs * 4]);
+        const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+      }
+    }
+  }
+  // the lanes of a group are adjacent and cs is a power of two <= 32: butterfly inside the group
+  for (int o = cs >> 1; o > 0; o >>= 1) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) acc[i][j] += __shfl_xor_sync(0xffffffffu, acc[i][j], o);
+  }
+}
+
+template <typename Tin>
+__global__ void __launch_bounds__(256) gram_small_norm_kernel(const Tin* __restrict__ G,
+                                                              const Tin* __restrict__ X,
+                                                              float* __restrict__ sumsq, int T, int n_in,
+                                                              int n_out, int tb, int cs) {
+  __shared__ __align__(16) float tile[GS_COLS][GS_PITCH];
+  __shared__ float red[32];
+  const int b = blockIdx.x;
+  float gg[4][4] = {}, xx[4][4] = {};
+  gram_small_accumulate<Tin>(G + static_cast<size_t>(b) * T * n_out, T, n_out, tb, cs, tile, gg);
+  gram_small_accumulate<Tin>(X + static_cast<size_t>(b) * T * n_in, T, n_in, tb, cs, tile, xx);
+  float v = 0.f;
+  if (threadIdx.x % cs == 0 && threadIdx.x / cs < tb * tb) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) v = fmaf(gg[i][j], xx[i][j], v);
+  }
+  v = block_sum(v, red);
+  if (threadIdx.x == 0) sumsq[b] = v;
+}
+
+void simt_norm_gram_small(const void* G, const void* X, float* sumsq, int B, int T, int n_in, int n_out,
+                          int dt, cudaStream_t s) {
+  const int tb = ceil_div(T, 4);                 // T < 64: at most 16 x 16 thread groups
+  int cs = 32;
+  while (cs > 1 && tb * tb * cs > 256) cs >>= 1;
+  const int threads = ceil_div(tb * tb * cs, 32) * 32;
+  if (dt == FDP_F32)
+    gram_small_norm_kernel<float><<<B, threads, 0, s>>>((const float*)G, (const float*)X, sumsq, T, n_in, n_out, tb, cs);
+  else if (dt == FDP_BF16)
+    gram_small_norm_kernel<__nv_bfloat16><<<B, threads, 0, s>>>((const __nv_bfloat16*)G, (const __nv_bfloat16*)X, sumsq, T, n_in, n_out, tb, cs);
+  else
+    gram_small_norm_kernel<__half><<<B, threads, 0, s>>>((const __half*)G, (const __half*)X, sumsq, T, n_in, n_out, tb, cs);
+  note_launch();
+}
+
 // ---- clip factors --------------------------------------------------------------------------------
 // split > 0: entries [split, ..) report their norm to norms_out2[b - split] (two tensors, one launch)
 __global__ void __launch_bounds__(256) clip_factors_kernel(const float* __restrict__ partials,

@@ -879,8 +879,18 @@ int gram_tiles(int T) {
 // matrices large enough that the 128x256 tile is not mostly padding.
 TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo) {
   TcPlan p; p.ok = false; p.algo = FDP_NORM_DIRECT; p.ws_bytes = 0; p.nparts = 0; p.scaled_epilogue = false;
+  p.short_seq = false; p.split_bytes = 0;
   if (dt != FDP_BF16 && dt != FDP_F16) return p;
-  if (n_in % 8 != 0 || n_out % 8 != 0 || n_in < 128 || n_out < 128 || T < 64) return p;
+  if (n_in % 8 != 0 || n_out % 8 != 0 || n_in < 128 || n_out < 128) return p;
+  if (T < SHORT_SEQ) {
+    // short sequences: the norms come from the small Gram kernel (one partial per sample); the
+    // clipped sum is still one GEMM with K = B*T over the pre-scaled copy of G, if K is worth a tile
+    if (norm_algo == FDP_NORM_DIRECT || static_cast<long long>(B) * T < 4 * BK) return p;
+    p.ok = true; p.algo = FDP_NORM_GRAM; p.short_seq = true; p.nparts = 1;
+    p.split_bytes = split_ws_bytes();
+    p.ws_bytes = p.split_bytes + align256(static_cast<size_t>(B) * T * n_out * 2);
+    return p;
+  }
   const bool direct_ok = (T % BK == 0);   // a K stage must not run into the next sample's rows
   // tensor-core work of the two norm algorithms, in padded tile units
   const double direct = 2.0 * T * (ceil_div(n_out, BM) * BM) * static_cast<double>(ceil_div(n_in, BN) * BN);

@@ -9,7 +9,12 @@ size.  Parameters without the `requires_dp` flag carry ordinary local-mean gradi
 averaged instead.
 
     reducer = DPGradReducer(model)          # after wrap_with_flashdp_layers, on every rank
-    loss.backward(); reducer.finish(); optimizer.step()
+    loss.backward(); reducer.finish(); optimizer.step(); reducer.zero_grad()
+
+With `grad_as_bucket_view=True` every `p.grad` is a view into its bucket's flat buffer: autograd
+accumulates into the bucket in place, the all-reduce runs on the buffer itself and nothing is
+packed or unpacked.  With gradient accumulation (runtime.accumulate) pass `sync=False` to
+`finish()` on all but the last micro-step.
 """
 import torch
 import torch.distributed as dist
@@ -30,20 +35,24 @@ class DPGradReducer:
     Buckets follow reverse parameter order (roughly backward order).  When the last gradient of
     a bucket is accumulated, the bucket is packed into a flat buffer and all-reduced
     asynchronously on the communication stream of the backend, so the transfer overlaps the
-    rest of the backward pass; `finish()` waits and unpacks.
+    rest of the backward pass; `finish()` waits and unpacks.  With `grad_as_bucket_view` the
+    gradients live in the flat buffers from the start (buckets then hold either DP tensors, which
+    are summed, or ordinary ones, which are averaged) and packing/unpacking disappears.
     """
 
-    def __init__(self, module_or_params, group=None, bucket_bytes=64 << 20, overlap=True):
+    def __init__(self, module_or_params, group=None, bucket_bytes=64 << 20, overlap=True,
+                 grad_as_bucket_view=False):
         params = list(module_or_params.parameters()) if hasattr(module_or_params, "parameters") \
             else list(module_or_params)
         self.params = [p for p in params if p.requires_grad]
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.overlap = overlap
-        self.buckets = []          # list of lists of params (same dtype/device)
+        self.as_view = grad_as_bucket_view
+        self.buckets = []          # list of lists of params (same dtype/device; with views also same scale)
         cur, cur_bytes, key = [], 0, None
         for p in reversed(self.params):
-            k = (p.dtype, p.device)
+            k = (p.dtype, p.device, self._scale(p, self.world) if self.as_view else None)
             nbytes = p.numel() * p.element_size()
             if cur and (k != key or cur_bytes + nbytes > bucket_bytes):
                 self.buckets.append(cur)
@@ -57,9 +66,40 @@ class DPGradReducer:
         self._pending = [len(b) for b in self.buckets]
         self._inflight = {}
         self._hooks = []
+        self._sync = True
+        self._flat, self._views = [], {}
+        if self.as_view:
+            for b in self.buckets:
+                flat = torch.zeros(sum(p.numel() for p in b), dtype=b[0].dtype, device=b[0].device)
+                off = 0
+                for p in b:
+                    self._views[id(p)] = flat[off:off + p.numel()].view_as(p)
+                    off += p.numel()
+                self._flat.append(flat)
+            self._attach_views()
         if overlap and self.world > 1:
             for p in self.params:
                 self._hooks.append(p.register_post_accumulate_grad_hook(self._on_grad))
+
+    def _attach_views(self):
+        for i in range(len(self.buckets)):
+            self._attach_views_of(i)
+
+    def zero_grad(self):
+        """Zero the gradients while keeping them views of the buckets (an optimizer's
+        zero_grad(set_to_none=True) would detach them; the next finish() re-attaches by copy)."""
+        if self.as_view:
+            for flat in self._flat:
+                flat.zero_()
+            self._attach_views()
+        else:
+            for p in self.params:
+                p.grad = None
+
+    def set_sync(self, sync: bool):
+        """sync=False: the coming backward is an accumulation micro-step -- gradients pile up
+        locally and no collective starts.  Set it back to True before the last micro-step."""
+        self._sync = bool(sync)
 
     # a non-DP gradient is a local mean: average it; a DP gradient is already divided by the
     # global batch: sum it
@@ -68,32 +108,55 @@ class DPGradReducer:
         return 1.0 if getattr(p, "requires_dp", False) else 1.0 / world
 
     def _launch(self, i):
-        bucket = [p for p in self.buckets[i] if p.grad is not None]
-        if not bucket:
-            return
-        parts = []
-        for p in bucket:
-            sc = self._scale(p, self.world)
-            parts.append((p.grad if sc == 1.0 else p.grad * sc).reshape(-1))
-        flat = torch.cat(parts)
+        if self.as_view:
+            self._attach_views_of(i)
+            flat, bucket = self._flat[i], self.buckets[i]
+            sc = self._scale(bucket[0], self.world)
+            if sc != 1.0:
+                flat.mul_(sc)
+        else:
+            bucket = [p for p in self.buckets[i] if p.grad is not None]
+            if not bucket:
+                return
+            parts = []
+            for p in bucket:
+                sc = self._scale(p, self.world)
+                parts.append((p.grad if sc == 1.0 else p.grad * sc).reshape(-1))
+            flat = torch.cat(parts)
         work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
         self._inflight[i] = (work, flat, bucket)
 
+    def _attach_views_of(self, i):
+        """Make every gradient of bucket i a view of its flat buffer; a gradient that autograd
+        allocated itself (after a zero_grad(set_to_none=True)) is copied in first."""
+        for p in self.buckets[i]:
+            v = self._views[id(p)]
+            if p.grad is not None and p.grad.data_ptr() != v.data_ptr():
+                v.copy_(p.grad)
+            p.grad = v
+
     def _on_grad(self, p):
+        if not self._sync:
+            return
         i = self._bucket_of[id(p)]
         self._pending[i] -= 1
         if self._pending[i] == 0:
             self._launch(i)
 
-    def finish(self):
+    def finish(self, sync=None):
         """Wait for every bucket (launching those not yet started) and write the reduced
-        gradients back.  Call once per step, after backward and before the optimizer."""
-        if self.world > 1:
+        gradients back.  Call once per optimizer step, after the (last) backward and before the
+        optimizer; `sync=False` skips the collective (an accumulation micro-step)."""
+        if sync is None:
+            sync = self._sync
+        if self.world > 1 and sync:
             for i in range(len(self.buckets)):
                 if i not in self._inflight:
                     self._launch(i)
             for i, (work, flat, bucket) in sorted(self._inflight.items()):
                 work.wait()
+                if self.as_view:
+                    continue
                 off = 0
                 for p in bucket:
                     n = p.numel()

@@ -33,8 +33,11 @@ def reshape_to_3d(input, grad_output):
 def dp_scalars(local_batch, noise_multiplier, param_id, step, param_id2=0):
     """(batch_divisor, NoiseSpec) for one backward call under the current run layout."""
     rank, world = runtime.data_parallel()
-    global_batch = local_batch * world
-    return global_batch, NoiseSpec(std=noise_std(noise_multiplier, global_batch), seed=runtime.get_seed(),
+    micro_index, micro_steps = runtime.accumulation()
+    global_batch = local_batch * world * micro_steps
+    # under gradient accumulation only the last micro-step carries the (single) noise draw
+    std = noise_std(noise_multiplier, global_batch) if micro_index == micro_steps - 1 else 0.0
+    return global_batch, NoiseSpec(std=std, seed=runtime.get_seed(),
                                    param_id=param_id, param_id2=param_id2, step=step, rank=rank, world=world)
 
 

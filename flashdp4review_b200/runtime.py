@@ -5,6 +5,7 @@ Here the noise is a pure function of (seed, param_id, step, element index), and 
 data-parallel job is described once so every layer scales by the global batch and draws only
 its share of the noise before the all-reduce of the clipped sums.
 """
+import contextlib
 import itertools
 import os
 import threading
@@ -18,6 +19,8 @@ class _Run:
     world = 1
     rank = 0
     input_grad_impl = "library"   # "library": cuBLAS via torch (as the reference); "native": fdp_linear_dgrad
+    micro_index = 0               # gradient accumulation: which micro-step of `micro_steps` runs now
+    micro_steps = 1
 
 
 _run = _Run()
@@ -52,6 +55,37 @@ def set_data_parallel(rank: int, world: int):
 
 def data_parallel():
     return _run.rank, _run.world
+
+
+def set_accumulation(micro_index: int, micro_steps: int):
+    """Declare that the next backward pass is micro-step `micro_index` of `micro_steps` whose
+    gradients autograd adds up before one optimizer step.
+
+    The reference divides by the micro-batch and draws fresh noise in every backward
+    (flashdp/layers/linear.py:72-80), so accumulating k micro-steps yields k times the mean and k
+    noise draws.  With this setting every micro-step divides by the whole logical batch
+    (micro_steps * world * B_local) and only the last one adds noise, with
+    std = noise_multiplier / sqrt(whole batch): the accumulated gradient equals one step on the
+    concatenated batch.
+    """
+    if micro_steps < 1 or not (0 <= micro_index < micro_steps):
+        raise ValueError(f"bad accumulation state micro_index={micro_index} micro_steps={micro_steps}")
+    _run.micro_index, _run.micro_steps = int(micro_index), int(micro_steps)
+
+
+def accumulation():
+    return _run.micro_index, _run.micro_steps
+
+
+@contextlib.contextmanager
+def accumulate(micro_index: int, micro_steps: int):
+    """`with accumulate(i, k): loss_i.backward()` -- set_accumulation for the block, then back to
+    single-step behaviour."""
+    set_accumulation(micro_index, micro_steps)
+    try:
+        yield
+    finally:
+        set_accumulation(0, 1)
 
 
 def set_input_grad_impl(name: str):

@@ -46,7 +46,8 @@ enum fdp_layout { FDP_OUT_IN = 0, FDP_IN_OUT = 1 };
 
 /* how the per-sample norms ||G_b^T X_b||_F are obtained */
 enum fdp_norm_algo {
-  FDP_NORM_AUTO = 0,   /* pick per shape */
+  FDP_NORM_AUTO = 0,   /* pick per shape; sequences shorter than 64 rows use the Gram identity on T x T
+                        * blocks (for T = 1, i.e. 2-D layer inputs, that is ||g_b|| * ||x_b||) */
   FDP_NORM_DIRECT = 1, /* per-sample GEMM tiles, squared and reduced in the epilogue, never stored */
   FDP_NORM_GRAM = 2    /* sum_{t,s} (G_b G_b^T)_{ts} (X_b X_b^T)_{ts} */
 };

@@ -222,3 +222,37 @@ def test_batch_sharding_equals_single_rank(dtype, tol):
     two = sum(ops.dp_linear_weight_grad(Xd[:4], Z[:4], 1.0, 1.0, batch_divisor=B, out_dtype=torch.float32,
                                         noise=ops.NoiseSpec(std, 5, 3, 0, 9, r, 2)) for r in range(2))
     assert torch.equal(one, two)
+
+
+def test_gradient_accumulation_equals_one_step_on_the_whole_batch():
+    """Two micro-steps of 4 samples under runtime.accumulate add up to the gradient of one step on
+    all 8 samples (divisor 8, per-sample clipping unchanged), and only the last micro-step draws
+    noise, with the std of the whole batch."""
+    import flashdp4review_b200 as fdp
+    from flashdp4review_b200 import runtime
+    B, T, n_in, n_out = 8, 32, 64, 48
+    X, G, W = O.make_linear_inputs(B, T, n_in, n_out, 5e-2, seed=23)
+    G[1] *= 30.0
+
+    def grads(sigma, micro_steps):
+        fdp.manual_seed(3)
+        torch.manual_seed(0)              # same initial bias in every run
+        lin = fdp.DPLinear(n_in, n_out, C=0.4, noise_multiplier=sigma).to(dev())
+        ln = fdp.DPLayerNorm(n_out, C=0.4, noise_multiplier=sigma).to(dev())
+        with torch.no_grad():
+            lin.weight.copy_(W)
+        per = B // micro_steps
+        for i in range(micro_steps):
+            with runtime.accumulate(i, micro_steps):
+                sl = slice(i * per, (i + 1) * per)
+                ln(lin(X[sl].to(dev()))).backward(G[sl].to(dev()))
+        return [p.grad.clone() for p in (lin.weight, lin.bias, ln.weight, ln.bias)]
+
+    whole, split = grads(0.0, 1), grads(0.0, 2)
+    for a, b in zip(whole, split):
+        assert rel_err(b.cpu().numpy(), a.cpu().numpy()) < 1e-5
+    noisy = grads(2.0, 2)
+    resid = (noisy[0] - split[0]).flatten()
+    want = 2.0 / B ** 0.5
+    assert abs(float(resid.std()) / want - 1.0) < 0.05 and abs(float(resid.mean())) < 4 * want / resid.numel() ** 0.5
+    assert runtime.accumulation() == (0, 1)

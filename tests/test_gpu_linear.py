@@ -225,3 +225,28 @@ def test_abi_status_codes():
     with pytest.raises(RuntimeError):
         from flashdp4review_b200.core import ops
         ops.dp_linear_weight_grad(torch.zeros(1, 1, 8), torch.zeros(1, 1, 8), 1.0, 1.0)   # CPU tensors
+
+
+def test_bmm_clip_and_per_token_mm_clip(ops):
+    """The two operators flashdp.core exports beside bmtm_clip (flashdp/core/__init__.py:1-3):
+    bmm_clip sums clip(A_b B_b) over the batch, mm_clip clips every rank-one term a_k b_k^T."""
+    import numpy as np
+    gen = torch.Generator().manual_seed(12)
+    A = torch.randn(3, 20, 14, generator=gen) * 0.3
+    Bm = torch.randn(3, 14, 24, generator=gen)
+    A[1] *= 10.0
+    clip = torch.tensor([0.9, 1.0])
+    got = ops.bmm_clip(A.to(dev()), Bm.to(dev()), clip_args=clip).cpu().numpy()
+    want = np.zeros((20, 24))
+    for b in range(3):
+        P = A[b].double().numpy() @ Bm[b].double().numpy()
+        want += O.clip_factor(np.linalg.norm(P), 0.9, 1.0) * P
+    assert rel_err(got, want) < 1e-5
+
+    m1 = torch.randn(40, 50, generator=gen) * 0.2
+    m2 = torch.randn(50, 32, generator=gen)
+    m1[:, 7] *= 30.0
+    got = ops.mm_clip(m1.to(dev()), m2.to(dev()), clip_args=clip).cpu().numpy()
+    a, b = m1.double().numpy(), m2.double().numpy()
+    f = O.clip_factor(np.linalg.norm(a, axis=0) * np.linalg.norm(b, axis=1), 0.9, 1.0)
+    assert rel_err(got, (a * f[None, :]) @ b) < 1e-5

@@ -135,3 +135,45 @@ def test_kernel_variants_selected_by_environment(env):
     assert r.returncode == 0, r.stderr[-2000:]
     worst = float(r.stdout.strip().split("WORST")[-1])
     assert worst < 1e-2, worst
+
+
+# short sequences (T < 64): norms through the small Gram kernel, clipped sum as one GEMM over B*T rows
+SHORT = [(512, 1, 256, 384), (300, 1, 136, 264), (64, 7, 256, 128), (16, 32, 384, 256), (9, 63, 128, 520),
+         (4096, 1, 128, 128)]
+
+
+@pytest.mark.parametrize("layout", ["out_in", "in_out"])
+@pytest.mark.parametrize("shape", SHORT)
+def test_wgrad_short_sequences_bf16(shape, layout):
+    B, T, n_in, n_out = shape
+    X, G, _ = O.make_linear_inputs(B, T, n_in, n_out, 1e-2, seed=sum(shape), dtype=torch.bfloat16)
+    G[0] *= 40.0
+    G[B // 2] *= 1e-2
+    check_wgrad(X, G, 0.05, 1.0, torch.bfloat16, layout=layout)
+
+
+@pytest.mark.parametrize("shape", [(512, 1, 64, 48), (40, 5, 72, 136), (6, 33, 264, 96), (3, 63, 40, 24)])
+def test_wgrad_short_sequences_fp32_and_direct_hint(shape):
+    B, T, n_in, n_out = shape
+    X, G, _ = O.make_linear_inputs(B, T, n_in, n_out, 1e-2, seed=sum(shape))
+    G[0] *= 40.0
+    _, n_gram = check_wgrad(X, G, 0.05, 1.0, torch.float32)
+    _, n_direct = check_wgrad(X, G, 0.05, 1.0, torch.float32, norm_algo="direct")
+    assert norm_err(n_gram.cpu().numpy(), n_direct.cpu().numpy()) < 1e-5
+
+
+def test_dplinear_2d_large_batch_bf16():
+    """2-D inputs (T = 1) with a batch large enough for the tensor-core clipped sum."""
+    import flashdp4review_b200 as fdp
+    B, n_in, n_out = 1024, 256, 128
+    X, G, W = O.make_linear_inputs(B, 1, n_in, n_out, 1e-1, seed=77, dtype=torch.bfloat16)
+    lin = fdp.DPLinear(n_in, n_out, C=0.3, noise_multiplier=0.0, dtype=torch.bfloat16).to(dev())
+    with torch.no_grad():
+        lin.weight.copy_(W)
+    x = X[:, 0].to(dev()).requires_grad_(True)
+    lin(x).backward(G[:, 0].to(dev()))
+    want, _ = O.linear_weight_grad(G, X, 0.3, 1.0)
+    want_b = O.linear_bias_grad(G, 0.3, 1.0)[0]
+    assert rel_err(lin.weight.grad.float().cpu().numpy(), want) < 1e-2
+    assert rel_err(lin.bias.grad.float().cpu().numpy(), want_b) < 1e-2
+    assert x.grad.shape == x.shape
