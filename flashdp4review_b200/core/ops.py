@@ -77,13 +77,15 @@ def _params(C, clamp_value, batch_divisor, noise):
 # weight gradient
 # ------------------------------------------------------------------------------------------------
 def dp_linear_weight_grad(input, grad_output, C, clamp_value, *, batch_divisor=None, noise=None,
-                          layout="out_in", out_dtype=None, norm_algo="auto", return_norms=False):
+                          layout="out_in", out_dtype=None, norm_algo="auto", return_norms=False, out=None):
     """Clipped, averaged, noised weight gradient of a Linear/Conv1D layer in one library call.
 
     input (B,T,in), grad_output (B,T,out).  Returns dW [out,in] (layout='out_in', nn.Linear) or
     [in,out] (layout='in_out', transformers Conv1D), and with return_norms the per-sample
     Frobenius norms and clip factors.  Computes
     (1/divisor) * sum_b min(clamp, C/(||G_b^T X_b||+1e-10)) * G_b^T X_b + N(0, noise.std^2).
+    `out`: a contiguous tensor of the result's shape to write into (e.g. a slice of a gradient
+    bucket) instead of a fresh allocation.
     """
     lib = _lib.load()
     _require_cuda(input, grad_output)
@@ -93,9 +95,14 @@ def dp_linear_weight_grad(input, grad_output, C, clamp_value, *, batch_divisor=N
     X = input.to(G.dtype).contiguous()     # the reference casts input to the grad dtype (linear_clip.py:111)
     B, T, n_in = X.shape
     n_out = G.shape[-1]
-    out_dtype = out_dtype or G.dtype
     shape = (n_out, n_in) if layout == "out_in" else (n_in, n_out)
-    dW = torch.empty(shape, dtype=out_dtype, device=G.device)
+    if out is not None:
+        if tuple(out.shape) != shape or not out.is_contiguous() or out.device != G.device:
+            raise RuntimeError(f"out must be a contiguous {shape} tensor on {G.device}")
+        dW, out_dtype = out, out.dtype
+    else:
+        out_dtype = out_dtype or G.dtype
+        dW = torch.empty(shape, dtype=out_dtype, device=G.device)
     norms = torch.empty(B, dtype=torch.float32, device=G.device) if return_norms else None
     factors = torch.empty(B, dtype=torch.float32, device=G.device) if return_norms else None
     algo = NORM_ALGOS[norm_algo]

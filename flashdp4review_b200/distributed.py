@@ -16,10 +16,24 @@ accumulates into the bucket in place, the all-reduce runs on the buffer itself a
 packed or unpacked.  With gradient accumulation (runtime.accumulate) pass `sync=False` to
 `finish()` on all but the last micro-step.
 """
+import weakref
+
 import torch
 import torch.distributed as dist
+from torch.utils.weak import WeakIdKeyDictionary
 
 from . import runtime
+
+
+# DP parameter -> weak reference to the reducer whose bucket slices it may be written into.  Kept
+# here rather than as an attribute of the parameter, so that parameters stay picklable.
+_direct = WeakIdKeyDictionary()     # keyed by identity: tensors do not compare with ==
+
+
+def direct_reducer(param):
+    """The live DPGradReducer offering bucket slices for `param`, or None."""
+    ref = _direct.get(param)
+    return ref() if ref is not None else None
 
 
 def init_data_parallel(group=None):
@@ -41,7 +55,7 @@ class DPGradReducer:
     """
 
     def __init__(self, module_or_params, group=None, bucket_bytes=64 << 20, overlap=True,
-                 grad_as_bucket_view=False):
+                 grad_as_bucket_view=False, direct_write=True):
         params = list(module_or_params.parameters()) if hasattr(module_or_params, "parameters") \
             else list(module_or_params)
         self.params = [p for p in params if p.requires_grad]
@@ -67,6 +81,7 @@ class DPGradReducer:
         self._inflight = {}
         self._hooks = []
         self._sync = True
+        self._claimed, self._counted = set(), set()
         self._flat, self._views = [], {}
         if self.as_view:
             for b in self.buckets:
@@ -77,6 +92,11 @@ class DPGradReducer:
                     off += p.numel()
                 self._flat.append(flat)
             self._attach_views()
+            if direct_write:
+                # DP layers may write a weight gradient straight into its bucket slice (claim_direct)
+                for p in self.params:
+                    if getattr(p, "requires_dp", False):
+                        _direct[p] = weakref.ref(self)
         if overlap and self.world > 1:
             for p in self.params:
                 self._hooks.append(p.register_post_accumulate_grad_hook(self._on_grad))
@@ -92,9 +112,28 @@ class DPGradReducer:
             for flat in self._flat:
                 flat.zero_()
             self._attach_views()
+            self._claimed.clear()
         else:
             for p in self.params:
                 p.grad = None
+
+    def claim_direct(self, p):
+        """The bucket slice of `p` if the coming gradient may overwrite it, else None: the first
+        gradient after zero_grad() (or after the gradient was set to None) overwrites, later ones
+        are returned to autograd, which adds them to the slice -- torch's accumulation semantics.
+        Assumes a DP weight takes part in one layer call per backward pass (build the reducer with
+        direct_write=False for a model that shares a DP weight between layers)."""
+        if not self.as_view or id(p) not in self._views:
+            return None
+        if id(p) in self._claimed and p.grad is not None:
+            return None
+        self._claimed.add(id(p))
+        p.grad = self._views[id(p)]
+        return p.grad
+
+    def direct_written(self, p):
+        if self._hooks:
+            self._on_grad(p)
 
     def set_sync(self, sync: bool):
         """sync=False: the coming backward is an accumulation micro-step -- gradients pile up
@@ -128,16 +167,20 @@ class DPGradReducer:
 
     def _attach_views_of(self, i):
         """Make every gradient of bucket i a view of its flat buffer; a gradient that autograd
-        allocated itself (after a zero_grad(set_to_none=True)) is copied in first."""
+        allocated itself (after a zero_grad(set_to_none=True)) is copied in first, a missing one
+        counts as zero."""
         for p in self.buckets[i]:
             v = self._views[id(p)]
-            if p.grad is not None and p.grad.data_ptr() != v.data_ptr():
+            if p.grad is None:
+                v.zero_()              # nothing arrived since the gradient was reset
+            elif p.grad.data_ptr() != v.data_ptr():
                 v.copy_(p.grad)
             p.grad = v
 
     def _on_grad(self, p):
-        if not self._sync:
+        if not self._sync or id(p) in self._counted:
             return
+        self._counted.add(id(p))
         i = self._bucket_of[id(p)]
         self._pending[i] -= 1
         if self._pending[i] == 0:
@@ -164,8 +207,12 @@ class DPGradReducer:
                     off += n
         self._inflight = {}
         self._pending = [len(b) for b in self.buckets]
+        self._counted.clear()
 
     def remove(self):
         for h in self._hooks:
             h.remove()
         self._hooks = []
+        for p in self.params:
+            if direct_reducer(p) is self:
+                del _direct[p]

@@ -1,6 +1,7 @@
 """Shared pieces of the DP layer backward passes."""
 from .. import runtime
 from ..core.ops import NoiseSpec, noise_std
+from ..distributed import direct_reducer
 
 
 class DPLayerMixin:
@@ -39,6 +40,23 @@ def dp_scalars(local_batch, noise_multiplier, param_id, step, param_id2=0):
     std = noise_std(noise_multiplier, global_batch) if micro_index == micro_steps - 1 else 0.0
     return global_batch, NoiseSpec(std=std, seed=runtime.get_seed(),
                                    param_id=param_id, param_id2=param_id2, step=step, rank=rank, world=world)
+
+
+def direct_grad_target(param):
+    """The bucket slice a DP weight gradient may be written into directly, or None.
+
+    A DPGradReducer built with grad_as_bucket_view=True offers the slice once per accumulation
+    cycle (the first gradient of the cycle overwrites it: no zero fill, no accumulate pass by
+    autograd); later gradients of the same cycle go the ordinary way and are added by autograd.
+    """
+    reducer = direct_reducer(param)
+    return reducer.claim_direct(param) if reducer is not None else None
+
+
+def direct_grad_done(param):
+    """Tell the reducer that the gradient written into the claimed slice is complete (queued on
+    the current stream), as autograd's post-accumulate hook would have."""
+    direct_reducer(param).direct_written(param)
 
 
 def autocast_dtype(*tensors):

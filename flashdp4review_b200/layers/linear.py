@@ -14,7 +14,8 @@ from .. import runtime
 from ..core import ops
 from ..core.ops import RuntimeAutoTuner
 from .utils import DPParameter as Parameter
-from ._common import DPLayerMixin, reshape_to_3d, dp_scalars, autocast_dtype
+from ._common import (DPLayerMixin, reshape_to_3d, dp_scalars, autocast_dtype, direct_grad_target,
+                      direct_grad_done)
 
 
 class _DPLinearFunc(Function):
@@ -52,11 +53,15 @@ class _DPLinearFunc(Function):
 
         if ctx.needs_input_grad[1]:
             div, noise = dp_scalars(B, layer.noise_multiplier, layer._dp_param_ids[0], step)
+            target = direct_grad_target(weight)      # a gradient-bucket slice, or None
             grad_weight = ops.dp_linear_weight_grad(
                 x3, g3, layer.C, layer.clamp_value, batch_divisor=div, noise=noise,
-                layout="out_in", out_dtype=weight.dtype, norm_algo=layer.norm_algo)
+                layout="out_in", out_dtype=weight.dtype, norm_algo=layer.norm_algo, out=target)
             if grad_weight.shape != weight.shape:
                 raise RuntimeError(f"grad_weight shape {grad_weight.shape} is not equal to weight shape {weight.shape}")
+            if target is not None:
+                direct_grad_done(weight)
+                grad_weight = None                    # already where the optimizer and the all-reduce read it
 
         if bias is not None and ctx.needs_input_grad[2]:
             div, noise = dp_scalars(B, layer.noise_multiplier, layer._dp_param_ids[1], step)

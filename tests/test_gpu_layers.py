@@ -256,3 +256,43 @@ def test_gradient_accumulation_equals_one_step_on_the_whole_batch():
     want = 2.0 / B ** 0.5
     assert abs(float(resid.std()) / want - 1.0) < 0.05 and abs(float(resid.mean())) < 4 * want / resid.numel() ** 0.5
     assert runtime.accumulation() == (0, 1)
+
+
+def test_weight_gradients_written_straight_into_the_bucket():
+    """With DPGradReducer(grad_as_bucket_view=True) the DP layers write dW into the bucket slice
+    (no autograd accumulate pass): same values as the ordinary route, p.grad is the slice, a second
+    backward of the same cycle is added by autograd, zero_grad() starts a new cycle."""
+    import flashdp4review_b200 as fdp
+    from flashdp4review_b200.distributed import DPGradReducer
+    torch.manual_seed(0)
+
+    def make():
+        torch.manual_seed(1)
+        return nn.Sequential(fdp.DPLinear(32, 48, C=0.3, noise_multiplier=0.0),
+                             fdp.DPConv1D(40, 48, C=0.3, noise_multiplier=0.0),
+                             fdp.DPLayerNorm(40, C=0.3, noise_multiplier=0.0)).to(dev())
+
+    x = torch.randn(4, 6, 32, device=dev())
+    g = torch.randn(4, 6, 40, device=dev()) * 0.1
+    plain = make()
+    plain(x).backward(g)
+    model = make()
+    red = DPGradReducer(model, bucket_bytes=1 << 12, grad_as_bucket_view=True)
+    model(x).backward(g)
+    red.finish()
+    for p, q in zip(model.parameters(), plain.parameters()):
+        assert p.grad.data_ptr() == red._views[id(p)].data_ptr()
+        assert torch.equal(p.grad, q.grad)
+    model(x).backward(g)                      # no zero_grad: accumulates like torch does
+    for p, q in zip(model.parameters(), plain.parameters()):
+        assert rel_err(p.grad.cpu().numpy(), 2 * q.grad.cpu().numpy()) < 1e-6
+    red.zero_grad()
+    model(x).backward(g)
+    for p, q in zip(model.parameters(), plain.parameters()):
+        assert torch.equal(p.grad, q.grad)
+    model.zero_grad(set_to_none=True)         # the optimizer's default: slices are claimed anew
+    model(x).backward(g)
+    red.finish()
+    for p, q in zip(model.parameters(), plain.parameters()):
+        assert torch.equal(p.grad, q.grad)
+    red.remove()
