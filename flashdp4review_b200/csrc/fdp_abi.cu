@@ -209,7 +209,7 @@ int fdp_linear_wgrad(const void* G, const void* X, void* dW, float* norms_out, f
 // ---- bias gradient ----------------------------------------------------------------------------------
 size_t fdp_bias_grad_workspace_bytes(int B, int T, int n_out, int in_dtype) {
   if (B <= 0 || T <= 0 || n_out <= 0 || !valid_dtype(in_dtype)) return 0;
-  const GstatsPlan pl = gstats_plan(T, n_out, in_dtype);
+  const GstatsPlan pl = gstats_plan(B, T, n_out, in_dtype);
   Carver c(nullptr);
   c.take<float>(B);                                                      // factors
   c.take<float>(static_cast<size_t>(B) * pl.row_chunks * pl.col_chunks); // sq partials
@@ -230,7 +230,7 @@ int fdp_bias_grad(const void* G, void* db, float* norms_out, float* factors_out,
   if (workspace == nullptr || !aligned16(workspace) ||
       workspace_bytes < fdp_bias_grad_workspace_bytes(B, T, n_out, in_dtype))
     return FDP_ERR_WORKSPACE;
-  const GstatsPlan pl = gstats_plan(T, n_out, in_dtype);
+  const GstatsPlan pl = gstats_plan(B, T, n_out, in_dtype);
   Carver c(workspace);
   float* factors = c.take<float>(B);
   float* sq_part = c.take<float>(static_cast<size_t>(B) * pl.row_chunks * pl.col_chunks);
@@ -315,11 +315,13 @@ int fdp_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* 
 
 size_t fdp_layernorm_bwd_workspace_bytes(int B, int T, int d) {
   if (B <= 0 || T <= 0 || d <= 0) return 0;
-  const LnPlan pl = ln_plan(T, d, FDP_F32);  // the chunk count does not depend on the dtype
+  // the query has no dtype: take the larger chunk count of the 32-bit and the 16-bit plan
+  const int c32 = ln_plan(B, T, d, FDP_F32).chunks, c16 = ln_plan(B, T, d, FDP_BF16).chunks;
+  const int chunks = c32 > c16 ? c32 : c16;
   Carver c(nullptr);
   c.take<float>(static_cast<size_t>(2) * B * ln_sumsq_parts(d)); // partial sums of squares
   c.take<float>(2 * B);                                          // factors
-  c.take<float>(static_cast<size_t>(2) * B * pl.chunks * d);     // partials, both tensors
+  c.take<float>(static_cast<size_t>(2) * B * chunks * d);        // partials, both tensors
   return c.off;
 }
 
@@ -339,7 +341,7 @@ int fdp_layernorm_bwd(const void* dy, const void* x, const void* gamma, const fl
   if (workspace == nullptr || !aligned16(workspace) ||
       workspace_bytes < fdp_layernorm_bwd_workspace_bytes(B, T, d))
     return FDP_ERR_WORKSPACE;
-  const LnPlan pl = ln_plan(T, d, dtype);
+  const LnPlan pl = ln_plan(B, T, d, dtype);
   Carver c(workspace);
   float* sumsq = c.take<float>(static_cast<size_t>(2) * B * ln_sumsq_parts(d));
   float* factors = c.take<float>(2 * B);

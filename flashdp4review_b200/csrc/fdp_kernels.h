@@ -36,7 +36,7 @@ void simt_fwd(const void* X, const void* W, const void* bias, void* Y, int rows,
 
 // ---- bias gradient (HBM-bound; G read once) ----------------------------------------------------
 struct GstatsPlan { int vec, cols_per_block, col_chunks, rows_per_chunk, row_chunks; };
-GstatsPlan gstats_plan(int T, int n_out, int dt);
+GstatsPlan gstats_plan(int B, int T, int n_out, int dt);
 void gstats(const void* G, float* colsum_part, float* sq_part, int B, int T, int n_out, int dt,
             const GstatsPlan& pl, cudaStream_t s);
 void bias_finalize(const float* colsum_part, const float* factors, void* db, int B, int n_out,
@@ -48,7 +48,7 @@ void bias_clip_finalize(const float* colsum_part, const float* sq_part, int npar
 
 // ---- LayerNorm -----------------------------------------------------------------------------------
 struct LnPlan { int tpr, cpt, cw, rows_per_block, chunks; bool vec; };
-LnPlan ln_plan(int T, int d, int dt);
+LnPlan ln_plan(int B, int T, int d, int dt);
 void ln_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean, float* rstd,
             int rows, int d, float eps, int dt, int pdt, cudaStream_t s);
 void ln_bwd(const void* dy, const void* x, const void* gamma, const float* mean, const float* rstd,

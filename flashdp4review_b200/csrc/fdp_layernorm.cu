@@ -103,7 +103,7 @@ __global__ void __launch_bounds__(128) ln_fwd_kernel(const Tin* __restrict__ x,
 // async copies (several groups in flight per SM, so HBM latency is covered whatever the occupancy);
 // eight consumer warps take one row each, reduce mean and variance out of shared memory and write y.
 constexpr int LN_MAX_STAGES = 8;
-constexpr int LN_MAX_ROWS_PER_BLOCK = 64;
+constexpr int LN_MAX_ROWS_PER_BLOCK = 256;
 constexpr size_t LN_SMEM_BUDGET = 192 * 1024;
 // NV > 0: a lane keeps its NV vectors of the row, gamma and beta in registers (d <= 32*VEC*NV), so the
 // row is read from shared memory once; NV = 0: generic three-pass loop for longer rows.
@@ -568,7 +568,7 @@ __global__ void __launch_bounds__(STAGED ? CW + 32 : CW) ln_bwd_kernel(
   }
 }
 
-LnPlan ln_plan(int T, int d, int dt) {
+LnPlan ln_plan(int B, int T, int d, int dt) {
   LnPlan pl;
   const int V = 16 / static_cast<int>(dtype_size(dt));
   pl.vec = (d % V == 0);
@@ -581,8 +581,22 @@ LnPlan ln_plan(int T, int d, int dt) {
   pl.cpt = nv_max * vec;
   pl.tpr = 32;
   while (pl.tpr < 256 && pl.tpr * pl.cpt < d) pl.tpr *= 2;
-  // partials are [B, chunks, d], one chunk = 64 rows of one sample
-  pl.rows_per_block = 64;
+  // Partials are [B, chunks, d]; one chunk = rows_per_block rows of one sample = one block.  The
+  // backward kernel holds one block per SM, so B * chunks blocks run in whole waves of LN_SMS: pick
+  // the chunk length that minimises waves * (rows + fixed cost per block); ties go to the longer
+  // chunk (fewer partials).  The count must not depend on the device in use -- the workspace
+  // query has to agree with the launch -- hence the constant.
+  constexpr int LN_SMS = 148, BLOCK_FIXED_ROWS = 6;
+  const int rg = pl.cw / pl.tpr;   // rows a block works on at a time
+  int best_r = 64, best_cost = 1 << 30;
+  for (int r = 32; r <= LN_MAX_ROWS_PER_BLOCK; r += 8) {
+    if (r % rg != 0) continue;
+    const long long blocks = static_cast<long long>(B) * ceil_div(T, r);
+    const long long waves = (blocks + LN_SMS - 1) / LN_SMS;
+    const long long cost = waves * (r + BLOCK_FIXED_ROWS);
+    if (cost <= best_cost) { best_cost = static_cast<int>(cost < (1 << 30) ? cost : (1 << 30) - 1); best_r = r; }
+  }
+  pl.rows_per_block = best_r;
   pl.chunks = ceil_div(T, pl.rows_per_block);
   return pl;
 }

@@ -393,12 +393,16 @@ __global__ void __launch_bounds__(256) gstats_kernel(const Tin* __restrict__ G,
   }
 }
 
-GstatsPlan gstats_plan(int T, int n_out, int dt) {
+GstatsPlan gstats_plan(int B, int T, int n_out, int dt) {
   GstatsPlan pl;
   pl.vec = (dt == FDP_F32) ? 4 : 8;
   pl.cols_per_block = 32 * pl.vec;
   pl.col_chunks = ceil_div(n_out, pl.cols_per_block);
-  pl.rows_per_chunk = 128;  // 16 rows per thread: few partials, still thousands of blocks at LLM sizes
+  // 256 rows per block (32 per thread) when that still leaves four blocks for each of the 148 SMs:
+  // half the partials and a shorter finalisation (27.6 us against 30.8 us per call at B=16, T=1024,
+  // 3072 columns); otherwise 128 rows, which keeps the grid large at small batch sizes
+  pl.rows_per_chunk = 256;
+  if (static_cast<long long>(B) * pl.col_chunks * ceil_div(T, 256) < 4 * 148) pl.rows_per_chunk = 128;
   pl.row_chunks = ceil_div(T, pl.rows_per_chunk);
   return pl;
 }

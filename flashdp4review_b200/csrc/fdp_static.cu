@@ -76,7 +76,7 @@ extern "C" int fdp_bias_grad_static(const void* G, void* db, float* norms_out, f
   const int st = static_scratch(&scratch);
   if (st != FDP_OK) return st;
 
-  const GstatsPlan pl = gstats_plan(T, n_out, in_dtype);
+  const GstatsPlan pl = gstats_plan(B, T, n_out, in_dtype);
   Carver c(scratch);
   float* factors = c.take<float>(B);
   float* sq_part = c.take<float>(static_cast<size_t>(B) * pl.row_chunks * pl.col_chunks);
