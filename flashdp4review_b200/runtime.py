@@ -8,9 +8,7 @@ its share of the noise before the all-reduce of the clipped sums.
 import contextlib
 import itertools
 import os
-import threading
 
-_state = threading.local()
 _ids = itertools.count(1)
 
 

@@ -99,3 +99,23 @@ def test_conv1d_twin_and_constructor_attributes():
     assert lin.dp and lin.runtime_tuner.enable is False and lin.weight.requires_dp
     ln = fdp.DPLayerNorm(6, use_fused=False, bias=None)
     assert ln.bias is None and ln.use_fused is False
+
+
+def test_workspace_queries_are_pure_host_functions():
+    """The *_workspace_bytes queries run without a GPU, reject nonsense with 0 and grow with the
+    problem; every plan the launch would pick (tensor-core, short-sequence, generic) fits them."""
+    from flashdp4review_b200 import _lib
+    lib = _lib.load()
+    q = lib.fdp_linear_wgrad_workspace_bytes
+    assert q(0, 128, 256, 256, _lib.FDP_BF16, 0) == 0 and q(4, 128, 256, 256, 7, 0) == 0
+    sizes = [q(B, T, 256, 384, dt, 0) for dt in (_lib.FDP_F32, _lib.FDP_BF16)
+             for (B, T) in ((2, 7), (512, 1), (4, 128), (32, 1024))]
+    assert all(s > 0 and s % 256 == 0 for s in sizes)
+    assert q(64, 1024, 256, 384, _lib.FDP_BF16, 0) >= q(32, 1024, 256, 384, _lib.FDP_BF16, 0)
+    b = lib.fdp_bias_grad_workspace_bytes
+    assert b(0, 1, 1, _lib.FDP_F32) == 0
+    assert 0 < b(4, 128, 768, _lib.FDP_F32) <= b(8, 128, 768, _lib.FDP_F32) <= b(8, 4096, 768, _lib.FDP_F32)
+    ln = lib.fdp_layernorm_bwd_workspace_bytes
+    assert ln(0, 1, 1) == 0
+    assert 0 < ln(4, 9, 40) <= ln(16, 1024, 1024) <= ln(32, 1024, 4096)
+    assert lib.fdp_linear_dgrad_workspace_bytes(4096, 256, 384, _lib.FDP_BF16) >= 0
