@@ -85,11 +85,15 @@ class DPGradReducer:
         self._flat, self._views = [], {}
         if self.as_view:
             for b in self.buckets:
-                flat = torch.zeros(sum(p.numel() for p in b), dtype=b[0].dtype, device=b[0].device)
-                off = 0
+                # every slice starts on a 64-byte boundary (the kernels want 16-byte-aligned outputs)
+                quantum = 64 // b[0].element_size()
+                starts, off = [], 0
                 for p in b:
-                    self._views[id(p)] = flat[off:off + p.numel()].view_as(p)
-                    off += p.numel()
+                    starts.append(off)
+                    off += (p.numel() + quantum - 1) // quantum * quantum
+                flat = torch.zeros(off, dtype=b[0].dtype, device=b[0].device)
+                for p, st in zip(b, starts):
+                    self._views[id(p)] = flat[st:st + p.numel()].view_as(p)
                 self._flat.append(flat)
             self._attach_views()
             if direct_write:

@@ -32,7 +32,7 @@ def _worker(rank, world, port, overlap, as_view, results):
         assert (noise.rank, noise.world, noise.param_id, noise.step) == (rank, world, 7, 3)
 
         torch.manual_seed(0)
-        model = nn.Sequential(nn.Linear(6, 5), nn.Linear(5, 3))
+        model = nn.Sequential(nn.Linear(6, 5), nn.Linear(5, 3))      # odd sizes: bucket slices need padding
         model[0].weight = DPParameter(model[0].weight.data)       # DP tensor: SUM
         model[0].bias = DPParameter(model[0].bias.data)
         twin = copy.deepcopy(model)          # same weights, no reducer: yields the local gradients
@@ -57,6 +57,7 @@ def _worker(rank, world, port, overlap, as_view, results):
                 assert torch.allclose(p.grad, want, rtol=1e-6, atol=1e-6)
             if as_view:
                 assert all(p.grad.data_ptr() == red._views[id(p)].data_ptr() for p in model.parameters())
+                assert all(p.grad.data_ptr() % 64 == 0 for p in model.parameters())
 
         # gradient accumulation: two micro-steps, one collective after the second
         from flashdp4review_b200 import runtime

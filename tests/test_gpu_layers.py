@@ -268,8 +268,8 @@ def test_weight_gradients_written_straight_into_the_bucket():
 
     def make():
         torch.manual_seed(1)
-        return nn.Sequential(fdp.DPLinear(32, 48, C=0.3, noise_multiplier=0.0),
-                             fdp.DPConv1D(40, 48, C=0.3, noise_multiplier=0.0),
+        return nn.Sequential(fdp.DPLinear(32, 50, C=0.3, noise_multiplier=0.0),    # 50: slices need padding
+                             fdp.DPConv1D(40, 50, C=0.3, noise_multiplier=0.0),
                              fdp.DPLayerNorm(40, C=0.3, noise_multiplier=0.0)).to(dev())
 
     x = torch.randn(4, 6, 32, device=dev())
