@@ -38,7 +38,7 @@ constexpr int threads_for(int epi) { return epi == EPI_STORE_SCALED ? 320 : 192;
 
 struct TcArgs {
   int M, N;             // extents of the output space of one batch (masks)
-  int tiles_m, tiles_n; // tile grid of one batch (EPI_GRAM: tiles_m = t-blocks of 128, tiles_n = s-blocks of 256)
+  int tiles_m, tiles_n; // tile grid of one batch
   int tiles_per_batch;
   int n_fastest;        // tile order: 1 = consecutive tiles walk along N (keeps the B operand in L2), 0 = along M
   int batch;
@@ -56,11 +56,12 @@ struct TcArgs {
   // EPI_STORE_SCALED: K is `segs` segments (samples) of `seg_stages` stages; factors[seg] scales each
   const float* factors;
   int segs, seg_stages;
-  // EPI_GRAM: per sample `gram_full` tiles need all 256 s-columns and `gram_half` tiles (the t-block is
-  // the lower half of the s-block) only columns 128..255, done with an N = 128 MMA (idesc_half).
-  // Tiles are numbered sample by sample: the sample's full tiles, then its half tiles.  A work unit is
-  // one full tile or two half tiles, so all units cost the same and round-robin dealing is balanced.
-  int gram_full, gram_half;
+  // EPI_GRAM: the T x T plane of a sample is cut into 128 x 128 blocks; only blocks (i, j) with j >= i
+  // are computed (weight 2, the diagonal ones weight 1).  A work unit is one t-block i against TWO
+  // s-blocks j1, j2 (an N = 256 MMA whose B stage is filled by two 128-row copies), see gram_decode;
+  // at most one unit per sample has a single block (N = 128, idesc_half).  Units are numbered sample
+  // by sample and all cost the same, so round-robin dealing is balanced.
+  int gram_nb;          // 128-row blocks per sample
   uint32_t idesc_half;
   // store epilogue: optional bias[N] (same 16-bit type as the operands) added to every row
   const void* bias; int bias_dt;
@@ -211,6 +212,48 @@ __device__ __forceinline__ void store_chunk32(const TcArgs& args, float v[32], i
   }
 }
 
+// ---- Gram work units -----------------------------------------------------------------------------------
+// Row i of the upper block triangle holds blocks (i, i..nb-1).  Rows with an odd block count (every
+// second row) are paired (a, a+2): block (a, a+2) is computed as its mirror image (a+2, a) in row a+2
+// instead -- the summand (G G^T)(X X^T) is symmetric -- so both rows end up with an even count and
+// every unit is a pair of blocks of one row.  Only when the number of odd rows is odd does one row keep
+// a single-block unit.  Unit u of a sample -> t-block i and s-blocks j1, j2 (j2 = -1: single block).
+__host__ __device__ inline int gram_row_len(int nb, int i, int& role) {
+  const int p = (nb - 1) & 1;      // odd rows are i = p, p+2, ...
+  int len = nb - i;
+  role = 0;                        // 0: untouched row, 1: gives block (i, i+2) away, 2: receives (i, i-2)
+  if (i >= p && ((i - p) & 1) == 0) {
+    const int m = (i - p) >> 1;
+    if (m & 1) { role = 2; len += 1; }
+    else if (i + 2 < nb) { role = 1; len -= 1; }
+  }
+  return len;
+}
+__host__ __device__ inline int gram_col(int i, int role, int e) {
+  if (role == 2) return e == 0 ? i - 2 : i + e - 1;
+  if (role == 1) return e >= 2 ? i + e + 1 : i + e;
+  return i + e;
+}
+__host__ __device__ inline int gram_units(int nb) {
+  int n = 0, role;
+  for (int i = 0; i < nb; ++i) n += (gram_row_len(nb, i, role) + 1) >> 1;
+  return n;
+}
+__host__ __device__ inline void gram_decode(int nb, int u, int& i, int& j1, int& j2) {
+  int role;
+  for (i = 0; i < nb; ++i) {
+    const int len = gram_row_len(nb, i, role);
+    const int n = (len + 1) >> 1;
+    if (u < n) {
+      j1 = gram_col(i, role, 2 * u);
+      j2 = (2 * u + 1 < len) ? gram_col(i, role, 2 * u + 1) : -1;
+      return;
+    }
+    u -= n;
+  }
+  i = j1 = 0; j2 = -1;   // not reached for u < gram_units(nb)
+}
+
 // accr[4g .. 4g+3] += z * f with g known only at run time: a switch keeps every index static, so
 // the 128 accumulators stay in registers.
 __device__ __forceinline__ void add_group(float (&accr)[128], int g, const float z[4], float f) {
@@ -266,7 +309,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int total_tiles = args.batch * args.tiles_per_batch;
   const int kst_total = args.k_stages + (EPI == EPI_GRAM ? args.k_stages2 : 0);
   const int total_units = (EPI == EPI_GRAM)
-      ? args.batch * (args.gram_full + (args.gram_half + 1) / 2)
+      ? args.batch * args.tiles_per_batch
       : args.units_full + (total_tiles - args.units_full) * args.split;
 
   if (threadIdx.x == 0) {
@@ -299,25 +342,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int wid = blockIdx.x / CTAS, wstep = gridDim.x / CTAS;
   const uint32_t tmem_base = *tmem_slot;
 
-  // tile -> (batch, m0, n0, half).  EPI_GRAM: per sample the full (t-block, s-block) pairs with
-  // t-block <= 2*s-block, then the half tiles t-block = 2*s-block + 1
+  // tile -> (batch, m0, n0, half).  EPI_GRAM: m0 = first row of the t-block, n0 / n1 = first rows of
+  // the two s-blocks (n1 < 0 and half = 1 for a single-block unit)
+  int gram_n1 = -1;
   auto decode = [&](int tile, int& b, int& m0, int& n0, int& half) {
     half = 0;
     b = tile / args.tiles_per_batch;
     int q = tile - b * args.tiles_per_batch;
     if (EPI == EPI_GRAM) {
-      if (q < args.gram_full) {
-        int j = 0;
-        while (true) {
-          const int cnt = min(2 * j + 1, args.tiles_m);
-          if (q < cnt) break;
-          q -= cnt; ++j;
-        }
-        m0 = q * BM; n0 = j * BN;
-      } else {
-        const int j = q - args.gram_full;
-        m0 = (2 * j + 1) * BM; n0 = j * BN; half = 1;
-      }
+      int i, j1, j2;
+      gram_decode(args.gram_nb, q, i, j1, j2);
+      m0 = i * BM; n0 = j1 * BM;
+      gram_n1 = j2 >= 0 ? j2 * BM : -1;
+      half = j2 < 0;
       return;
     }
     int mi, ni;
@@ -334,15 +371,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     m0 = mi * (BM * CTAS) + cta_rank * BM;
     n0 = ni * BN;
   };
-  // EPI_GRAM: unit u -> its sub-tile `sub` (of nsub) in the sample-by-sample tile numbering
-  const int gram_ups = args.gram_full + (args.gram_half + 1) / 2;   // units per sample
-  auto gram_unit = [&](int u, int sub, int& nsub, int& tile) {
-    const int b = u / gram_ups, lu = u - b * gram_ups;
-    if (lu < args.gram_full) { nsub = 1; tile = b * args.tiles_per_batch + lu; return; }
-    const int h0 = 2 * (lu - args.gram_full);
-    nsub = min(2, args.gram_half - h0);
-    tile = b * args.tiles_per_batch + args.gram_full + h0 + sub;
-  };
+  // EPI_GRAM: a unit is one tile
+  auto gram_unit = [&](int u, int sub, int& nsub, int& tile) { (void)sub; nsub = 1; tile = u; };
 
   // work unit -> tile, K-stage range, slot in split_ws (-1: whole tile, normal epilogue)
   auto decode_unit = [&](int u, int& tile, int& ks0, int& ks1, int& slot) {
@@ -381,7 +411,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const CUtensorMap* mb = second ? &tmB2 : &tmB;
           const int k0 = (second ? ks - args.k_stages : ks) * BK;
           const uint32_t sa = base + stage * STG, sb = sa + A_STAGE_BYTES;
-          if (CTAS == 1) {
+          if (EPI == EPI_GRAM) {
+            // A: the t-block; B: two independent 128-row s-blocks, one per half of the stage
+            constexpr uint32_t HALF_B = B_STAGE_BYTES / 2;
+            mbar_expect_tx(full_bar(stage), A_STAGE_BYTES + (gram_n1 >= 0 ? 2 : 1) * HALF_B);
+            tma_load_2d(sa, ma, k0, row0 + m0, full_bar(stage));
+            tma_load_2d(sb, mb, k0, row0 + n0, full_bar(stage));
+            if (gram_n1 >= 0) tma_load_2d(sb + HALF_B, mb, k0, row0 + gram_n1, full_bar(stage));
+          } else if (CTAS == 1) {
             mbar_expect_tx(full_bar(stage), STG);
             if (A_MN) {
 #pragma unroll
@@ -439,9 +476,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         if (EPI == EPI_GRAM) { gram_unit(u, sub, nsub, tile); ks0 = 0; ks1 = kst_total; slot = -1; }
         else decode_unit(u, tile, ks0, ks1, slot);
         decode(tile, tb, tm0, tn0, half);
-        // a half tile multiplies by the upper 128 rows of the B stage only (N = 128)
+        // a single-block unit multiplies by the first 128 rows of the B stage only (N = 128)
         const uint32_t idesc = half ? args.idesc_half : args.idesc;
-        const uint32_t b_off = half ? 128u * 128u : 0u;
+        const uint32_t b_off = 0u;
         int ks = ks0;
         // one accumulator per segment: the whole unit, or one sample for EPI_STORE_SCALED
         while (ks < ks1 && ok) {
@@ -612,21 +649,24 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           for (int j = 0; j < 32; ++j) { const float f = __uint_as_float(r[j]); part = fmaf(f, f, part); }
         }
       } else {
-        // weight 2 above the diagonal, 1 on it, 0 below it and outside the sample
+        // columns 0..127 belong to s-block n0, 128..255 to s-block gram_n1; a diagonal block counts
+        // once, any other block twice (it stands for its mirror image too); rows and columns past the
+        // end of the sample (they belong to the next one) count nothing
         const int t = m0 + row;
-        const int ncols = half ? BN / 2 : BN;       // a half tile holds s-columns 128..255 in columns 0..127
-        const int s_base = n0 + (half ? BN / 2 : 0);
+        const int ncols = half ? BN / 2 : BN;
 #pragma unroll 1
         for (int c = 0; c < ncols; c += 32) {
           uint32_t p[32], q[32];
           tc_ld32(tbase + c, p);
           tc_ld32(tbase + BN + c, q);
           tc_wait_ld();
+          const int sb0 = (c < BN / 2) ? n0 : gram_n1;          // first row of this chunk's s-block
+          const int s0 = sb0 + (c & (BN / 2 - 1));
+          const float wblk = (sb0 == m0) ? 1.f : 2.f;
           if (t < args.T) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
-              const int sidx = s_base + c + j;
-              const float w = (sidx >= args.T || sidx < t) ? 0.f : (sidx == t ? 1.f : 2.f);
+              const float w = (s0 + j < args.T) ? wblk : 0.f;
               part = fmaf(w * __uint_as_float(p[j]), __uint_as_float(q[j]), part);
             }
           }
@@ -808,7 +848,6 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, co
   const int total = la.batch * la.tiles_per_batch;
   if (la.split <= 1) { la.split = 1; la.units_full = total; }
   int units = la.units_full + (total - la.units_full) * la.split;
-  if (EPI == EPI_GRAM) units = la.batch * (la.gram_full + (la.gram_half + 1) / 2);
   const int workers = sm_count() / CTAS;   // CTAs, or CTA pairs
   const int grid = CTAS * (units < workers ? units : workers);
   if (CTAS == 1) {
@@ -866,12 +905,7 @@ int plan_tail_split(int total_tiles, int k_stages, int sms) {
 size_t split_ws_bytes() { return static_cast<size_t>(2) * sm_count() * BM * BN * sizeof(float); }
 size_t align256(size_t n) { return (n + 255) & ~static_cast<size_t>(255); }
 
-int gram_tiles(int T) {
-  const int tm = ceil_div(T, BM), tn = ceil_div(T, BN);
-  int n = 0;
-  for (int j = 0; j < tn; ++j) n += (2 * j + 2 < tm) ? 2 * j + 2 : tm;
-  return n;
-}
+int gram_tiles(int T) { return gram_units(ceil_div(T, BM)); }   // work units (128 x 256 tiles) per sample
 
 }  // namespace
 
@@ -927,15 +961,14 @@ int tc_norms(const void* G, const void* X, float* partials, int* dev_status, int
     args.idesc = make_idesc(dt, true, true);
     return launch<true, true, EPI_SUMSQ>(a, b, a, b, args, s);
   }
-  if (!make_map(&a, G, rows, n_out, BK, BM, dt) || !make_map(&b, G, rows, n_out, BK, BN, dt) ||
-      !make_map(&a2, X, rows, n_in, BK, BM, dt) || !make_map(&b2, X, rows, n_in, BK, BN, dt))
+  // A and B boxes are both 128 rows: a B stage is filled by two independent copies
+  if (!make_map(&a, G, rows, n_out, BK, BM, dt) || !make_map(&b, G, rows, n_out, BK, BN / 2, dt) ||
+      !make_map(&a2, X, rows, n_in, BK, BM, dt) || !make_map(&b2, X, rows, n_in, BK, BN / 2, dt))
     return FDP_ERR_LAUNCH;
   args.M = T; args.N = T;
-  args.tiles_m = ceil_div(T, BM); args.tiles_n = ceil_div(T, BN);
+  args.gram_nb = ceil_div(T, BM);
+  args.tiles_m = args.gram_nb; args.tiles_n = args.gram_nb;
   args.tiles_per_batch = gram_tiles(T);
-  args.gram_half = 0;
-  for (int j = 0; j < args.tiles_n; ++j) args.gram_half += (2 * j + 1 < args.tiles_m) ? 1 : 0;
-  args.gram_full = args.tiles_per_batch - args.gram_half;
   args.idesc_half = make_idesc(dt, false, false, 1, BN / 2);
   args.k_stages = ceil_div(n_out, BK); args.k_stages2 = ceil_div(n_in, BK);
   args.idesc = make_idesc(dt, false, false);
