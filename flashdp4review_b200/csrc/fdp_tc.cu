@@ -413,9 +413,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const uint32_t sa = base + stage * STG, sb = sa + A_STAGE_BYTES;
           if (EPI == EPI_GRAM) {
             // A: the t-block; B: two independent 128-row s-blocks, one per half of the stage
+            // (a unit that contains the diagonal block (i, i) has its t-block in the B stage already:
+            // the MMA warp points the A descriptor there and no A copy is made)
             constexpr uint32_t HALF_B = B_STAGE_BYTES / 2;
-            mbar_expect_tx(full_bar(stage), A_STAGE_BYTES + (gram_n1 >= 0 ? 2 : 1) * HALF_B);
-            tma_load_2d(sa, ma, k0, row0 + m0, full_bar(stage));
+            const bool a_in_b = (n0 == m0) || (gram_n1 == m0);
+            mbar_expect_tx(full_bar(stage), (a_in_b ? 0 : A_STAGE_BYTES) + (gram_n1 >= 0 ? 2 : 1) * HALF_B);
+            if (!a_in_b) tma_load_2d(sa, ma, k0, row0 + m0, full_bar(stage));
             tma_load_2d(sb, mb, k0, row0 + n0, full_bar(stage));
             if (gram_n1 >= 0) tma_load_2d(sb + HALF_B, mb, k0, row0 + gram_n1, full_bar(stage));
           } else if (CTAS == 1) {
@@ -494,7 +497,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const bool second = (EPI == EPI_GRAM) && ks >= args.k_stages;
             const uint32_t d = tmem_base + (EPI == EPI_GRAM ? (second ? BN : 0) : acc * BN);
             const bool first_stage = second ? (ks == args.k_stages) : (ks == seg_begin);
-            const uint32_t sa = base + stage * STG, sb = sa + A_STAGE_BYTES;
+            uint32_t sa = base + stage * STG;
+            const uint32_t sb = sa + A_STAGE_BYTES;
+            if (EPI == EPI_GRAM) {   // diagonal block in this unit: A is the matching half of the B stage
+              if (tn0 == tm0) sa = sb;
+              else if (gram_n1 == tm0) sa = sb + B_STAGE_BYTES / 2;
+            }
 #pragma unroll
             for (int k16 = 0; k16 < BK / UMMA_K; ++k16) {
               if (CTAS == 1)
