@@ -491,7 +491,7 @@ def run_gpt2(args):
     lib = _lib.load()
     fdp.manual_seed(1234)
     fdp.set_data_parallel(rank, world)
-    fdp.set_input_grad_impl("native")
+    fdp.set_input_grad_impl(args.gemm_impl)
     micro_batch, seq = args.micro_batch, 1024
     cfg = GPT2Config(n_layer=args.layers, n_embd=1024, n_head=16, n_positions=1024, vocab_size=50257,
                      resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
@@ -568,7 +568,7 @@ def run_gpt2(args):
                 "data": "synthetic",
                 "config": {"workload": args.workload, "layers": args.layers, "d_model": 1024, "heads": 16,
                            "seq_len": seq, "micro_batch_per_gpu": micro_batch, "global_batch": micro_batch * world,
-                           "dp_wrapped": not args.no_dp, "optimizer": "Adam lr 1e-4 (fused)", "C": 1.0,
+                           "dp_wrapped": not args.no_dp, "gemm_impl": args.gemm_impl, "optimizer": "Adam lr 1e-4 (fused)", "C": 1.0,
                            "noise_multiplier": 1.0, "parallelism": f"dp{world}",
                            "l2": "activations and weights (GBs) far larger than the 126 MB L2"},
                 "e2e": {"value": world * micro_batch * seq / (e2e_ms * 1e-3), "unit": "tokens/s",
@@ -589,6 +589,8 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + ["gpt2_medium", "hbm_kernels_bf16_b16_t1024"])
     ap.add_argument("--layers", type=int, default=24, help="gpt2_medium: number of transformer blocks")
     ap.add_argument("--micro-batch", type=int, default=8, help="gpt2_medium: samples per GPU and step")
+    ap.add_argument("--gemm-impl", default="native", choices=["native", "library"],
+                    help="gpt2_medium: forward / input-gradient GEMMs of the DP layers by this library or by cuBLAS")
     ap.add_argument("--no-dp", action="store_true", help="gpt2_medium: leave the model unwrapped (context only)")
     ap.add_argument("--norm-algo", default="auto", choices=["auto", "direct", "gram"])
     ap.add_argument("--sigma", type=float, default=1.0, help="noise_multiplier of the DP-Linear workloads")
