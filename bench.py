@@ -38,7 +38,7 @@ DEFAULT_WORKLOAD = "linear_bf16_b32_t1024_4096x4096"
 METRIC, UNIT = "dp_linear_bwd_tflops", "TFLOP/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one clipped-sum GEMM launch (ncu capture summarised
 # in profiles/tc_gemm_kernels_bf16_b32_t1024_4096x4096_ncu_full.md)
-TRAFFIC = {"linear_bf16_b32_t1024_4096x4096": 1.687e9}
+TRAFFIC = {"linear_bf16_b32_t1024_4096x4096": 1.579e9}
 
 
 def peaks():
