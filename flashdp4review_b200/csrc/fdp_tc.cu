@@ -934,9 +934,16 @@ TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo) {
     return p;
   }
   const bool direct_ok = (T % BK == 0);   // a K stage must not run into the next sample's rows
-  // tensor-core work of the two norm algorithms, in padded tile units
-  const double direct = 2.0 * T * (ceil_div(n_out, BM) * BM) * static_cast<double>(ceil_div(n_in, BN) * BN);
-  const double gram = 2.0 * gram_tiles(T) * BM * BN * (static_cast<double>(ceil_div(n_in, BK) + ceil_div(n_out, BK)) * BK);
+  // Cost of the two norm algorithms in K stages on the critical path: both kernels deal equal work
+  // units (128x256 tiles) round-robin to one CTA per SM, so a pass takes
+  // ceil(units / SMs) * (stages per unit + a fixed cost per unit of about four stages).  The SM
+  // count is a constant here: the workspace query and the launch must pick the same algorithm.
+  constexpr long long PLAN_SMS = 148, UNIT_FIXED_STAGES = 4;
+  const long long units_d = static_cast<long long>(B) * ceil_div(n_out, BM) * ceil_div(n_in, BN);
+  const long long units_g = static_cast<long long>(B) * gram_tiles(T);
+  const double direct = static_cast<double>((units_d + PLAN_SMS - 1) / PLAN_SMS) * (ceil_div(T, BK) + UNIT_FIXED_STAGES);
+  const double gram = static_cast<double>((units_g + PLAN_SMS - 1) / PLAN_SMS) *
+                      (ceil_div(n_in, BK) + ceil_div(n_out, BK) + UNIT_FIXED_STAGES);
   int algo = norm_algo;
   if (algo == FDP_NORM_AUTO) algo = (direct_ok && direct <= gram) ? FDP_NORM_DIRECT : FDP_NORM_GRAM;
   if (algo == FDP_NORM_DIRECT && !direct_ok) algo = FDP_NORM_GRAM;
