@@ -119,3 +119,46 @@ def test_workspace_queries_are_pure_host_functions():
     assert ln(0, 1, 1) == 0
     assert 0 < ln(4, 9, 40) <= ln(16, 1024, 1024) <= ln(32, 1024, 4096)
     assert lib.fdp_linear_dgrad_workspace_bytes(4096, 256, 384, _lib.FDP_BF16) >= 0
+
+
+def test_gram_work_units_cover_the_block_triangle_once(tmp_path):
+    """The Gram norm pass deals units of (t-block, two s-blocks); compiled for the host, the
+    enumeration must cover every unordered block pair exactly once, with at most one single-block
+    unit per sample, for every block count."""
+    import shutil
+    import subprocess
+    gxx = shutil.which("g++")
+    if gxx is None:
+        pytest.skip("no host C++ compiler")
+    hdr = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))),
+                       "flashdp4review_b200", "csrc", "fdp_gram_units.h")
+    src = tmp_path / "units.cpp"
+    src.write_text('#include <cstdio>\n#include <set>\n#include <utility>\n#include "%s"\n' % hdr + r'''
+int main() {
+  for (int nb = 1; nb <= 160; ++nb) {
+    std::set<std::pair<int, int>> seen;
+    const int units = fdp::gram_units(nb);
+    int singles = 0;
+    for (int u = 0; u < units; ++u) {
+      int i, j1, j2;
+      fdp::gram_decode(nb, u, i, j1, j2);
+      if (i < 0 || i >= nb || j1 < 0 || j1 >= nb || j2 >= nb) { std::printf("range nb=%d u=%d\n", nb, u); return 1; }
+      if (j2 < 0) ++singles;
+      const int js[2] = {j1, j2};
+      for (int k = 0; k < 2; ++k) {
+        if (js[k] < 0) continue;
+        const std::pair<int, int> key(i < js[k] ? i : js[k], i < js[k] ? js[k] : i);
+        if (!seen.insert(key).second) { std::printf("twice nb=%d (%d,%d)\n", nb, key.first, key.second); return 1; }
+      }
+    }
+    if (static_cast<int>(seen.size()) != nb * (nb + 1) / 2) { std::printf("missing nb=%d\n", nb); return 1; }
+    if (singles > 1 || units != (nb * (nb + 1) / 2 + 1) / 2) { std::printf("count nb=%d\n", nb); return 1; }
+  }
+  std::printf("ok\n");
+  return 0;
+}
+''')
+    exe = tmp_path / "units"
+    subprocess.run([gxx, "-O1", "-std=c++17", "-o", str(exe), str(src)], check=True)
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0 and out.stdout.strip() == "ok", out.stdout
