@@ -204,10 +204,14 @@ def run_native(args, wl):
                               rank=rank, world=world)
         dW = ops.dp_linear_weight_grad(Xd, Gd, 1.0, 1.0, batch_divisor=B * world, noise=noise,
                                        out_dtype=torch.float32, norm_algo=args.norm_algo)
-        work = dist.all_reduce(dW, op=dist.ReduceOp.SUM, async_op=True) if world > 1 else None
-        dX = ops.linear_input_grad(Gd, W, "out_in")
-        if work is not None:
-            work.wait()
+        if world == 1:
+            return dW, ops.linear_input_grad(Gd, W, "out_in")
+        # the all-reduce of this layer's gradient runs beside the input-gradient GEMM, which leaves a few
+        # SMs free for it; the norm pass and the clipped-sum GEMM above had the whole GPU
+        work = dist.all_reduce(dW, op=dist.ReduceOp.SUM, async_op=True)
+        with fdp.sm_reservation():
+            dX = ops.linear_input_grad(Gd, W, "out_in")
+        work.wait()
         return dW, dX
 
     def barrier():

@@ -9,6 +9,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 # FDP_B200_LIB points at another build of the same ABI (used to compare builds on one GPU)
 LIB_PATH = os.environ.get("FDP_B200_LIB") or os.path.join(PKG, "libfdp_b200.so")
 
+ABI_VERSION = 2
 FDP_OK = 0
 FDP_ERR_ARG, FDP_ERR_DTYPE, FDP_ERR_SHAPE, FDP_ERR_ALIGN = -1, -2, -3, -4
 FDP_ERR_WORKSPACE, FDP_ERR_ARCH, FDP_ERR_LAUNCH, FDP_ERR_TIMEOUT = -5, -6, -7, -8
@@ -36,6 +37,10 @@ SIGNATURES = {
     "fdp_status_string": (ctypes.c_char_p, [c_int]),
     "fdp_check_device": (c_int, [c_int]),
     "fdp_device_status": (c_int, [c_void_p, c_void_p]),
+    "fdp_async_status": (c_int, [c_int]),
+    "fdp_clear_async_status": (c_int, [c_int]),
+    "fdp_selftest_wait_timeout": (c_int, [ctypes.c_longlong, c_void_p, c_size_t, c_void_p]),
+    "fdp_set_sm_reserve": (c_int, [c_int]),
     "fdp_launch_count": (ctypes.c_ulonglong, []),
     "fdp_profile_enable": (c_int, [c_int]),
     "fdp_profile_read": (c_int, [ctypes.POINTER(c_float), c_int]),
@@ -73,7 +78,7 @@ def load():
         for name, (res, args) in SIGNATURES.items():
             fn = getattr(lib, name)
             fn.restype, fn.argtypes = res, args
-        if lib.fdp_abi_version() != 1:
+        if lib.fdp_abi_version() != ABI_VERSION:
             raise ImportError("libfdp_b200.so: ABI version mismatch, rebuild the library")
         _lib = lib
     return _lib

@@ -43,6 +43,12 @@ def _stream(device):
     return torch.cuda.current_stream(device).cuda_stream
 
 
+def _aligned(t):
+    """`t` itself, or a copy when its storage offset leaves it off a 16-byte boundary (the
+    tensor-core kernels move 16-byte vectors; .contiguous() keeps the offset of a contiguous view)."""
+    return t if t.data_ptr() % 16 == 0 else t.clone(memory_format=torch.contiguous_format)
+
+
 def _workspace(nbytes, device):
     return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
 
@@ -91,8 +97,8 @@ def dp_linear_weight_grad(input, grad_output, C, clamp_value, *, batch_divisor=N
     _require_cuda(input, grad_output)
     if input.dim() != 3 or grad_output.dim() != 3 or input.shape[:2] != grad_output.shape[:2]:
         raise RuntimeError(f"expected (B,T,in) and (B,T,out), got {tuple(input.shape)} and {tuple(grad_output.shape)}")
-    G = grad_output.contiguous()
-    X = input.to(G.dtype).contiguous()     # the reference casts input to the grad dtype (linear_clip.py:111)
+    G = _aligned(grad_output.contiguous())
+    X = _aligned(input.to(G.dtype).contiguous())     # the reference casts input to the grad dtype (linear_clip.py:111)
     B, T, n_in = X.shape
     n_out = G.shape[-1]
     shape = (n_out, n_in) if layout == "out_in" else (n_in, n_out)

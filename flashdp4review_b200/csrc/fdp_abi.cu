@@ -10,6 +10,33 @@ using namespace fdp;
 namespace fdp {
 static std::atomic<unsigned long long> g_launches{0};
 void note_launch(int n) { g_launches.fetch_add(static_cast<unsigned long long>(n), std::memory_order_relaxed); }
+
+// Host-visible status array: one int per device in mapped, pinned host memory (allocated once per
+// process; with unified addressing the host pointer is valid on every device).  Kernels store a
+// code there when a bounded wait runs out; the host reads it without synchronising anything.
+static volatile int* sticky_array() {
+  static std::mutex mu;
+  static volatile int* arr = nullptr;
+  static bool tried = false;
+  std::lock_guard<std::mutex> lk(mu);
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, 64 * sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable) == cudaSuccess) {
+      for (int i = 0; i < 64; ++i) static_cast<int*>(p)[i] = 0;
+      arr = static_cast<volatile int*>(p);
+    } else {
+      cudaGetLastError();
+    }
+  }
+  return arr;
+}
+int* sticky_status_slot() {
+  volatile int* arr = sticky_array();
+  int dev = 0;
+  if (arr == nullptr || cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return nullptr; }
+  return const_cast<int*>(arr + dev);
+}
 }  // namespace fdp
 
 namespace {
@@ -35,10 +62,14 @@ int device_cc_major(int dev) {
   return cache[dev];
 }
 
+// Is the current device a B200, and has no earlier kernel on it reported a wait that ran out?
 int current_device_ok() {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return FDP_ERR_LAUNCH; }
-  return device_cc_major(dev) == 10 ? FDP_OK : FDP_ERR_ARCH;
+  if (device_cc_major(dev) != 10) return FDP_ERR_ARCH;
+  volatile int* arr = sticky_array();
+  if (arr != nullptr && dev < 64 && arr[dev] != 0) return FDP_ERR_TIMEOUT;
+  return FDP_OK;
 }
 
 int check_params(const fdp_dp_params* p) {
@@ -128,7 +159,7 @@ const char* fdp_status_string(int status) {
     case FDP_ERR_WORKSPACE: return "workspace missing or too small";
     case FDP_ERR_ARCH: return "device is not sm_100 (B200)";
     case FDP_ERR_LAUNCH: return "CUDA launch/runtime error";
-    case FDP_ERR_TIMEOUT: return "a bounded device-side wait ran out";
+    case FDP_ERR_TIMEOUT: return "a bounded device-side wait ran out (results of that call are undefined; fdp_clear_async_status re-arms the device)";
     case FDP_ERR_STATIC_LIMIT: return "problem needs more scratch than the library's fixed buffer (FDP_STATIC_SCRATCH_BYTES)";
     default: return "unknown status";
   }
@@ -137,12 +168,39 @@ const char* fdp_status_string(int status) {
 int fdp_check_device(int device) { return device_cc_major(device) == 10 ? FDP_OK : FDP_ERR_ARCH; }
 
 int fdp_device_status(const void* workspace, fdp_stream_t stream) {
-  if (workspace == nullptr) return FDP_ERR_ARG;
   int h = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  FDP_CUDA_OK(cudaMemcpyAsync(&h, workspace, sizeof(int), cudaMemcpyDeviceToHost, s));
+  if (workspace != nullptr)
+    FDP_CUDA_OK(cudaMemcpyAsync(&h, workspace, sizeof(int), cudaMemcpyDeviceToHost, s));
   FDP_CUDA_OK(cudaStreamSynchronize(s));
-  return h == 0 ? FDP_OK : FDP_ERR_TIMEOUT;
+  if (h != 0) return FDP_ERR_TIMEOUT;
+  return fdp_async_status(-1);
+}
+
+int fdp_async_status(int device) {
+  if (device < 0 && cudaGetDevice(&device) != cudaSuccess) { cudaGetLastError(); return FDP_ERR_LAUNCH; }
+  if (device < 0 || device >= 64) return FDP_ERR_ARG;
+  volatile int* arr = fdp::sticky_array();
+  return (arr != nullptr && arr[device] != 0) ? FDP_ERR_TIMEOUT : FDP_OK;
+}
+
+int fdp_clear_async_status(int device) {
+  if (device < 0 && cudaGetDevice(&device) != cudaSuccess) { cudaGetLastError(); return FDP_ERR_LAUNCH; }
+  if (device < 0 || device >= 64) return FDP_ERR_ARG;
+  volatile int* arr = fdp::sticky_array();
+  if (arr != nullptr) arr[device] = 0;
+  return FDP_OK;
+}
+
+int fdp_set_sm_reserve(int n) { return sm_reserve_exchange(n); }
+
+int fdp_selftest_wait_timeout(long long limit_cycles, void* workspace, size_t workspace_bytes, fdp_stream_t stream) {
+  if (workspace == nullptr || workspace_bytes < 256 || !aligned16(workspace)) return FDP_ERR_WORKSPACE;
+  int st = current_device_ok();
+  if (st != FDP_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  FDP_CUDA_OK(cudaMemsetAsync(workspace, 0, sizeof(int), s));
+  return tc_wait_selftest(static_cast<int*>(workspace), limit_cycles, s);
 }
 
 // ---- weight gradient ------------------------------------------------------------------------------
@@ -164,11 +222,13 @@ int fdp_linear_wgrad(const void* G, const void* X, void* dW, float* norms_out, f
   if (static_cast<long long>(B) * T >= (1ll << 31) / 2 || B > 65535) return FDP_ERR_SHAPE;  // B is a grid dimension
   int st = check_params(p);
   if (st != FDP_OK) return st;
-  if (!aligned16(G) || !aligned16(X) || !aligned16(dW)) return FDP_ERR_ALIGN;
   if ((st = current_device_ok()) != FDP_OK) return st;
   if (workspace == nullptr) return FDP_ERR_WORKSPACE;
   WgradWs w = wgrad_ws(workspace, B, T, n_in, n_out, in_dtype, norm_algo);
   if (workspace_bytes < w.bytes || !aligned16(workspace)) return FDP_ERR_WORKSPACE;
+  // the tensor-core path moves 16-byte vectors (TMA, vector stores); the generic kernels load and
+  // store single elements and take any naturally aligned pointer
+  if (w.tc.ok && (!aligned16(G) || !aligned16(X) || !aligned16(dW))) return FDP_ERR_ALIGN;
 
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int div = p->batch_divisor > 0 ? p->batch_divisor : B;
@@ -176,6 +236,8 @@ int fdp_linear_wgrad(const void* G, const void* X, void* dW, float* norms_out, f
   const NoiseKey nk = make_noise_key(p, p->param_id);
   FDP_CUDA_OK(cudaMemsetAsync(w.status, 0, sizeof(int), s));
 
+  // the scaled epilogue of the clipped-sum GEMM reduces the norm partials itself: no clip-factor launch
+  const bool fused_factors = w.tc.ok && w.tc.scaled_epilogue && tc_fused_factors_ok(B);
   prof_mark(0, s);
   if (w.short_seq) {
     simt_norm_gram_small(G, X, w.partials, B, T, n_in, n_out, in_dtype, s);
@@ -185,7 +247,8 @@ int fdp_linear_wgrad(const void* G, const void* X, void* dW, float* norms_out, f
     simt_norm_direct(G, X, w.partials, B, T, n_in, n_out, in_dtype, s);
   }
   prof_mark(1, s);
-  clip_factors(w.partials, w.nparts, B, p->C, p->clamp_value, w.norms, w.factors, norms_out, factors_out, s);
+  if (!fused_factors)
+    clip_factors(w.partials, w.nparts, B, p->C, p->clamp_value, w.norms, w.factors, norms_out, factors_out, s);
   prof_mark(2, s);
   if (w.tc.ok) {
     float* split_ws = static_cast<float*>(w.tc_extra);
@@ -194,9 +257,16 @@ int fdp_linear_wgrad(const void* G, const void* X, void* dW, float* norms_out, f
       if ((st = tc_prescale(G, w.factors, gs, B, T, n_out, in_dtype, s)) != FDP_OK) return st;
     }
     prof_mark(3, s);
-    if ((st = tc_clipped_wgrad(w.tc.scaled_epilogue ? G : gs, X, w.tc.scaled_epilogue ? w.factors : nullptr,
-                               split_ws, dW, w.status, B, T, n_in, n_out, in_dtype, out_dtype, layout, inv_div,
-                               nk, s)) != FDP_OK) return st;
+    TcFactorSource fs{};
+    if (fused_factors) {
+      fs.norm_partials = w.partials; fs.nparts = w.nparts; fs.C = p->C; fs.clamp = p->clamp_value;
+      fs.norms_out = norms_out; fs.factors_out = factors_out;
+    } else {
+      fs.factors = w.factors;
+    }
+    if ((st = tc_clipped_wgrad(w.tc.scaled_epilogue ? G : gs, X, w.tc.scaled_epilogue ? &fs : nullptr, split_ws,
+                               dW, w.status, B, T, n_in, n_out, in_dtype, out_dtype, layout, inv_div, nk,
+                               s)) != FDP_OK) return st;
   } else {
     prof_mark(3, s);
     simt_clipped_wgrad(G, X, w.factors, dW, B, T, n_in, n_out, in_dtype, out_dtype, layout, inv_div, nk, s);

@@ -6,6 +6,13 @@ namespace fdp {
 
 // every kernel launch of the library is counted (fdp_launch_count)
 void note_launch(int n = 1);
+// The current device's slot of the host-visible (mapped, pinned) status array, as a pointer kernels
+// may write through; null when the array could not be set up.  A bounded wait that runs out stores
+// its code there, and every later entry-point call on that device returns FDP_ERR_TIMEOUT until
+// fdp_clear_async_status.
+int* sticky_status_slot();
+// SMs persistent GEMM grids leave free (fdp_set_sm_reserve)
+int sm_reserve_exchange(int n);
 
 // ---- generic-shape kernels (any dtype, any size; fp32 FMA accumulation) -----------------------
 int simt_norm_tiles(int n_in, int n_out);
@@ -82,11 +89,23 @@ int tc_norms(const void* G, const void* X, float* partials, int* dev_status, int
 // Gs[r,:] = factors[r / T] * G[r,:]
 int tc_prescale(const void* G, const float* factors, void* Gs, int B, int T, int n_out, int dt,
                 cudaStream_t s);
-// dW = inv_div * sum_b c_b G_b^T X_b + noise over K = B*T.  factors == nullptr: Gs is the pre-scaled
-// copy; otherwise Gs is G itself and c_b is applied per sample in the epilogue.
-int tc_clipped_wgrad(const void* Gs, const void* X, const float* factors, float* split_ws, void* dW,
-                     int* dev_status, int B, int T, int n_in, int n_out, int dt, int out_dt, int layout,
-                     float inv_div, NoiseKey nk, cudaStream_t s);
+// Where the scaled epilogue of the clipped-sum GEMM takes its clip factors from: `factors` (device,
+// computed by an earlier kernel), or -- factors == nullptr -- the norm pass's partial sums, reduced
+// inside the GEMM kernel (tc_fused_factors_ok(B) must hold); the kernel then also fills
+// norms_out / factors_out (each may be null).
+struct TcFactorSource {
+  const float* factors;
+  const float* norm_partials; int nparts; float C, clamp;
+  float* norms_out; float* factors_out;
+};
+bool tc_fused_factors_ok(int B);
+// dW = inv_div * sum_b c_b G_b^T X_b + noise over K = B*T.  fs == nullptr: Gs is the pre-scaled copy;
+// otherwise Gs is G itself and c_b is applied per sample in the epilogue.
+int tc_clipped_wgrad(const void* Gs, const void* X, const TcFactorSource* fs, float* split_ws,
+                     void* dW, int* dev_status, int B, int T, int n_in, int n_out, int dt, int out_dt,
+                     int layout, float inv_div, NoiseKey nk, cudaStream_t s);
+// test aid: one warp waits `limit_cycles` on a barrier nobody arrives on and reports the timeout
+int tc_wait_selftest(int* status, long long limit_cycles, cudaStream_t s);
 bool tc_dgrad_ok(int rows, int n_in, int n_out, int dt);
 int tc_fwd(const void* X, const void* W, const void* bias, void* Y, int* dev_status, int rows, int n_in,
            int n_out, int dt, int out_dt, int w_layout, cudaStream_t s);

@@ -6,6 +6,18 @@
 
 namespace fdp {
 
+// named barrier `id` over `nthreads` threads that also ANDs a predicate across them
+__device__ __forceinline__ bool bar_red_and(int id, int nthreads, bool pred) {
+  uint32_t r;
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 q, %3, 0;\n\t"
+      "bar.red.and.pred p, %1, %2, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(r) : "r"(id), "r"(nthreads), "r"(static_cast<uint32_t>(pred)) : "memory");
+  return r != 0;
+}
+
 // VEC adjacent affine parameters starting at column c (a multiple of VEC) as fp32: one or two
 // 16-byte loads when the parameter array is 16-byte aligned, scalar loads otherwise
 template <int VEC>
@@ -114,12 +126,12 @@ __global__ void __launch_bounds__(288) ln_fwd_staged_kernel(const Tin* __restric
                                                             Tin* __restrict__ y, float* __restrict__ mean,
                                                             float* __restrict__ rstd, int rows, int d,
                                                             float eps, int pdt, int n_stages,
-                                                            int pvec_ok) {
+                                                            int pvec_ok, int* sticky) {
   constexpr int VEC = 16 / sizeof(Tin);
   extern __shared__ __align__(128) unsigned char ln_smem[];
   __shared__ __align__(8) unsigned long long bars[2 * LN_MAX_STAGES];
   __shared__ int abort_flag_s;
-  volatile int* abort_flag = &abort_flag_s;
+  const WaitCtx wctx{&abort_flag_s, nullptr, sticky, WAIT_LIMIT_CYCLES};
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t row_bytes = static_cast<uint32_t>(d) * sizeof(Tin);
   const uint32_t stage_bytes = 8 * row_bytes;
@@ -136,7 +148,7 @@ __global__ void __launch_bounds__(288) ln_fwd_staged_kernel(const Tin* __restric
     if (lane == 0) {
       int s = 0; uint32_t ph = 0;
       for (int g = g0; g < g1; g += gstep) {
-        if (!mbar_wait(smem_u32(&bars[LN_MAX_STAGES + s]), ph ^ 1u, abort_flag, nullptr, 0)) break;
+        if (!mbar_wait(smem_u32(&bars[LN_MAX_STAGES + s]), ph ^ 1u, wctx, 5)) break;
         const int nrows = min(8, rows - g * 8);
         mbar_expect_tx(smem_u32(&bars[s]), nrows * row_bytes);
         bulk_load(smem_u32(ln_smem + s * stage_bytes), x + static_cast<size_t>(g) * 8 * d, nrows * row_bytes, smem_u32(&bars[s]));
@@ -159,7 +171,7 @@ __global__ void __launch_bounds__(288) ln_fwd_staged_kernel(const Tin* __restric
   }
   int s = 0; uint32_t ph = 0;
   for (int g = g0; g < g1; g += gstep) {
-    if (!mbar_wait(smem_u32(&bars[s]), ph, abort_flag, nullptr, 0)) break;
+    if (!mbar_wait_warp(smem_u32(&bars[s]), ph, wctx, 6)) break;
     const int row = g * 8 + warp;
     if (NV > 0) {
       // ---- the row lives in registers ----
@@ -349,13 +361,13 @@ static void ln_fwd_t(const void* x, const void* gamma, const void* beta, void* y
     const int pv = aligned16(gamma) && aligned16(beta) ? 1 : 0;
     if (in_regs && smem_opt_in(done_r, mu, ln_fwd_staged_kernel<Tin, NVR>, LN_SMEM_BUDGET)) {
       ln_fwd_staged_kernel<Tin, NVR><<<grid, 288, n_stages * stage_bytes, s>>>(
-          (const Tin*)x, gamma, beta, (Tin*)y, mean, rstd, rows, d, eps, pdt, n_stages, pv);
+          (const Tin*)x, gamma, beta, (Tin*)y, mean, rstd, rows, d, eps, pdt, n_stages, pv, sticky_status_slot());
       note_launch();
       return;
     }
     if (smem_opt_in(done, mu, ln_fwd_staged_kernel<Tin, 0>, LN_SMEM_BUDGET)) {
       ln_fwd_staged_kernel<Tin, 0><<<grid, 288, n_stages * stage_bytes, s>>>(
-          (const Tin*)x, gamma, beta, (Tin*)y, mean, rstd, rows, d, eps, pdt, n_stages, pv);
+          (const Tin*)x, gamma, beta, (Tin*)y, mean, rstd, rows, d, eps, pdt, n_stages, pv, sticky_status_slot());
       note_launch();
       return;
     }
@@ -393,7 +405,7 @@ __global__ void __launch_bounds__(STAGED ? CW + 32 : CW) ln_bwd_kernel(
     const Tin* __restrict__ dy, const Tin* __restrict__ x, const void* __restrict__ gamma,
     const float* __restrict__ mean, const float* __restrict__ rstd, Tin* __restrict__ dx,
     float* __restrict__ dg_part, float* __restrict__ db_part, int T, int d, int pdt,
-    int rows_per_block, int chunks, int n_stages) {
+    int rows_per_block, int chunks, int n_stages, int* sticky) {
   constexpr int RG = CW / TPR;
   constexpr int NWG = TPR / 32;  // warps per row group
   // dynamic shared memory: the ring (STAGED), reused at the end as [RG][TPR*NV*VEC] floats for the
@@ -404,7 +416,7 @@ __global__ void __launch_bounds__(STAGED ? CW + 32 : CW) ln_bwd_kernel(
   __shared__ __align__(8) unsigned long long bars[2 * LN_MAX_STAGES];
   __shared__ int abort_flag_s;
   __shared__ float s_mean[LN_MAX_ROWS_PER_BLOCK], s_rstd[LN_MAX_ROWS_PER_BLOCK];  // this chunk's row statistics
-  volatile int* abort_flag = &abort_flag_s;
+  const WaitCtx wctx{&abort_flag_s, nullptr, sticky, WAIT_LIMIT_CYCLES};
   const int rg = (threadIdx.x % CW) / TPR, t = threadIdx.x % TPR;
   const int lane = threadIdx.x & 31, wig = (threadIdx.x % TPR) >> 5;
   const int b = blockIdx.y, chunk = blockIdx.x;
@@ -441,7 +453,7 @@ __global__ void __launch_bounds__(STAGED ? CW + 32 : CW) ln_bwd_kernel(
     if (threadIdx.x == CW) {
       int s = 0; uint32_t ph = 0;
       for (int it = 0; it < n_iter; ++it) {
-        if (!mbar_wait(smem_u32(&bars[LN_MAX_STAGES + s]), ph ^ 1u, abort_flag, nullptr, 0)) break;
+        if (!mbar_wait(smem_u32(&bars[LN_MAX_STAGES + s]), ph ^ 1u, wctx, 7)) break;
         const int rb = r0 + it * RG;
         const int nrows = min(RG, r1 - rb);
         const size_t goff = (static_cast<size_t>(b) * T + rb) * d;
@@ -460,8 +472,10 @@ __global__ void __launch_bounds__(STAGED ? CW + 32 : CW) ln_bwd_kernel(
       const size_t row = static_cast<size_t>(b) * T + r;
       const Tin* xr = x + row * d;
       const Tin* dyr = dy + row * d;
+      bool ok = true;   // whether this warp saw the stage arrive; agreed on by the row group below
       if (STAGED) {
-        if (!mbar_wait(smem_u32(&bars[s]), ph, abort_flag, nullptr, 0)) break;
+        ok = mbar_wait_warp(smem_u32(&bars[s]), ph, wctx, 8);
+        if (NWG == 1 && !ok) break;
         xr = reinterpret_cast<const Tin*>(ln_smem + s * stage_bytes + rg * row_bytes);
         dyr = reinterpret_cast<const Tin*>(ln_smem + s * stage_bytes + (RG + rg) * row_bytes);
       }
@@ -508,11 +522,13 @@ __global__ void __launch_bounds__(STAGED ? CW + 32 : CW) ln_bwd_kernel(
         if (lane == 0) mbar_arrive(smem_u32(&bars[LN_MAX_STAGES + s]));
         if (++s == n_stages) { s = 0; ph ^= 1u; }
       }
-      if (!valid) continue;
+      if (!valid) { if (!ok) break; continue; }     // `valid` is the same for the whole row group
       s1 = warp_sum(s1); s2 = warp_sum(s2);
       if (NWG > 1) {
         if (lane == 0) xch[rg][wig] = make_float2(s1, s2);
-        asm volatile("bar.sync %0, %1;" ::"r"(1 + rg), "r"(TPR) : "memory");
+        // the barrier also carries the row group's verdict on the wait: either all of its warps go
+        // on or all of them leave, so none is left waiting at a barrier the others never reach
+        if (!bar_red_and(1 + rg, TPR, ok)) break;
         s1 = 0.f; s2 = 0.f;
 #pragma unroll
         for (int w = 0; w < NWG; ++w) { s1 += xch[rg][w].x; s2 += xch[rg][w].y; }
@@ -616,7 +632,7 @@ static bool ln_bwd_launch_one(const void* dy, const void* x, const void* gamma, 
   if (smem > 48 * 1024 && !smem_opt_in(done, mu, ln_bwd_kernel<Tin, VEC, NV, TPRV, STAGED, CW>, LN_SMEM_BUDGET)) return false;
   ln_bwd_kernel<Tin, VEC, NV, TPRV, STAGED, CW><<<grid, STAGED ? CW + 32 : CW, smem, s>>>(
       (const Tin*)dy, (const Tin*)x, gamma, mean, rstd, (Tin*)dx, dg_part, db_part, T, d, pdt,
-      pl.rows_per_block, pl.chunks, n_stages);
+      pl.rows_per_block, pl.chunks, n_stages, sticky_status_slot());
   note_launch();
   return true;
 }

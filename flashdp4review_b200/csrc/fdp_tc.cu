@@ -14,6 +14,7 @@
 // bounded: when one runs out the CTA records a code in the status word, drains and leaves.
 // No TMA load here uses cluster multicast.
 #include <cuda.h>
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 
@@ -29,13 +30,18 @@ constexpr int A_STAGE_BYTES = BM * BK * 2;  // 16 KiB
 constexpr int B_STAGE_BYTES = BN * BK * 2;  // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
 constexpr int BAR_BYTES = 256;
+// EPI_STORE_SCALED keeps the clip factors of up to MAX_SMEM_FACTORS samples in shared memory
+constexpr int MAX_SMEM_FACTORS = 4096;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 + BAR_BYTES;
+constexpr int SMEM_BYTES_SCALED = SMEM_BYTES + MAX_SMEM_FACTORS * 4;
 constexpr int TMEM_COLS = 512;
+constexpr int MAX_SMS = 148;           // workers the split-K parking area is sized for
 
 // EPI_STORE_SCALED: the accumulator of each sample (K segment) is drained on its own and added, times
 // that sample's clip factor, to fp32 registers of eight epilogue warps; G needs no scaled copy.
 enum { EPI_STORE = 0, EPI_SUMSQ = 1, EPI_GRAM = 2, EPI_STORE_SCALED = 3 };
 constexpr int threads_for(int epi) { return epi == EPI_STORE_SCALED ? 320 : 192; }
+constexpr int smem_for(int epi) { return epi == EPI_STORE_SCALED ? SMEM_BYTES_SCALED : SMEM_BYTES; }
 
 struct TcArgs {
   int M, N;             // extents of the output space of one batch (masks)
@@ -46,17 +52,28 @@ struct TcArgs {
   int k_stages, k_stages2;  // K loop of operand pair 1 (and pair 2 for EPI_GRAM)
   int batch_rows;           // rows of one batch along the row coordinate of the tensor maps
   void* out; int out_dt; long long ld_out; float scale; NoiseKey nk;
-  float* partials;
+  float* partials;      // norm passes: one partial per (work unit, epilogue warp)
   int T;
-  int* status;
+  int* status;          // status word of the call (workspace)
+  int* sticky;          // this device's slot of the host-visible status array, or null
   uint32_t idesc;
-  // split-K tail (EPI_STORE only): work units [0, units_full) are whole tiles; each later tile is cut
-  // into `split` K ranges whose raw fp32 accumulators go to split_ws[slot][BM][BN] for the fix-up kernel
+  // split-K (store epilogues): work units [0, units_full) are whole tiles; each later tile is cut into
+  // `split` K-stage ranges whose fp32 accumulators are parked in split_ws[slot][BM][BN]; the fix-up
+  // kernel adds the parts in index order, adds the noise and stores the tile.  Nobody waits.
+  // (Tried: the part that finishes last -- a ticket per tile -- sums the parts inside this kernel.
+  // At B=16, T=1024, 1024->3072 that took 0.19 ms against 0.10 ms with the separate launch: the
+  // sums then sit on the critical path of a few warps instead of spreading over the whole GPU.)
   int units_full, split;
   float* split_ws;
-  // EPI_STORE_SCALED: K is `segs` segments (samples) of `seg_stages` stages; factors[seg] scales each
+  // EPI_STORE_SCALED: K is `segs` segments (samples) of `seg_stages` stages; every segment has its own
+  // accumulator, scaled by that sample's clip factor when it is drained.  The factors come either from
+  // `factors` (global, computed by an earlier kernel) or, when norm_partials != null, from the norm
+  // pass's partial sums: the epilogue warps reduce them into shared memory while the first main loop
+  // runs, and the first CTA also writes the norms and factors out.
   const float* factors;
   int segs, seg_stages;
+  const float* norm_partials; int norm_nparts; float C, clamp;
+  float* norms_ws; float* factors_ws; float* norms_out; float* factors_out;
   // EPI_GRAM: the T x T plane of a sample is cut into 128 x 128 blocks; only blocks (i, j) with j >= i
   // are computed (weight 2, the diagonal ones weight 1).  A work unit is one t-block i against TWO
   // s-blocks j1, j2 (an N = 256 MMA whose B stage is filled by two 128-row copies), see gram_decode;
@@ -158,9 +175,20 @@ __device__ __forceinline__ uint64_t operand_desc(uint32_t stage_base, int k16) {
   return make_desc(stage_base + k16 * (UMMA_K * 2), 0, 1024);
 }
 
-// Finish 32 adjacent output columns of row m starting at column n: add the noise, convert, store.
-__device__ __forceinline__ void store_chunk32(const TcArgs& args, float v[32], int m, int n,
-                                              bool add_noise = true) {
+// The Gaussian noise of 32 adjacent output elements starting at flat index idx0 (a multiple of 4: the
+// tensor-core kernels only see row pitches and column offsets that are multiples of 8).
+__device__ __forceinline__ void add_noise32(const NoiseKey& nk, size_t idx0, float v[32]) {
+#pragma unroll
+  for (int g = 0; g < 8; ++g) {
+    float z[4];
+    noise_group(nk, (idx0 >> 2) + g, z);
+    v[4 * g] += z[0]; v[4 * g + 1] += z[1]; v[4 * g + 2] += z[2]; v[4 * g + 3] += z[3];
+  }
+}
+
+// Finish 32 adjacent output columns of row m starting at column n: bias, noise (NOISE), convert, store.
+template <bool NOISE>
+__device__ __forceinline__ void store_chunk32(const TcArgs& args, float v[32], int m, int n) {
   if (m >= args.M || n >= args.N) return;
   const size_t idx0 = static_cast<size_t>(m) * args.ld_out + n;
   if (args.bias != nullptr) {
@@ -168,19 +196,7 @@ __device__ __forceinline__ void store_chunk32(const TcArgs& args, float v[32], i
     for (int j = 0; j < 32; ++j)
       if (n + j < args.N) v[j] += load_as(args.bias, args.bias_dt, n + j);
   }
-  if (add_noise && args.nk.std != 0.f) {
-    if ((idx0 & 3) == 0) {
-#pragma unroll
-      for (int g = 0; g < 8; ++g) {
-        float z[4];
-        noise_group(args.nk, (idx0 >> 2) + g, z);
-        v[4 * g] += z[0]; v[4 * g + 1] += z[1]; v[4 * g + 2] += z[2]; v[4 * g + 3] += z[3];
-      }
-    } else {
-#pragma unroll
-      for (int j = 0; j < 32; ++j) v[j] += noise_at(args.nk, idx0 + j);
-    }
-  }
+  if (NOISE && args.nk.std != 0.f) add_noise32(args.nk, idx0, v);
   const bool vec_ok = (args.ld_out * static_cast<long long>(dtype_size(args.out_dt))) % 16 == 0;
   if (n + 32 <= args.N && vec_ok) {
     if (args.out_dt == FDP_F32) {
@@ -238,13 +254,13 @@ template <bool A_MN, bool B_MN, int EPI, int CTAS>
 __global__ void __launch_bounds__(threads_for(EPI), 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2,
-               const TcArgs args) {
+               const __grid_constant__ TcArgs args) {
   constexpr int NST = (CTAS == 2) ? 6 : STAGES;          // ring depth
   constexpr int B_BYTES = B_STAGE_BYTES / CTAS;          // this CTA's share of the B stage
   constexpr int STG = A_STAGE_BYTES + B_BYTES;
   constexpr int BN_CTA = BN / CTAS;                      // B columns (rows if K-major) loaded by this CTA
   constexpr int EPI_WARPS = (EPI == EPI_STORE_SCALED) ? 8 : 4;
-  static_assert(NST * STG == NST * STG, "ring size");
+  static_assert(NST * STG <= STAGES * STAGE_BYTES, "ring size");
   static_assert(CTAS == 1 || EPI == EPI_STORE || EPI == EPI_STORE_SCALED, "pairs: store epilogues only");
   const uint32_t cta_rank = (CTAS == 2) ? cluster_ctarank() : 0u;
   const bool is_leader = cta_rank == 0;
@@ -261,15 +277,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const uint32_t drain_bar = bar_base + 8u * (2 * NST + 4);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_gen + 8 * (2 * NST + 5));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_gen + 8 * (2 * NST + 5) + 4);
-  float* red = reinterpret_cast<float*>(bar_gen + 8 * (2 * NST + 6));  // 4 floats
+  float* sfac = reinterpret_cast<float*>(bar_gen + BAR_BYTES);   // EPI_STORE_SCALED: clip factors [segs]
+  const WaitCtx wctx{abort_flag, args.status, args.sticky, WAIT_LIMIT_CYCLES};
 
   constexpr int NUM_ACC = (EPI == EPI_GRAM) ? 1 : 2;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int total_tiles = args.batch * args.tiles_per_batch;
   const int kst_total = args.k_stages + (EPI == EPI_GRAM ? args.k_stages2 : 0);
-  const int total_units = (EPI == EPI_GRAM)
-      ? args.batch * args.tiles_per_batch
-      : args.units_full + (total_tiles - args.units_full) * args.split;
+  const int total_units = args.units_full + (total_tiles - args.units_full) * args.split;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < NST; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -330,8 +345,6 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     m0 = mi * (BM * CTAS) + cta_rank * BM;
     n0 = ni * BN;
   };
-  // EPI_GRAM: a unit is one tile
-  auto gram_unit = [&](int u, int sub, int& nsub, int& tile) { (void)sub; nsub = 1; tile = u; };
 
   // work unit -> tile, K-stage range, slot in split_ws (-1: whole tile, normal epilogue)
   auto decode_unit = [&](int u, int& tile, int& ks0, int& ks1, int& slot) {
@@ -339,14 +352,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     const int v = u - args.units_full;
     const int part = v % args.split;
     tile = args.units_full + v / args.split;
-    if (EPI == EPI_STORE_SCALED) {  // cut between samples
-      ks0 = (args.segs * part / args.split) * args.seg_stages;
-      ks1 = (args.segs * (part + 1) / args.split) * args.seg_stages;
-    } else {
-      ks0 = static_cast<int>(static_cast<long long>(kst_total) * part / args.split);
-      ks1 = static_cast<int>(static_cast<long long>(kst_total) * (part + 1) / args.split);
-    }
+    ks0 = static_cast<int>(static_cast<long long>(kst_total) * part / args.split);
+    ks1 = static_cast<int>(static_cast<long long>(kst_total) * (part + 1) / args.split);
     slot = v;
+  };
+  // EPI_STORE_SCALED: end of the sample segment that contains stage ks, cut at the unit's end
+  auto segment_end = [&](int ks, int ks1) {
+    const int e = (ks / args.seg_stages + 1) * args.seg_stages;
+    return e < ks1 ? e : ks1;
   };
 
   if (warp == 0) {
@@ -354,17 +367,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (lane == 0) {
       int stage = 0; uint32_t phase = 0;
       bool ok = true;
-      int nsub = 1;
-      for (int round = 0, sub = 0; ok; (++sub >= nsub) ? (void)(sub = 0, ++round) : (void)0) {
-        const int u = wid + round * wstep;
-        if (u >= total_units) break;
+      for (int u = wid; u < total_units && ok; u += wstep) {
         int tile, ks0, ks1, slot, b, m0, n0, half;
-        if (EPI == EPI_GRAM) { gram_unit(u, sub, nsub, tile); ks0 = 0; ks1 = kst_total; slot = -1; }
-        else decode_unit(u, tile, ks0, ks1, slot);
+        decode_unit(u, tile, ks0, ks1, slot);
         decode(tile, b, m0, n0, half);
         const int row0 = b * args.batch_rows;
         for (int ks = ks0; ks < ks1; ++ks) {
-          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, args.status, 1)) { ok = false; break; }
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, wctx, 1)) { ok = false; break; }
           const bool second = (EPI == EPI_GRAM) && ks >= args.k_stages;
           const CUtensorMap* ma = second ? &tmA2 : &tmA;
           const CUtensorMap* mb = second ? &tmB2 : &tmB;
@@ -430,28 +439,23 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       int stage = 0; uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      int nsub = 1;
-      for (int round = 0, sub = 0; ok; (++sub >= nsub) ? (void)(sub = 0, ++round) : (void)0) {
-        const int u = wid + round * wstep;
-        if (u >= total_units) break;
+      for (int u = wid; u < total_units && ok; u += wstep) {
         int tile, ks0, ks1, slot, tb, tm0, tn0, half;
-        if (EPI == EPI_GRAM) { gram_unit(u, sub, nsub, tile); ks0 = 0; ks1 = kst_total; slot = -1; }
-        else decode_unit(u, tile, ks0, ks1, slot);
+        decode_unit(u, tile, ks0, ks1, slot);
         decode(tile, tb, tm0, tn0, half);
         // a single-block unit multiplies by the first 128 rows of the B stage only (N = 128)
         const uint32_t idesc = half ? args.idesc_half : args.idesc;
-        const uint32_t b_off = 0u;
         int ks = ks0;
-        // one accumulator per segment: the whole unit, or one sample for EPI_STORE_SCALED
+        // one accumulator per segment: the whole unit, or one sample's share of it for EPI_STORE_SCALED
         while (ks < ks1 && ok) {
           const int seg_begin = ks;
-          const int seg_end = (EPI == EPI_STORE_SCALED) ? ks + args.seg_stages : ks1;
+          const int seg_end = (EPI == EPI_STORE_SCALED) ? segment_end(ks, ks1) : ks1;
           const int acc = it % NUM_ACC;
           const uint32_t acc_phase = (it / NUM_ACC) & 1u;
-          if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, args.status, 2)) { ok = false; break; }
+          if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, wctx, 2)) { ok = false; break; }
           tc_fence_after();
           for (; ks < seg_end; ++ks) {
-            if (!mbar_wait(full_bar(stage), phase, abort_flag, args.status, 3)) { ok = false; break; }
+            if (!mbar_wait(full_bar(stage), phase, wctx, 3)) { ok = false; break; }
             tc_fence_after();
             const bool second = (EPI == EPI_GRAM) && ks >= args.k_stages;
             const uint32_t d = tmem_base + (EPI == EPI_GRAM ? (second ? BN : 0) : acc * BN);
@@ -465,7 +469,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 #pragma unroll
             for (int k16 = 0; k16 < BK / UMMA_K; ++k16) {
               if (CTAS == 1)
-                tc_mma(d, operand_desc<A_MN>(sa, k16), operand_desc<B_MN>(sb + b_off, k16), idesc,
+                tc_mma(d, operand_desc<A_MN>(sa, k16), operand_desc<B_MN>(sb, k16), idesc,
                        (first_stage && k16 == 0) ? 0u : 1u);
               else
                 tc_mma_pair(d, operand_desc<A_MN>(sa, k16), operand_desc<B_MN>(sb, k16), idesc,
@@ -502,45 +506,63 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // ================= epilogue: warps 2.., TMEM lane quarter = warp % 4 =================
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
+    const int ew = warp - 2;
     int it = 0;
     bool ok = true;
-    int nsub = 1;
-    for (int round = 0, sub = 0; ok; (++sub >= nsub) ? (void)(sub = 0, ++round) : (void)0) {
-      const int u = wid + round * wstep;
-      if (u >= total_units) break;
+    if (EPI == EPI_STORE_SCALED && args.norm_partials != nullptr) {
+      // clip factors of all samples from the norm pass's partial sums (fixed order: a lane adds every
+      // 32nd partial, then the shuffle tree), while the producer and MMA warps start the main loop
+      for (int b = ew; b < args.segs; b += EPI_WARPS) {
+        const float* pp = args.norm_partials + static_cast<size_t>(b) * args.norm_nparts;
+        float sq = 0.f;
+        for (int i = lane; i < args.norm_nparts; i += 32) sq += pp[i];
+        sq = warp_sum(sq);
+        if (lane == 0) {
+          const float n = sqrtf(fmaxf(sq, 0.f));
+          const float f = clip_factor(n, args.C, args.clamp);
+          sfac[b] = f;
+          if (blockIdx.x == 0) {
+            if (args.norms_out != nullptr) args.norms_out[b] = n;
+            if (args.factors_out != nullptr) args.factors_out[b] = f;
+          }
+        }
+      }
+      asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight epilogue warps
+    }
+    for (int u = wid; u < total_units && ok; u += wstep) {
       int tile, ks0, ks1, slot, b, m0, n0, half;
-      if (EPI == EPI_GRAM) { gram_unit(u, sub, nsub, tile); ks0 = 0; ks1 = kst_total; slot = -1; }
-      else decode_unit(u, tile, ks0, ks1, slot);
+      decode_unit(u, tile, ks0, ks1, slot);
       decode(tile, b, m0, n0, half);
       const int m = m0 + row;
       if (EPI == EPI_STORE_SCALED) {
         // eight warps: two per lane quarter, each owning 128 of the tile's 256 columns in registers
-        const int half = (warp - 2) >> 2;
+        const int chalf = ew >> 2;
         float accr[128];
 #pragma unroll
         for (int i = 0; i < 128; ++i) accr[i] = 0.f;
-        // Whole tiles take their Gaussian noise into the accumulators a few element groups per
-        // sample segment, in the time these warps would otherwise wait for the next segment's
-        // MMAs; K-split parts stay noise-free (the fix-up kernel adds the noise once per tile).
-        const bool pre_noise = slot < 0 && args.nk.std != 0.f && (args.ld_out & 3) == 0 && m < args.M;
-        const uint64_t g0 = (static_cast<uint64_t>(m) * args.ld_out + n0 + half * 128) >> 2;
-        const float unscale = 1.f / args.scale;
-        const int nseg = (ks1 - ks0 + args.seg_stages - 1) / args.seg_stages;
+        // A whole tile's Gaussian noise goes into the accumulators a few element groups per sample
+        // segment, in the time these warps would otherwise wait for the next segment's MMAs; K-split
+        // parts stay noise-free (the fix-up kernel adds the noise once per tile).
+        const bool pre_noise = slot < 0 && args.nk.std != 0.f && m < args.M;
+        const uint64_t g0 = (static_cast<uint64_t>(m) * args.ld_out + n0 + chalf * 128) >> 2;
+        const int nseg = (ks1 - 1) / args.seg_stages - ks0 / args.seg_stages + 1;
         int ng = 0, seg = 0;
-        for (int ks = ks0; ks < ks1 && ok; ks += args.seg_stages, ++it) {
+        for (int ks = ks0; ks < ks1 && ok; ks = segment_end(ks, ks1), ++it) {
           const int acc = it % NUM_ACC;
           const uint32_t acc_phase = (it / NUM_ACC) & 1u;
-          if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, args.status, 4)) { ok = false; break; }
+          if (!mbar_wait_warp(tfull_bar(acc), acc_phase, wctx, 4)) { ok = false; break; }
           tc_fence_after();
-          const float cb = __ldg(args.factors + ks / args.seg_stages);
-          const uint32_t tb = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + half * 128;
+          const int sample = ks / args.seg_stages;
+          // the divisor goes into the factor, so the noise is added as it is drawn
+          const float cbs = (args.norm_partials != nullptr ? sfac[sample] : __ldg(args.factors + sample)) * args.scale;
+          const uint32_t tb = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + chalf * 128;
 #pragma unroll
           for (int c4 = 0; c4 < 4; ++c4) {
             uint32_t r[32];
             tc_ld32(tb + c4 * 32, r);
             tc_wait_ld();
 #pragma unroll
-            for (int j = 0; j < 32; ++j) accr[c4 * 32 + j] = fmaf(cb, __uint_as_float(r[j]), accr[c4 * 32 + j]);
+            for (int j = 0; j < 32; ++j) accr[c4 * 32 + j] = fmaf(cbs, __uint_as_float(r[j]), accr[c4 * 32 + j]);
           }
           tc_fence_before();
           __syncwarp();
@@ -554,35 +576,36 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             for (; ng < target; ++ng) {
               float z[4];
               noise_group(args.nk, g0 + ng, z);
-              add_group(accr, ng, z, unscale);
+              add_group(accr, ng, z, 1.0f);
             }
           }
         }
         if (!ok) break;
-        if (slot >= 0) {
-          float4* dst = reinterpret_cast<float4*>(args.split_ws + ((static_cast<size_t>(slot) * CTAS + cta_rank) * BM + row) * BN + half * 128);
-#pragma unroll
-          for (int j = 0; j < 32; ++j)
-            dst[j] = make_float4(accr[4 * j], accr[4 * j + 1], accr[4 * j + 2], accr[4 * j + 3]);
-        } else {
+        if (slot < 0) {
 #pragma unroll
           for (int c4 = 0; c4 < 4; ++c4) {
             float v[32];
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = accr[c4 * 32 + j] * args.scale;
-            store_chunk32(args, v, m, n0 + half * 128 + c4 * 32, !pre_noise);
+            for (int j = 0; j < 32; ++j) v[j] = accr[c4 * 32 + j];
+            store_chunk32<false>(args, v, m, n0 + chalf * 128 + c4 * 32);
           }
+        } else {
+          // park this part (already divided by the batch) for the fix-up kernel
+          float4* dst = reinterpret_cast<float4*>(args.split_ws + ((static_cast<size_t>(slot) * CTAS + cta_rank) * BM + row) * BN + chalf * 128);
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            dst[j] = make_float4(accr[4 * j], accr[4 * j + 1], accr[4 * j + 2], accr[4 * j + 3]);
         }
         continue;
       }
       const int acc = it % NUM_ACC;
       const uint32_t acc_phase = (it / NUM_ACC) & 1u;
-      if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, args.status, 4)) { ok = false; break; }
+      if (!mbar_wait_warp(tfull_bar(acc), acc_phase, wctx, 4)) { ok = false; break; }
       tc_fence_after();
       const uint32_t tbase = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (EPI == EPI_GRAM ? 0 : acc * BN);
       float part = 0.f;
       if (EPI == EPI_STORE && slot >= 0) {
-        // K-split unit: park the raw accumulator; the fix-up kernel adds the parts in fixed order
+        // K-split unit: park the raw accumulator for the fix-up kernel
         float4* dst = reinterpret_cast<float4*>(args.split_ws + ((static_cast<size_t>(slot) * CTAS + cta_rank) * BM + row) * BN);
 #pragma unroll 1
         for (int c = 0; c < BN; c += 32) {
@@ -603,7 +626,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           float v[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * args.scale;
-          store_chunk32(args, v, m, n0 + c);
+          store_chunk32<true>(args, v, m, n0 + c);
         }
       } else if (EPI == EPI_SUMSQ) {
         // rows / columns outside the matrix were zero-filled by TMA, so they add nothing
@@ -648,14 +671,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       }
       ++it;
       if (EPI == EPI_SUMSQ || EPI == EPI_GRAM) {
+        // one partial per (unit, epilogue warp); units are numbered sample by sample
         part = warp_sum(part);
-        if (lane == 0) red[quarter] = part;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (warp == 2 && lane == 0) {
-          const int pslot = tile;  // tiles are numbered sample by sample
-          args.partials[pslot] = (red[0] + red[1]) + (red[2] + red[3]);
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (lane == 0) args.partials[static_cast<size_t>(tile) * 4 + quarter] = part;
       }
     }
   }
@@ -674,7 +692,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   }
 }
 
-// ---- split-K fix-up: out = scale * (part_0 + part_1 + ...) + noise for the tiles of the tail wave ------
+// ---- split-K fix-up: out = scale * (part_0 + part_1 + ...) + noise for the K-split tiles --------------
 __global__ void __launch_bounds__(256) splitk_fixup_kernel(const float* __restrict__ ws, int first_tile, int split,
                                                            int tile_rows, int M, int N, int tiles_m, int tiles_n, int n_fastest,
                                                            int m_group,
@@ -705,14 +723,10 @@ __global__ void __launch_bounds__(256) splitk_fixup_kernel(const float* __restri
   }
   float v[4] = {acc.x * scale, acc.y * scale, acc.z * scale, acc.w * scale};
   const size_t idx0 = static_cast<size_t>(m) * ld_out + n;
-  if (nk.std != 0.f) {
-    if ((idx0 & 3) == 0) {
-      float z[4];
-      noise_group(nk, idx0 >> 2, z);
-      v[0] += z[0]; v[1] += z[1]; v[2] += z[2]; v[3] += z[3];
-    } else {
-      for (int j = 0; j < 4; ++j) v[j] += noise_at(nk, idx0 + j);
-    }
+  if (nk.std != 0.f) {   // idx0 is a multiple of 4: the row pitch and n are
+    float z[4];
+    noise_group(nk, idx0 >> 2, z);
+    v[0] += z[0]; v[1] += z[1]; v[2] += z[2]; v[3] += z[3];
   }
   for (int j = 0; j < 4; ++j)
     if (n + j < N) store_as(out, out_dt, idx0 + j, v[j]);
@@ -784,25 +798,32 @@ uint32_t make_idesc(int dt, bool a_mn, bool b_mn, int ctas = 1, int n = BN) {
   return d;
 }
 
-// SMs the persistent GEMM grids may occupy.  FDP_TC_RESERVE_SMS=n leaves n SMs free, e.g. for the
-// NCCL kernels of a data-parallel job: a persistent CTA holds a whole SM's shared memory, so a
-// collective launched beside it cannot start until SMs are free.
+// SMs of the current device (cached per device).
 int sm_count() {
   static std::mutex mu;
   static int cache[64];
   static bool have[64];
-  static const int reserve = [] { const char* e = getenv("FDP_TC_RESERVE_SMS"); return e ? atoi(e) : 0; }();
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return 148; }
   std::lock_guard<std::mutex> lk(mu);
   if (!have[dev]) {
     int n = 148;
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) { cudaGetLastError(); n = 148; }
-    if (reserve > 0 && n - reserve >= 16) n -= reserve;
-    n &= ~1;  // CTA pairs
     cache[dev] = n; have[dev] = true;
   }
   return cache[dev];
+}
+// SMs the next persistent GEMM grid may occupy: all of them minus the current reservation
+// (fdp_set_sm_reserve; FDP_TC_RESERVE_SMS is its initial value).  A persistent CTA holds a whole SM's
+// shared memory, so a collective kernel launched beside such a grid cannot start until SMs are free;
+// a caller that overlaps a GEMM with a collective reserves a few SMs for the duration of that call.
+std::atomic<int> g_sm_reserve{[] { const char* e = getenv("FDP_TC_RESERVE_SMS"); return e ? atoi(e) : 0; }()};
+int launch_sms() {
+  int n = sm_count();
+  const int reserve = g_sm_reserve.load(std::memory_order_relaxed);
+  if (n > MAX_SMS) n = MAX_SMS;   // the parking area is sized for MAX_SMS workers
+  if (reserve > 0 && n - reserve >= 16) n -= reserve;
+  return n & ~1;  // CTA pairs
 }
 
 template <bool A_MN, bool B_MN, int EPI, int CTAS = 1>
@@ -810,20 +831,22 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, co
            const TcArgs& args, cudaStream_t s) {
   static std::mutex mu;
   static bool done[64];
-  if (!smem_opt_in(done, mu, tc_gemm_kernel<A_MN, B_MN, EPI, CTAS>, SMEM_BYTES)) return FDP_ERR_LAUNCH;
+  constexpr int SMEM = smem_for(EPI);
+  if (!smem_opt_in(done, mu, tc_gemm_kernel<A_MN, B_MN, EPI, CTAS>, SMEM)) return FDP_ERR_LAUNCH;
   TcArgs la = args;
+  la.sticky = sticky_status_slot();
   const int total = la.batch * la.tiles_per_batch;
   if (la.split <= 1) { la.split = 1; la.units_full = total; }
   int units = la.units_full + (total - la.units_full) * la.split;
-  const int workers = sm_count() / CTAS;   // CTAs, or CTA pairs
+  const int workers = launch_sms() / CTAS;   // CTAs, or CTA pairs
   const int grid = CTAS * (units < workers ? units : workers);
   if (CTAS == 1) {
-    tc_gemm_kernel<A_MN, B_MN, EPI, CTAS><<<grid, threads_for(EPI), SMEM_BYTES, s>>>(a, b, a2, b2, la);
+    tc_gemm_kernel<A_MN, B_MN, EPI, CTAS><<<grid, threads_for(EPI), SMEM, s>>>(a, b, a2, b2, la);
   } else {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(threads_for(EPI));
-    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.dynamicSmemBytes = SMEM;
     cfg.stream = s;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -844,37 +867,49 @@ int ctas_per_tile() {
   return v;
 }
 
-// K-split of the tail wave: `rem` tiles left after the full waves are cut into s parts each so that
-// the last round keeps more SMs busy; cost in tile-times = ceil(rem*s/sms)/s.  At most 2*sms units.
-int plan_tail_split(int total_tiles, int k_stages, int sms) {
-  if (total_tiles <= sms) {
-    // fewer tiles than SMs: one partial wave
-    if (k_stages < 64) return 1;
-    int best_s = 1; double best = 1.0;
-    for (int sp = 2; sp <= 8; ++sp) {
-      if (total_tiles * sp > 2 * sms || k_stages / sp < 16) break;
-      const double cost = static_cast<double>((total_tiles * sp + sms - 1) / sms) / sp;
-      if (cost < best - 0.05) { best = cost; best_s = sp; }
-    }
-    return best_s;
-  }
-  const int rem = total_tiles % sms;
-  if (rem == 0 || k_stages < 64) return 1;
+// K-split of the tail wave: `rem` tiles left after the full waves (all of them when there are fewer
+// tiles than workers) are cut into s parts of equal K-stage count, so that the last round keeps more
+// SMs busy; cost in tile-times = ceil(rem*s/workers)/s plus a fixed cost per extra part for parking
+// and re-reading the accumulators.  At most 2 * workers parked parts (workers <= MAX_SMS / CTAS).
+int plan_tail_split(int total_tiles, int k_stages, int workers) {
+  const int rem = total_tiles <= workers ? total_tiles : total_tiles % workers;
+  if (rem == 0 || k_stages < 32) return 1;
   int best_s = 1; double best = 1.0;
-  for (int sp = 2; sp <= 8; ++sp) {
-    if (rem * sp > 2 * sms || k_stages / sp < 16) break;
-    const double cost = static_cast<double>((rem * sp + sms - 1) / sms) / sp;
-    if (cost < best - 0.05) { best = cost; best_s = sp; }
+  for (int sp = 2; sp <= 16; ++sp) {
+    if (rem * sp > 2 * workers || k_stages / sp < 8) break;
+    const double cost = static_cast<double>((rem * sp + workers - 1) / workers) / sp + 0.02 * sp;
+    if (cost < best - 0.03) { best = cost; best_s = sp; }
   }
   return best_s;
 }
-// up to 2*SMs parked 128-row accumulators (a CTA pair parks two per slot)
-size_t split_ws_bytes() { return static_cast<size_t>(2) * sm_count() * BM * BN * sizeof(float); }
+// parked accumulators: up to 2 * MAX_SMS parts of 128 x 256 fp32 (a CTA pair parks two per part)
+size_t split_ws_bytes() { return static_cast<size_t>(2) * MAX_SMS * BM * BN * sizeof(float); }
 size_t align256(size_t n) { return (n + 255) & ~static_cast<size_t>(255); }
 
 int gram_tiles(int T) { return gram_units(ceil_div(T, BM)); }   // work units (128 x 256 tiles) per sample
 
+// A warp waits on a barrier nobody arrives on, so the wait runs out after `limit` cycles and takes the
+// reporting path of every bounded wait of the library: abort flag, status word, host-visible slot.
+__global__ void __launch_bounds__(32) wait_selftest_kernel(int* status, int* sticky, long long limit) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) { mbar_init(smem_u32(&bar), 1); abort_flag = 0; mbar_fence_init(); }
+  __syncwarp();
+  const WaitCtx w{&abort_flag, status, sticky, limit};
+  mbar_wait_warp(smem_u32(&bar), 0, w, 9);
+}
+
 }  // namespace
+
+int sm_reserve_exchange(int n) { return g_sm_reserve.exchange(n < 0 ? 0 : n); }
+
+int tc_wait_selftest(int* status, long long limit_cycles, cudaStream_t s) {
+  if (limit_cycles < 1) limit_cycles = 1;
+  if (limit_cycles > WAIT_LIMIT_CYCLES) limit_cycles = WAIT_LIMIT_CYCLES;
+  wait_selftest_kernel<<<1, 32, 0, s>>>(status, sticky_status_slot(), limit_cycles);
+  note_launch();
+  return cudaPeekAtLastError() == cudaSuccess ? FDP_OK : (cudaGetLastError(), FDP_ERR_LAUNCH);
+}
 
 // The tensor-core path needs 16-bit inputs, row pitches that are multiples of 16 bytes, and
 // matrices large enough that the 128x256 tile is not mostly padding.
@@ -913,7 +948,8 @@ TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo) {
   // FDP_WGRAD_PRESCALE=1 forces the pre-scale pass (for A/B measurements)
   static const bool force_prescale = [] { const char* e = getenv("FDP_WGRAD_PRESCALE"); return e && e[0] == '1'; }();
   p.scaled_epilogue = !force_prescale && (T % BK == 0) && T >= 256;
-  p.nparts = (algo == FDP_NORM_DIRECT) ? ceil_div(n_out, BM) * ceil_div(n_in, BN) : gram_tiles(T);
+  // one partial per work unit and epilogue warp
+  p.nparts = 4 * ((algo == FDP_NORM_DIRECT) ? ceil_div(n_out, BM) * ceil_div(n_in, BN) : gram_tiles(T));
   // the parked accumulators of the split-K tail, then (pre-scale path only) the c_b-scaled copy of G
   p.split_bytes = split_ws_bytes();
   p.ws_bytes = p.split_bytes + (p.scaled_epilogue ? 0 : align256(static_cast<size_t>(B) * T * n_out * 2));
@@ -961,11 +997,13 @@ int tc_prescale(const void* G, const float* factors, void* Gs, int B, int T, int
   return FDP_OK;
 }
 
-int tc_clipped_wgrad(const void* Gs, const void* X, const float* factors, float* split_ws, void* dW,
-                     int* dev_status, int B, int T, int n_in, int n_out, int dt, int out_dt, int layout,
-                     float inv_div, NoiseKey nk, cudaStream_t s) {
+bool tc_fused_factors_ok(int B) { return B <= MAX_SMEM_FACTORS; }
+
+int tc_clipped_wgrad(const void* Gs, const void* X, const TcFactorSource* fs, float* split_ws,
+                     void* dW, int* dev_status, int B, int T, int n_in, int n_out, int dt, int out_dt,
+                     int layout, float inv_div, NoiseKey nk, cudaStream_t s) {
   const uint64_t rows = static_cast<uint64_t>(B) * T;
-  const bool scaled = factors != nullptr;  // Gs is then the unscaled G
+  const bool scaled = fs != nullptr;  // Gs is then the unscaled G
   CUtensorMap mg, mx;
   if (!make_map(&mg, Gs, rows, n_out, 64, BK, dt) || !make_map(&mx, X, rows, n_in, 64, BK, dt)) return FDP_ERR_LAUNCH;
   TcArgs args{};
@@ -974,7 +1012,16 @@ int tc_clipped_wgrad(const void* Gs, const void* X, const float* factors, float*
   args.out = dW; args.out_dt = out_dt; args.scale = inv_div; args.nk = nk;
   const int ctas = ctas_per_tile();
   args.idesc = make_idesc(dt, true, true, ctas);
-  if (scaled) { args.factors = factors; args.segs = B; args.seg_stages = T / BK; }
+  if (scaled) {
+    args.segs = B; args.seg_stages = T / BK;
+    args.factors = fs->factors;
+    if (fs->factors == nullptr) {
+      if (!tc_fused_factors_ok(B) || fs->norm_partials == nullptr) return FDP_ERR_ARG;
+      args.norm_partials = fs->norm_partials; args.norm_nparts = fs->nparts;
+      args.C = fs->C; args.clamp = fs->clamp;
+      args.norms_out = fs->norms_out; args.factors_out = fs->factors_out;
+    }
+  }
   // [out,in]: A = G (M = n_out), B = X (N = n_in); [in,out]: operands swap roles, no transpose pass
   const bool oi = (layout == FDP_OUT_IN);
   args.M = oi ? n_out : n_in; args.N = oi ? n_in : n_out; args.ld_out = args.N;
@@ -982,11 +1029,10 @@ int tc_clipped_wgrad(const void* Gs, const void* X, const float* factors, float*
   args.tiles_per_batch = args.tiles_m * args.tiles_n;
   static const int m_group = [] { const char* e = getenv("FDP_TC_MGROUP"); return e ? atoi(e) : 8; }();
   args.m_group = m_group;
-  // tail wave: split K so the SMs left idle by the tile count get work; parts are parked in the
+  // tail wave: split K so the SMs left idle by the tile count get work; the parts are parked in the
   // workspace and summed in fixed order by the fix-up kernel (deterministic, no waits)
-  const int total = args.tiles_per_batch, workers = sm_count() / ctas;
-  int split = plan_tail_split(total, args.k_stages, workers);
-  if (scaled && split > B) split = B;   // the scaled kernel cuts between samples
+  const int total = args.tiles_per_batch, workers = launch_sms() / ctas;
+  const int split = plan_tail_split(total, args.k_stages, workers);
   int n_split_tiles = 0;
   if (split > 1) {
     n_split_tiles = total <= workers ? total : total % workers;
@@ -1001,10 +1047,11 @@ int tc_clipped_wgrad(const void* Gs, const void* X, const float* factors, float*
   else st = ctas == 2 ? FDP_WGRAD_LAUNCH(EPI_STORE, 2) : FDP_WGRAD_LAUNCH(EPI_STORE, 1);
 #undef FDP_WGRAD_LAUNCH
   if (st != FDP_OK || split <= 1) return st;
+  // the scaled epilogue parks its parts already divided by the batch
   dim3 grid(BM * ctas * BN / (256 * 4), n_split_tiles);
   splitk_fixup_kernel<<<grid, 256, 0, s>>>(args.split_ws, args.units_full, split, BM * ctas, args.M, args.N,
                                            args.tiles_m, args.tiles_n, args.n_fastest, args.m_group, dW, out_dt,
-                                           args.ld_out, inv_div, nk);
+                                           args.ld_out, scaled ? 1.0f : inv_div, nk);
   note_launch();
   return FDP_OK;
 }

@@ -4,8 +4,10 @@ The reference knows one GPU (example/gpt2/train.py:33) and has no collective.  S
 independent, so each rank runs the DP backward on its own B_local samples with
 divisor = world * B_local and noise std = noise_multiplier / sqrt(world * B_local), drawing only the
 element groups it owns; ONE all-reduce (SUM) of each DP gradient then yields exactly what a single
-GPU would compute on the concatenated batch, noise included -- bit-identical noise for any world
-size.  Parameters without the `requires_dp` flag carry ordinary local-mean gradients and are
+GPU would compute on the concatenated batch, noise included: element i's noise is the same draw
+z_i(seed, param_id, step) for any world size, added by exactly one rank (the gradient it is added to
+is an fp32 sum whose association differs with the sharding, so whole results agree to rounding, not
+bit for bit).  Parameters without the `requires_dp` flag carry ordinary local-mean gradients and are
 averaged instead.
 
     reducer = DPGradReducer(model)          # after wrap_with_flashdp_layers, on every rank
@@ -37,9 +39,15 @@ def direct_reducer(param):
 
 
 def init_data_parallel(group=None):
-    """Read rank / world size from the (already initialised) process group."""
+    """Read rank / world size from the (already initialised) process group and give every rank
+    rank 0's noise seed (the ranks draw disjoint parts of ONE noise tensor, which is reproducible
+    across world sizes only under a common key)."""
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     runtime.set_data_parallel(rank, world)
+    if world > 1:
+        box = [runtime.get_seed()]
+        dist.broadcast_object_list(box, src=dist.get_global_rank(group, 0) if group is not None else 0, group=group)
+        runtime.manual_seed(box[0])
     return rank, world
 
 
@@ -81,6 +89,7 @@ class DPGradReducer:
         self._inflight = {}
         self._hooks = []
         self._sync = True
+        self._reserve_prev = None
         self._claimed, self._counted = set(), set()
         self._flat, self._views = [], {}
         if self.as_view:
@@ -166,8 +175,17 @@ class DPGradReducer:
                 sc = self._scale(p, self.world)
                 parts.append((p.grad if sc == 1.0 else p.grad * sc).reshape(-1))
             flat = torch.cat(parts)
+        if not self._inflight and self.world > 1 and flat.is_cuda:
+            # from the first collective of this step until finish(): the library's GEMM grids leave a
+            # few SMs free so the all-reduce kernels run beside them instead of behind them
+            self._reserve_prev = self._set_reserve(runtime.reserve_sms())
         work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
         self._inflight[i] = (work, flat, bucket)
+
+    @staticmethod
+    def _set_reserve(n):
+        from . import _lib
+        return _lib.load().fdp_set_sm_reserve(int(n))
 
     def _attach_views_of(self, i):
         """Make every gradient of bucket i a view of its flat buffer; a gradient that autograd
@@ -209,6 +227,11 @@ class DPGradReducer:
                     n = p.numel()
                     p.grad.copy_(flat[off:off + n].view_as(p.grad))
                     off += n
+        if self._reserve_prev is not None:
+            self._set_reserve(self._reserve_prev)
+            self._reserve_prev = None
+        if self.params and self.params[0].is_cuda:
+            runtime.check_device_status(self.params[0].device.index)
         self._inflight = {}
         self._pending = [len(b) for b in self.buckets]
         self._counted.clear()

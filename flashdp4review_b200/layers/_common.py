@@ -17,7 +17,7 @@ class DPLayerMixin:
 
     def _next_step(self):
         self._dp_step += 1
-        return self._dp_step
+        return runtime.noise_step(self._dp_step)
 
 
 def reshape_to_3d(input, grad_output):

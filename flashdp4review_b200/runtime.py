@@ -13,9 +13,15 @@ _ids = itertools.count(1)
 
 
 class _Run:
-    seed = 0
+    # Philox key of the noise.  Drawn from the OS by default: a fixed default would make the noise of
+    # every run a publicly computable function of (construction order, step).  manual_seed() fixes it.
+    seed = int.from_bytes(os.urandom(8), "little")
+    step_base = 0                 # added to every layer's own backward counter (see noise_state)
+    step_high = 0                 # largest step value any layer has drawn noise with so far
     world = 1
     rank = 0
+    # SMs the persistent GEMM grids leave free while a gradient all-reduce is in flight (world > 1)
+    reserve_sms = int(os.environ.get("FDP_DP_RESERVE_SMS", "8"))
     input_grad_impl = "library"   # "library": cuBLAS via torch (as the reference); "native": fdp_linear_dgrad
     micro_index = 0               # gradient accumulation: which micro-step of `micro_steps` runs now
     micro_steps = 1
@@ -33,6 +39,30 @@ def get_seed() -> int:
     return _run.seed
 
 
+def noise_step(local_count: int) -> int:
+    """Philox step word of a layer's `local_count`-th backward: the run's base plus the layer's own
+    counter, so that after `set_noise_state` no (parameter, step) pair of the earlier run recurs."""
+    step = (_run.step_base + int(local_count)) & 0xFFFFFFFF
+    if step > _run.step_high:
+        _run.step_high = step
+    return step
+
+
+def noise_state() -> dict:
+    """What a checkpoint must keep beside the model and optimizer state for the DP noise: the seed
+    and the highest step drawn so far.  Without it a resumed run would count its layers' steps from
+    zero again and, under the same seed, repeat the noise tensors of steps 1..N exactly -- noise an
+    observer of both runs could cancel."""
+    return {"seed": _run.seed, "step": _run.step_high}
+
+
+def set_noise_state(state: dict):
+    """Resume: same seed, and every layer's step counter continues above the saved high-water mark."""
+    _run.seed = int(state["seed"])
+    _run.step_base = int(state["step"])
+    _run.step_high = max(_run.step_high, _run.step_base)
+
+
 def set_data_parallel(rank: int, world: int):
     """Declare that the batch each DP layer sees is one of `world` equal shards.
 
@@ -44,11 +74,43 @@ def set_data_parallel(rank: int, world: int):
     if world < 1 or not (0 <= rank < world):
         raise ValueError(f"bad data-parallel layout rank={rank} world={world}")
     _run.rank, _run.world = int(rank), int(world)
-    if world > 1:
-        # The persistent GEMM grids otherwise take every SM (a CTA holds an SM's whole shared memory) and
-        # the NCCL kernels of the gradient all-reduce cannot start beside them.  Leaving a dozen SMs free
-        # measured +5 % on 8 GPUs.  The library reads this once, at its first tensor-core launch.
-        os.environ.setdefault("FDP_TC_RESERVE_SMS", "12")
+
+
+def reserve_sms() -> int:
+    """SMs to leave free for the collective kernels while an all-reduce overlaps GEMMs."""
+    return _run.reserve_sms if _run.world > 1 else 0
+
+
+@contextlib.contextmanager
+def sm_reservation(n=None):
+    """`with sm_reservation():` -- the library's persistent GEMM grids launched inside the block leave
+    `n` SMs free (default: reserve_sms()), so that a collective kernel launched beside them can run.
+    A persistent CTA holds a whole SM's shared memory; without the reservation the all-reduce of one
+    layer's gradient could not start before the next GEMM has ended.  Outside such a block the grids
+    take every SM."""
+    from . import _lib
+    n = reserve_sms() if n is None else int(n)
+    lib = _lib.load()
+    prev = lib.fdp_set_sm_reserve(n)
+    try:
+        yield
+    finally:
+        lib.fdp_set_sm_reserve(prev)
+
+
+def check_device_status(device=-1):
+    """Raise RuntimeError if a kernel of the library reported, since the last check, that one of its
+    bounded waits ran out (its outputs are then undefined).  A host read, no synchronisation: it sees
+    what the GPU has reported so far, so call it once per step before the optimizer uses the gradients
+    (DPGradReducer.finish does).  The flag stays up, and every library call on that device fails,
+    until clear_device_status()."""
+    from . import _lib
+    _lib.check(_lib.load().fdp_async_status(int(device)), "device status")
+
+
+def clear_device_status(device=-1):
+    from . import _lib
+    _lib.load().fdp_clear_async_status(int(device))
 
 
 def data_parallel():

@@ -5,7 +5,16 @@
  * tensors, sizes, and the CUDA stream to launch on.  Nothing here allocates device memory,
  * synchronises the host or throws: the caller passes a workspace whose size the matching
  * `*_workspace_bytes` query returns, and reads a status code (0 = FDP_OK, negative = error;
- * `fdp_status_string` names it).  Inputs are never modified.
+ * `fdp_status_string` names it).  Inputs are never modified.  (The first call of a process pins
+ * one 256-byte block of host memory for the asynchronous status described below.)
+ *
+ * Asynchronous errors: the only device-side failure the kernels can report is a bounded wait that
+ * ran out (an mbarrier that never completed within about a second).  The kernel then stops early
+ * -- the outputs of that call are undefined -- and records a code in the call's workspace and in a
+ * host-visible word of its device.  Like a CUDA asynchronous error it surfaces on a LATER call:
+ * every compute entry point first looks at that word (a plain host read, no synchronisation) and
+ * returns FDP_ERR_TIMEOUT while it is set; fdp_async_status polls it, fdp_clear_async_status
+ * re-arms the device.  A training loop should poll once per step before using the gradients.
  *
  * The comments cite, as file:line inside the FlashDP4Review project, the Python-level
  * interface of the reference that each entry point takes the place of.
@@ -20,7 +29,7 @@
 extern "C" {
 #endif
 
-#define FDP_ABI_VERSION 1
+#define FDP_ABI_VERSION 2
 
 typedef void* fdp_stream_t; /* a cudaStream_t */
 
@@ -29,11 +38,12 @@ enum fdp_status {
   FDP_ERR_ARG = -1,       /* null pointer, non-positive size, bad enum */
   FDP_ERR_DTYPE = -2,     /* dtype not supported by this entry point */
   FDP_ERR_SHAPE = -3,     /* shape outside what the kernels cover */
-  FDP_ERR_ALIGN = -4,     /* pointer not 16-byte aligned */
+  FDP_ERR_ALIGN = -4,     /* a pointer the chosen kernel needs 16-byte aligned is not (16-bit inputs with
+                           * tensor-core shapes; the generic kernels take any naturally aligned pointer) */
   FDP_ERR_WORKSPACE = -5, /* workspace missing or too small */
   FDP_ERR_ARCH = -6,      /* device is not sm_100 */
   FDP_ERR_LAUNCH = -7,    /* CUDA reported a launch/runtime error */
-  FDP_ERR_TIMEOUT = -8,   /* a bounded device-side wait ran out (see fdp_device_status) */
+  FDP_ERR_TIMEOUT = -8,   /* a bounded device-side wait ran out, in this or an earlier call (fdp_async_status) */
   FDP_ERR_STATIC_LIMIT = -9 /* fdp_bias_grad_static: the problem needs more scratch than FDP_STATIC_SCRATCH_BYTES */
 };
 
@@ -74,10 +84,31 @@ const char* fdp_status_string(int status);
 /* 0 if device `device` can run the library (compute capability 10.x), else FDP_ERR_ARCH. */
 int fdp_check_device(int device);
 
-/* Reads the device-side status word that the tensor-core kernels keep at the start of the
- * workspace (0 = no bounded wait ran out).  Synchronises `stream`.  Returns FDP_OK,
- * FDP_ERR_TIMEOUT or FDP_ERR_LAUNCH. */
+/* Waits for `stream`, then reports whether a bounded wait ran out: reads the status word at the start
+ * of `workspace` (of fdp_linear_wgrad / fdp_linear_dgrad / fdp_linear_fwd; may be NULL) and the
+ * device's host-visible word.  Returns FDP_OK, FDP_ERR_TIMEOUT or FDP_ERR_LAUNCH. */
 int fdp_device_status(const void* workspace, fdp_stream_t stream);
+
+/* Non-blocking poll / reset of the host-visible status word of `device` (-1: the current device).
+ * No counterpart in the reference (its Triton kernels spin without a limit,
+ * flashdp/core/layernorm_clip.py:111). */
+int fdp_async_status(int device);
+int fdp_clear_async_status(int device);
+
+/* Test aid: launches one warp that waits `limit_cycles` GPU clock cycles (clamped to about a second)
+ * on a barrier nobody arrives on, so that the wait runs out and the reporting path above is taken:
+ * afterwards fdp_device_status(workspace, stream) and fdp_async_status return FDP_ERR_TIMEOUT.
+ * The kernel returns normally; nothing faults.  `workspace`: at least 256 bytes. */
+int fdp_selftest_wait_timeout(long long limit_cycles, void* workspace, size_t workspace_bytes,
+                              fdp_stream_t stream);
+
+/* SMs that the persistent GEMM grids launched after this call leave free (0 = use all); returns the
+ * previous value.  The grids otherwise occupy every SM, so a collective kernel (the all-reduce of
+ * the gradients in a data-parallel job) launched beside one cannot start before it ends: a caller
+ * sets a reservation around the calls it wants to overlap with a collective and clears it after.
+ * Process-wide; FDP_TC_RESERVE_SMS in the environment is the initial value.  No counterpart in the
+ * reference (single GPU, example/gpt2/train.py:33). */
+int fdp_set_sm_reserve(int n);
 
 /* ---- instrumentation (no counterpart in the reference, which only wall-clocks whole functions in
  * RuntimeAutoTuner._measure_time, flashdp/core/utils.py:42-47) ---------------------------------------

@@ -23,7 +23,7 @@ def ops():
 def test_library_loaded_and_device_ok():
     from flashdp4review_b200 import _lib
     lib = _lib.load()
-    assert lib.fdp_abi_version() == 1
+    assert lib.fdp_abi_version() == _lib.ABI_VERSION
     assert lib.fdp_check_device(0) == 0
 
 
@@ -213,7 +213,18 @@ def test_abi_status_codes():
     assert call(B=0) == _lib.FDP_ERR_ARG
     assert call(layout=5) == _lib.FDP_ERR_ARG
     assert call(dt=7) == _lib.FDP_ERR_DTYPE
-    assert call(G=t.data_ptr() + 4) == _lib.FDP_ERR_ALIGN
+    assert call(G=t.data_ptr() + 4) == _lib.FDP_OK            # generic kernels: single-element accesses
+    big = torch.zeros(2 * 64 * 256 + 8, device=dev(), dtype=torch.bfloat16)
+    tc = lambda off: lib.fdp_linear_wgrad(big.data_ptr() + off, big.data_ptr(), big.data_ptr(), None, None, 2, 64, 128,
+                                          256, _lib.FDP_BF16, _lib.FDP_BF16, 0, 0, ctypes.byref(p), ws.data_ptr(),
+                                          ws.numel(), None)
+    assert ws.numel() < lib.fdp_linear_wgrad_workspace_bytes(2, 64, 128, 256, _lib.FDP_BF16, 0)
+    assert tc(0) == _lib.FDP_ERR_WORKSPACE                   # tensor-core shape: needs its parking area
+    ws_tc = torch.empty(lib.fdp_linear_wgrad_workspace_bytes(2, 64, 128, 256, _lib.FDP_BF16, 0), dtype=torch.uint8, device=dev())
+    tc2 = lambda off: lib.fdp_linear_wgrad(big.data_ptr() + off, big.data_ptr(), big.data_ptr(), None, None, 2, 64, 128,
+                                           256, _lib.FDP_BF16, _lib.FDP_BF16, 0, 0, ctypes.byref(p), ws_tc.data_ptr(),
+                                           ws_tc.numel(), None)
+    assert tc2(4) == _lib.FDP_ERR_ALIGN                      # TMA operands must sit on 16-byte boundaries
     assert call(wsp=None) == _lib.FDP_ERR_WORKSPACE
     assert call(wsn=8) == _lib.FDP_ERR_WORKSPACE
     assert call(pp=None) == _lib.FDP_ERR_ARG
@@ -225,6 +236,58 @@ def test_abi_status_codes():
     with pytest.raises(RuntimeError):
         from flashdp4review_b200.core import ops
         ops.dp_linear_weight_grad(torch.zeros(1, 1, 8), torch.zeros(1, 1, 8), 1.0, 1.0)   # CPU tensors
+
+
+def test_views_with_a_storage_offset(ops):
+    """A contiguous view that starts off a 16-byte boundary (x[1:] of a 3-column fp32 tensor; a bf16
+    tensor-core shape shifted by one row of 8 bytes): the generic kernels read it in place, the
+    tensor-core path gets an aligned copy from the operator layer."""
+    gen = torch.Generator().manual_seed(4)
+    Xf = torch.randn(5, 6, 3, generator=gen)
+    Gf = torch.randn(5, 6, 5, generator=gen) * 0.1
+    got = ops.dp_linear_weight_grad(Xf.to(dev())[1:], Gf.to(dev())[1:], 0.5, 1.0)
+    want, _ = O.linear_weight_grad(Gf[1:], Xf[1:], 0.5, 1.0)
+    assert rel_err(got.cpu().numpy(), want) < 1e-5
+    Xb = torch.randn(3 * 64 * 132 + 4, generator=gen).to(torch.bfloat16)
+    Gb = (torch.randn(3 * 64 * 136 + 4, generator=gen) * 0.01).to(torch.bfloat16)
+    xv = Xb.to(dev())[4:].view(3, 64, 132)[:, :, :128].contiguous()
+    gv = Gb.to(dev())[4:].view(3, 64, 136)
+    assert gv.data_ptr() % 16 == 8
+    got = ops.dp_linear_weight_grad(xv, gv, 0.05, 1.0, out_dtype=torch.float32)
+    want, _ = O.linear_weight_grad(gv.cpu(), xv.cpu(), 0.05, 1.0)
+    assert rel_err(got.cpu().numpy(), want) < 1e-2
+
+
+def test_bounded_wait_that_runs_out_is_reported_and_sticky():
+    """A one-warp kernel waits about a millisecond on a barrier nobody arrives on.  It must return
+    normally, leave its code in the workspace word and in the device's host-visible word, make every
+    later compute call fail with FDP_ERR_TIMEOUT (RuntimeError in Python) until the flag is cleared,
+    and leave the device fully usable."""
+    from flashdp4review_b200 import _lib, runtime
+    from flashdp4review_b200.core import ops
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    ws = torch.zeros(256, dtype=torch.uint8, device=dev())
+    assert lib.fdp_async_status(-1) == _lib.FDP_OK
+    try:
+        assert lib.fdp_selftest_wait_timeout(2_000_000, ws.data_ptr(), ws.numel(), stream) == _lib.FDP_OK
+        assert lib.fdp_device_status(ws.data_ptr(), stream) == _lib.FDP_ERR_TIMEOUT
+        assert int(ws[:4].view(torch.int32).item()) == 9
+        assert lib.fdp_async_status(-1) == _lib.FDP_ERR_TIMEOUT
+        with pytest.raises(RuntimeError, match="bounded device-side wait"):
+            runtime.check_device_status()
+        X = torch.zeros(2, 4, 8, device=dev())
+        with pytest.raises(RuntimeError, match="bounded device-side wait"):
+            ops.dp_linear_weight_grad(X, X, 1.0, 1.0)
+        with pytest.raises(RuntimeError, match="bounded device-side wait"):
+            ops.dp_bias_grad(X, 1.0, 1.0)
+    finally:
+        runtime.clear_device_status()
+    assert lib.fdp_async_status(-1) == _lib.FDP_OK
+    X, G, _ = O.make_linear_inputs(2, 64, 128, 128, 1e-2, seed=3, dtype=torch.bfloat16)
+    got = ops.dp_linear_weight_grad(X.to(dev()), G.to(dev()), 0.05, 1.0, out_dtype=torch.float32)
+    want, _ = O.linear_weight_grad(G, X, 0.05, 1.0)
+    assert rel_err(got.cpu().numpy(), want) < 1e-2
 
 
 def test_bmm_clip_and_per_token_mm_clip(ops):

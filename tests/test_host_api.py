@@ -19,7 +19,7 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in include/fdp_b200.h but not exported"
     assert declared == set(_lib.SIGNATURES), declared ^ set(_lib.SIGNATURES)
-    assert lib.fdp_abi_version() == 1
+    assert lib.fdp_abi_version() == _lib.ABI_VERSION
     assert lib.fdp_status_string(0) == b"ok"
     assert b"workspace" in lib.fdp_status_string(_lib.FDP_ERR_WORKSPACE)
     # pure host-side queries work without a device

@@ -5,9 +5,11 @@ allocator, a process whose memory pool has already taken the whole GPU, or a ste
 pay the device-wide synchronisation of cudaMalloc.  For them the library carries a fixed scratch
 buffer (FDP_STATIC_SCRATCH_BYTES, 8 MiB) in its own image.  This test drives the entry point
 through ctypes, twice in a row on different problems (the buffer is shared and keeps old
-contents), and checks each result against fdp_bias_grad given an ordinary workspace, at the
-tolerances of the other parity tests.  It also checks that a problem too large for the fixed
-buffer is refused with FDP_ERR_STATIC_LIMIT.  The file name sorts last on purpose.
+contents), and checks each result against fdp_bias_grad given an ordinary workspace and against
+the CPU oracle, at the tolerances of the other parity tests; the amount of device memory in use
+(as the driver reports it) must be the same before and after the calls.  It also checks that a
+problem too large for the fixed buffer is refused with FDP_ERR_STATIC_LIMIT.  The file name sorts
+last on purpose.
 """
 import ctypes
 
@@ -15,6 +17,7 @@ import numpy as np
 import pytest
 import torch
 
+from oracle import dp_oracle as O
 from conftest import rel_err, norm_err
 from gpu_util import TOL, dev
 
@@ -41,11 +44,16 @@ def _with_workspace(lib_mod, lib, G, std):
     return db, norms, factors
 
 
-def _static(lib_mod, lib, G, std):
+def _outputs(G):
     B, T, n_out = G.shape
-    db = torch.empty(n_out, dtype=torch.float32, device=G.device)
-    norms = torch.empty(B, dtype=torch.float32, device=G.device)
-    factors = torch.empty(B, dtype=torch.float32, device=G.device)
+    return (torch.empty(n_out, dtype=torch.float32, device=G.device),
+            torch.empty(B, dtype=torch.float32, device=G.device),
+            torch.empty(B, dtype=torch.float32, device=G.device))
+
+
+def _static(lib_mod, lib, G, std, outputs=None):
+    B, T, n_out = G.shape
+    db, norms, factors = outputs if outputs is not None else _outputs(G)
     p = _params(lib_mod, std)
     st = lib.fdp_bias_grad_static(G.data_ptr(), db.data_ptr(), norms.data_ptr(), factors.data_ptr(), B, T,
                                   n_out, _DT[G.dtype], 0, ctypes.byref(p), torch.cuda.current_stream().cuda_stream)
@@ -60,16 +68,32 @@ def test_static_scratch_bias_grad_matches_workspace_variant_twice_in_a_row():
     big = (torch.randn(16, 256, 1024, generator=gen) * 0.05).to(torch.bfloat16).to(dev())
     small = (torch.randn(3, 70, 200, generator=gen) * 0.05).to(dev())
     small[0] *= 25
+    _static(_lib, lib, small, 0.0)       # the first call on a device looks up the buffer's address
+    torch.cuda.synchronize()
     for std in (0.0, 0.5):
         want = [_with_workspace(_lib, lib, g, std) for g in (big, small)]
-        # two calls back to back on the same stream: the second must not see the first one's partials
-        got = [_static(_lib, lib, big, std), _static(_lib, lib, small, std)]
+        outs = [_outputs(big), _outputs(small)]      # the caller's outputs exist before the calls
         torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
+        # two calls back to back on the same stream: the second must not see the first one's partials
+        got = [_static(_lib, lib, big, std, outs[0]), _static(_lib, lib, small, std, outs[1])]
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        assert free_after == free_before             # the calls took nothing from the device
         for g, (db, n, f), (wdb, wn, wf) in zip((big, small), got, want):
             tol = TOL[g.dtype]
             assert norm_err(n.cpu().numpy(), wn.cpu().numpy()) < tol
             assert np.allclose(f.cpu().numpy(), wf.cpu().numpy(), rtol=tol, atol=0)
             assert rel_err(db.cpu().numpy(), wdb.cpu().numpy()) < tol
+            # and against the oracle of the reference's bias path (flashdp/core/linear_clip.py:116-123)
+            odb, on, of = O.linear_bias_grad(g.float().cpu(), 0.8, 1.0)
+            assert norm_err(n.cpu().numpy(), on) < tol
+            assert np.allclose(f.cpu().numpy(), of, rtol=2 * tol, atol=0)
+            if std == 0.0:
+                assert rel_err(db.cpu().numpy(), odb) < tol
+            else:
+                z = O.gaussian_noise(db.numel(), std, 4242, 17, 3)
+                assert np.abs(db.cpu().numpy() - z - odb).max() < tol * np.abs(odb).max() + 3e-6
 
 
 def test_static_scratch_limit_is_enforced():
