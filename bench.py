@@ -8,8 +8,12 @@ A step is one DP backward of one Linear layer on one batch of synthetic input:
     dX = G W                                                        (fdp_linear_dgrad)
 and, on N > 1 GPUs (one process per GPU, the batch sharded, B samples per rank), an NCCL all-reduce
 of the clipped sums.  The metric is algorithmic TFLOP/s: 4*B*T*in*out per rank and step.
-Rank 0 prints one JSON line.  `--impl reference` times the CPU port of the reference's
-pure-PyTorch per-sample path on the host cores instead (rank 0 only).
+Rank 0 prints one JSON line.  On the default workload the same run then times the GPT-2-medium DP
+training step on the same ranks and adds it to the line as "gpt2_medium", and an untimed check that
+the N-rank result equals a single-rank evaluation of the concatenated batch ("parity_check").
+`--impl reference` times the CPU port of the reference's pure-PyTorch per-sample path on the host
+cores instead (rank 0 only), a step being the whole batch of the workload.
+`--workload llama7b_shaped` runs a Llama-2-7B-shaped decoder with every Linear but lm_head wrapped.
 """
 import argparse
 import ctypes
@@ -36,9 +40,10 @@ WORKLOADS = {
 }
 DEFAULT_WORKLOAD = "linear_bf16_b32_t1024_4096x4096"
 METRIC, UNIT = "dp_linear_bwd_tflops", "TFLOP/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one clipped-sum GEMM launch (ncu capture summarised
-# in profiles/tc_gemm_kernels_bf16_b32_t1024_4096x4096_ncu_full.md)
+# dram__bytes_read.sum + dram__bytes_write.sum of one clipped-sum GEMM launch, from an ncu capture of
+# this workload (bytes per launch)
 TRAFFIC = {"linear_bf16_b32_t1024_4096x4096": 1.579e9}
+NOMINAL_BF16_TFLOPS = 2250.0
 
 
 def peaks():
@@ -149,20 +154,94 @@ def cpu_port_rate(T, n_in, n_out, dtype_name, budget_s, sample_b=2, steps=None, 
                 ms_per_step=med * 1e3, steps=len(times))
 
 
+def workload_config(args, wl, world, l2_note):
+    B, T, n_in, n_out, dtn, _ = wl
+    return {"workload": args.workload, "B_per_gpu": B, "T": T, "in": n_in, "out": n_out,
+            "C": 1.0, "noise_multiplier": args.sigma, "bias": False, "grad_dtype": "f32",
+            "flops_per_step_per_gpu": flops_bwd(B, T, n_in, n_out), "l2": l2_note,
+            "parallelism": f"dp{world}" + (" + NCCL all-reduce of dW" if world > 1 else "")}
+
+
 def run_reference(args, wl):
+    """The reference arm: the per-sample path on the host cores, one step = the workload's whole batch
+    (all B samples of one rank), all host threads.  Rank 0 alone works."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     B, T, n_in, n_out, dtn, _ = wl
-    base = cpu_port_rate(T, n_in, n_out, dtn, budget_s=0, steps=max(1, args.steps), warmup=max(1, args.warmup))
+    base = cpu_port_rate(T, n_in, n_out, dtn, budget_s=0, sample_b=B, steps=max(1, args.steps),
+                         warmup=max(1, args.warmup))
     line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": base["ms_per_step"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtn, "data": "synthetic",
-            "config": {"workload": args.workload, "where": "host CPU cores", "sample": base["sample"]},
+            "config": workload_config(args, wl, 1, "host memory"),
             "cpu_baseline": {k: base[k] for k in ("value", "unit", "cores", "kind", "sample")},
             "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
+
+
+def dist_setup():
+    """(rank, local_rank, world, device); one NCCL process group per process when launched by torchrun."""
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1 and not dist.is_initialized():
+        # a short collective timeout: a rank that falls out of step ends the job in minutes, not hours
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+    return rank, local_rank, world, dev
+
+
+def parity_check(dev, rank, world):
+    """Untimed: does the N-rank job reproduce the single-rank gradient of the concatenated batch?
+
+    Every rank generates all the shards (seed = shard index), runs its own through the library with
+    divisor world*B and its share of the noise, and the results are all-reduced (SUM).  Rank 0 then
+    evaluates the concatenated batch alone and compares: sigma = 0 -> max|a-b| / max|b| (the sums
+    differ only in fp32 association); zero gradient with sigma = 1 -> the noise tensors must be
+    bit-equal (each element is drawn by exactly one rank and the others add exact zeros)."""
+    import torch
+    import torch.distributed as dist
+    from flashdp4review_b200.core import ops
+    B, T, n_in, n_out = 4, 512, 1024, 768
+    shards = []
+    for r in range(world):
+        gen = torch.Generator().manual_seed(1000 + r)
+        shards.append((torch.randn(B, T, n_in, generator=gen).to(torch.bfloat16),
+                       (torch.randn(B, T, n_out, generator=gen) * 1e-3).to(torch.bfloat16)))
+    X, G = (t.to(dev) for t in shards[rank])
+    out = {}
+
+    def sharded(Xs, Gs, sigma):
+        noise = ops.NoiseSpec(std=ops.noise_std(sigma, B * world), seed=77, param_id=5, step=3, rank=rank, world=world)
+        dW = ops.dp_linear_weight_grad(Xs, Gs, 1.0, 1.0, batch_divisor=B * world, noise=noise, out_dtype=torch.float32)
+        if world > 1:
+            dist.all_reduce(dW, op=dist.ReduceOp.SUM)
+        return dW
+
+    def single(Xa, Ga, sigma):
+        noise = ops.NoiseSpec(std=ops.noise_std(sigma, B * world), seed=77, param_id=5, step=3)
+        return ops.dp_linear_weight_grad(Xa, Ga, 1.0, 1.0, batch_divisor=B * world, noise=noise, out_dtype=torch.float32)
+
+    got0 = sharded(X, G, 0.0)
+    gotz = sharded(torch.zeros_like(X), torch.zeros_like(G), 1.0)
+    got1 = sharded(X, G, 1.0)
+    if rank == 0:
+        Xa = torch.cat([x for x, _ in shards]).to(dev)
+        Ga = torch.cat([g for _, g in shards]).to(dev)
+        want0 = single(Xa, Ga, 0.0)
+        wantz = single(torch.zeros_like(Xa), torch.zeros_like(Ga), 1.0)
+        want1 = single(Xa, Ga, 1.0)
+        rel = lambda a, b: float((a - b).abs().max() / b.abs().max())
+        out = {"shape": f"B={B}/rank T={T} {n_in}->{n_out} bf16", "ranks": world,
+               "max_rel": rel(got0, want0), "max_rel_with_noise": rel(got1, want1),
+               "noise_bit_equal": bool(torch.equal(gotz, wantz)), "tolerance": 1e-2}
+        out["ok"] = out["max_rel"] < 1e-2 and out["max_rel_with_noise"] < 1e-2 and out["noise_bit_equal"]
+    return out
 
 
 def run_native(args, wl):
@@ -173,16 +252,9 @@ def run_native(args, wl):
     from flashdp4review_b200.core import ops
 
     B, T, n_in, n_out, dtn, g_scale = wl
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank, local_rank, world, dev = dist_setup()
     if world != args.gpus and world > 1:
         args.gpus = world
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        # a short collective timeout: a rank that falls out of step ends the job in minutes, not hours
-        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
     lib = _lib.load()
     _lib.check(lib.fdp_check_device(local_rank), "fdp_check_device")
     fdp.manual_seed(1234)
@@ -344,10 +416,13 @@ def run_native(args, wl):
                                                              "clipped_gemm_ms"), acc)}
             gemm_flops = 2.0 * B * T * n_in * n_out
             achieved = gemm_flops / (phases["clipped_gemm_ms"] * 1e-3) / 1e12
+            # against the BURST cuBLAS figure: the phase events are read right after five back-to-back
+            # steps that follow the mostly idle end-to-end leg, a burst-like window
             roof = {"kernel": "clipped-sum GEMM (tcgen05)" if dtn != "f32" else "clipped-sum GEMM (fp32 FMA)",
-                    "bound": "tensor", "achieved": achieved, "peak": pk["bf16_sustained"], "unit": "TFLOP/s",
-                    "frac": achieved / pk["bf16_sustained"], "frac_of_burst_peak": achieved / pk["bf16"],
-                    "peak_source": pk["source"] + " (sustained cuBLAS bf16; kernel timed inside the step loop)",
+                    "bound": "tensor", "achieved": achieved, "peak": pk["bf16"], "unit": "TFLOP/s",
+                    "frac": achieved / pk["bf16"], "frac_of_sustained_peak": achieved / pk["bf16_sustained"],
+                    "frac_of_nominal": achieved / NOMINAL_BF16_TFLOPS,
+                    "peak_source": pk["source"] + " (burst cuBLAS bf16, torch.matmul 8192^3)",
                     "traffic": TRAFFIC.get(args.workload), "phases_ms": phases,
                     "wgrad_path_tflops": gemm_flops / (sum(phases.values()) * 1e-3) / 1e12}
     barrier()
@@ -372,23 +447,39 @@ def run_native(args, wl):
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        full = cpu_port_rate(T, n_in, n_out, dtn, budget_s=0, sample_b=B, steps=2, warmup=1) if args.cpu_full else None
         cpu = cpu_port_rate(T, n_in, n_out, dtn, budget_s=args.cpu_budget)
         cpu = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        if full is not None:
+            # the same path on the workload's whole batch (the per-sample loop is linear in B)
+            cpu["whole_batch"] = {"value": full["value"], "ms_per_step": full["ms_per_step"], "steps": full["steps"],
+                                  "samples": B}
 
+    check = None
+    if not args.no_check and dtn == "bf16":
+        check = parity_check(dev, rank, world)
+
+    line = None
     if rank == 0:
+        l2_note = ("inputs (X, G: %.0f MB) larger than the 126 MB L2" % (h2d / 1e6)) if flush is None \
+            else "L2 overwritten by a 256 MB fill between steps"
         line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                 "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": dtn, "data": "synthetic",
-                "config": {"workload": args.workload, "B_per_gpu": B, "T": T, "in": n_in, "out": n_out,
-                           "C": 1.0, "noise_multiplier": args.sigma, "bias": False, "grad_dtype": "f32",
-                           "flops_per_step_per_gpu": flops_bwd(B, T, n_in, n_out),
-                           "l2": ("inputs (X, G: %.0f MB) larger than the 126 MB L2" % (h2d / 1e6)) if flush is None
-                           else "L2 overwritten by a 256 MB fill between steps",
-                           "parallelism": f"dp{world}" + (" + NCCL all-reduce of dW" if world > 1 else "")},
+                "config": workload_config(args, wl, world, l2_note),
                 "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": e2e_ms, "steps": e2e_steps},
                 "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
-                "gpu_loop_baseline": gpu_loop}
+                "step_frac_nominal": value / world / NOMINAL_BF16_TFLOPS, "step_frac_burst": value / world / pk["bf16"],
+                "parity_check": check, "gpu_loop_baseline": gpu_loop}
+    # the second headline metric on the same ranks: GPT-2-medium DP training tokens/s
+    if args.workload == DEFAULT_WORKLOAD and not args.no_gpt2:
+        del X, G, W, bufs, flush
+        torch.cuda.empty_cache()
+        g = gpt2_measure(args, steps=max(args.steps, 20), with_no_dp=True)
+        if rank == 0:
+            line["gpt2_medium"] = g
+    if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -472,11 +563,12 @@ def run_hbm(args):
     print(json.dumps(line), flush=True)
 
 
-def run_gpt2(args):
+def gpt2_measure(args, steps, with_no_dp=False, no_dp=False):
     """GPT-2-medium DP training step (24 layers, d=1024, 16 heads, ctx 1024, vocab 50257; random init,
     uniform random tokens, micro-batch 8 per GPU, bf16 autocast, Adam lr 1e-4, C=1, sigma=1): the
-    transformers GPT2LMHeadModel with every Conv1D / LayerNorm wrapped, lm_head skipped.  Metric:
-    tokens/s over all ranks.  `--no-dp` runs the same model unwrapped for context."""
+    transformers GPT2LMHeadModel with every Conv1D / LayerNorm wrapped, lm_head skipped
+    (the loop of example/gpt2/train.py:71-86).  Returns tokens/s over all ranks and the pieces of the
+    JSON line; `with_no_dp` also times the same model unwrapped for context."""
     import torch
     import torch.distributed as dist
     import flashdp4review_b200 as fdp
@@ -485,13 +577,7 @@ def run_gpt2(args):
     from flashdp4review_b200.layers import Conv1D
     from transformers import GPT2Config, GPT2LMHeadModel
 
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=180))
+    rank, local_rank, world, dev = dist_setup()
     lib = _lib.load()
     fdp.manual_seed(1234)
     fdp.set_data_parallel(rank, world)
@@ -499,18 +585,218 @@ def run_gpt2(args):
     micro_batch, seq = args.micro_batch, 1024
     cfg = GPT2Config(n_layer=args.layers, n_embd=1024, n_head=16, n_positions=1024, vocab_size=50257,
                      resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
-    torch.manual_seed(0)
-    model = GPT2LMHeadModel(cfg).to(dev)
-    if not args.no_dp:
-        fdp.wrap_with_flashdp_layers(model, target_modules=[Conv1D, torch.nn.Linear, torch.nn.LayerNorm],
-                                     skip_layers=["lm_head"], C=1.0, noise_multiplier=1.0, feedback=False)
-    # fused=True: one multi-tensor kernel; the default would fall back to ~300 per-parameter kernel chains
-    # because DPParameter is a Parameter subclass (torch's foreach/fused auto-selection wants exact types)
-    opt = torch.optim.Adam(model.parameters(), lr=1e-4, fused=True)
-    # gradients live in the all-reduce buckets; the DP layers write their weight gradients straight into them
-    reducer = DPGradReducer(model, grad_as_bucket_view=True) if world > 1 else None
     gen = torch.Generator().manual_seed(42 + rank)
     tokens_h = torch.randint(0, cfg.vocab_size, (micro_batch, seq + 1), generator=gen).pin_memory()
+    tokens = tokens_h.to(dev)
+    loss_h = torch.zeros((), dtype=torch.float32).pin_memory()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, n):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    def build(dp):
+        torch.manual_seed(0)
+        model = GPT2LMHeadModel(cfg).to(dev)
+        if dp:
+            fdp.wrap_with_flashdp_layers(model, target_modules=[Conv1D, torch.nn.Linear, torch.nn.LayerNorm],
+                                         skip_layers=["lm_head"], C=1.0, noise_multiplier=1.0, feedback=False)
+        # fused=True: one multi-tensor kernel; the default would fall back to ~300 per-parameter kernel chains
+        # because DPParameter is a Parameter subclass (torch's foreach/fused auto-selection wants exact types)
+        opt = torch.optim.Adam(model.parameters(), lr=1e-4, fused=True)
+        # gradients live in the all-reduce buckets; the DP layers write their weight gradients straight into them
+        reducer = DPGradReducer(model, grad_as_bucket_view=True) if world > 1 else None
+
+        def step(tok):
+            if reducer is not None:
+                reducer.zero_grad()
+            else:
+                opt.zero_grad(set_to_none=True)
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                out = model(input_ids=tok[:, :-1], labels=tok[:, :-1])
+            out.loss.backward()
+            if reducer is not None:
+                reducer.finish()
+            opt.step()
+            return out.loss
+        return step, reducer
+
+    res = {}
+    if with_no_dp and not no_dp:
+        plain_step, plain_reducer = build(False)
+        for _ in range(3):
+            plain_step(tokens)
+        res["no_dp_ms_per_step"] = timed(lambda: plain_step(tokens), 10) / 10
+        if plain_reducer is not None:
+            plain_reducer.remove()
+        del plain_step, plain_reducer
+        torch.cuda.empty_cache()
+
+    step, reducer = build(not no_dp)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    for _ in range(max(args.warmup, 3)):
+        step(tokens)
+    if sampler:
+        sampler.wait_first_sample()
+    l0, w0 = lib.fdp_launch_count(), time.time()
+    total_ms = timed(lambda: step(tokens), steps)
+    windows = [(w0, time.time())]
+    launches = lib.fdp_launch_count() - l0
+    ms_per_step = total_ms / steps
+
+    def e2e_step():
+        tokens.copy_(tokens_h, non_blocking=True)
+        loss_h.copy_(step(tokens).detach().float(), non_blocking=True)
+
+    e2e_steps = max(2, min(steps, 10))
+    e2e_step()
+    e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
+    clocks = sampler.stop(windows) if sampler else None
+    peak_mem = torch.cuda.max_memory_allocated(dev)
+    res.update({"tokens_per_s": world * micro_batch * seq / (ms_per_step * 1e-3), "ms_per_step": ms_per_step,
+                "steps": steps, "n_gpus": world, "gpu_launches": int(launches), "clocks": clocks,
+                "loss": float(loss_h), "peak_memory_bytes": int(peak_mem),
+                "e2e": {"value": world * micro_batch * seq / (e2e_ms * 1e-3), "unit": "tokens/s",
+                        "h2d_bytes_per_step": tokens_h.numel() * 8, "d2h_bytes_per_step": 4,
+                        "ms_per_step": e2e_ms, "steps": e2e_steps},
+                "config": {"layers": args.layers, "d_model": 1024, "heads": 16, "seq_len": seq,
+                           "micro_batch_per_gpu": micro_batch, "global_batch": micro_batch * world,
+                           "dp_wrapped": not no_dp, "gemm_impl": args.gemm_impl, "optimizer": "Adam lr 1e-4 (fused)",
+                           "C": 1.0, "noise_multiplier": 1.0, "parallelism": f"dp{world}",
+                           "grad_buckets": "fp32, 64 MB, gradients are views of the buckets" if world > 1 else None,
+                           "l2": "activations and weights (GBs) far larger than the 126 MB L2"}})
+    if reducer is not None:
+        reducer.remove()
+    return res
+
+
+def run_gpt2(args):
+    """`--workload gpt2_medium`: the GPT-2-medium DP step as a JSON line of its own (`--no-dp`: the
+    same model unwrapped)."""
+    import torch.distributed as dist
+    g = gpt2_measure(args, steps=args.steps, no_dp=args.no_dp)
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    if rank == 0:
+        cfg = dict(g["config"], workload=args.workload)
+        line = {"metric": "gpt2_medium_dp_tokens_per_s", "value": g["tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
+                "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": g["ms_per_step"],
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                "data": "synthetic", "config": cfg, "e2e": g["e2e"], "gpu_launches": g["gpu_launches"],
+                "clocks": g["clocks"], "loss": g["loss"], "peak_memory_bytes": g["peak_memory_bytes"]}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def build_llama(layers=32, d=4096, heads=32, ffn=11008, vocab=32000, dtype=None, device=None):
+    """A Llama-2-7B-shaped decoder in plain PyTorch (pre-norm blocks with RMSNorm, rotary attention
+    through scaled_dot_product_attention, SwiGLU MLP, untied lm_head); random init.  Every projection
+    is an nn.Linear without bias, so wrap_with_flashdp_layers can swap them."""
+    import torch
+    import torch.nn as nn
+    import torch.nn.functional as F
+
+    class RMSNorm(nn.Module):
+        def __init__(self, n, eps=1e-5):
+            super().__init__()
+            self.weight = nn.Parameter(torch.ones(n))
+            self.eps = eps
+
+        def forward(self, x):
+            v = x.float()
+            return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + self.eps)).to(x.dtype) * self.weight
+
+    def rope(x, cos, sin):          # x (B, H, T, hd)
+        x1, x2 = x[..., ::2], x[..., 1::2]
+        return torch.stack((x1 * cos - x2 * sin, x1 * sin + x2 * cos), dim=-1).flatten(-2)
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.attn_norm, self.mlp_norm = RMSNorm(d), RMSNorm(d)
+            self.q_proj, self.k_proj, self.v_proj, self.o_proj = (nn.Linear(d, d, bias=False) for _ in range(4))
+            self.gate_proj, self.up_proj = nn.Linear(d, ffn, bias=False), nn.Linear(d, ffn, bias=False)
+            self.down_proj = nn.Linear(ffn, d, bias=False)
+
+        def forward(self, x, cos, sin):
+            B, T, _ = x.shape
+            h = self.attn_norm(x)
+            split = lambda t: t.view(B, T, heads, d // heads).transpose(1, 2)
+            q, k, v = split(self.q_proj(h)), split(self.k_proj(h)), split(self.v_proj(h))
+            a = F.scaled_dot_product_attention(rope(q, cos, sin), rope(k, cos, sin), v, is_causal=True)
+            x = x + self.o_proj(a.transpose(1, 2).reshape(B, T, d))
+            h = self.mlp_norm(x)
+            return x + self.down_proj(F.silu(self.gate_proj(h)) * self.up_proj(h))
+
+    class Decoder(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.embed = nn.Embedding(vocab, d)
+            self.blocks = nn.ModuleList(Block() for _ in range(layers))
+            self.norm = RMSNorm(d)
+            self.lm_head = nn.Linear(d, vocab, bias=False)
+
+        def forward(self, tokens):
+            T = tokens.shape[1]
+            hd = d // heads
+            inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2, device=tokens.device, dtype=torch.float32) / hd))
+            ang = torch.arange(T, device=tokens.device, dtype=torch.float32)[:, None] * inv[None, :]
+            x = self.embed(tokens)
+            cos, sin = ang.cos().to(x.dtype), ang.sin().to(x.dtype)
+            for blk in self.blocks:
+                x = blk(x, cos, sin)
+            return self.lm_head(self.norm(x))
+
+    with torch.device(device if device is not None else "cpu"):
+        model = Decoder()
+    for name, prm in model.named_parameters():
+        if prm.dim() == 2:
+            torch.nn.init.normal_(prm, std=0.02)
+    return model.to(dtype) if dtype is not None else model
+
+
+def run_llama(args):
+    """Llama-2-7B-shaped decoder (32 layers, d 4096, 32 heads, SwiGLU 11008, RMSNorm, vocab 32000), every
+    nn.Linear but lm_head DP-wrapped, uniform random tokens, seq 2048, micro-batch 4 per GPU, parameters
+    and activations in bf16 (no autocast), C = 1, sigma = 1; data-parallel with the clipped sums written
+    straight into bf16 all-reduce buckets.  Optimizer: fused Adam on the bf16 parameters (bf16 moments).
+    Metric: tokens/s over all ranks; the line also carries the memory high-water mark."""
+    import torch
+    import torch.distributed as dist
+    import flashdp4review_b200 as fdp
+    from flashdp4review_b200 import _lib
+    from flashdp4review_b200.distributed import DPGradReducer
+
+    rank, local_rank, world, dev = dist_setup()
+    lib = _lib.load()
+    fdp.manual_seed(1234)
+    fdp.set_data_parallel(rank, world)
+    fdp.set_input_grad_impl(args.gemm_impl)
+    micro_batch, seq, vocab = args.llama_micro_batch, args.llama_seq, 32000
+    torch.manual_seed(0)
+    model = build_llama(layers=args.llama_layers, dtype=torch.bfloat16, device=dev)
+    n_params = sum(p.numel() for p in model.parameters())
+    if not args.no_dp:
+        fdp.wrap_with_flashdp_layers(model, target_modules=[torch.nn.Linear], skip_layers=["lm_head"], C=1.0,
+                                     noise_multiplier=1.0, feedback=False)
+    n_dp = sum(p.numel() for p in model.parameters() if getattr(p, "requires_dp", False))
+    opt = torch.optim.Adam(model.parameters(), lr=1e-4, fused=True)
+    reducer = DPGradReducer(model, grad_as_bucket_view=True, bucket_bytes=256 << 20) if world > 1 else None
+    gen = torch.Generator().manual_seed(42 + rank)
+    tokens_h = torch.randint(0, vocab, (micro_batch, seq + 1), generator=gen).pin_memory()
     tokens = tokens_h.to(dev)
     loss_h = torch.zeros((), dtype=torch.float32).pin_memory()
 
@@ -519,24 +805,24 @@ def run_gpt2(args):
             reducer.zero_grad()
         else:
             opt.zero_grad(set_to_none=True)
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            out = model(input_ids=tok[:, :-1], labels=tok[:, :-1])
-        out.loss.backward()
+        logits = model(tok[:, :-1])
+        loss = torch.nn.functional.cross_entropy(logits.float().view(-1, vocab), tok[:, 1:].reshape(-1))
+        loss.backward()
         if reducer is not None:
             reducer.finish()
         opt.step()
-        return out.loss
+        return loss
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps):
+    def timed(fn, n):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        for _ in range(steps):
+        for _ in range(n):
             fn()
         e1.record()
         barrier()
@@ -555,30 +841,40 @@ def run_gpt2(args):
     windows = [(w0, time.time())]
     launches = lib.fdp_launch_count() - l0
     ms_per_step = total_ms / args.steps
-    value = world * micro_batch * seq / (ms_per_step * 1e-3)
 
     def e2e_step():
         tokens.copy_(tokens_h, non_blocking=True)
         loss_h.copy_(step(tokens).detach().float(), non_blocking=True)
 
-    e2e_steps = max(2, min(args.steps, 10))
+    e2e_steps = max(2, min(args.steps, 5))
     e2e_step()
     e2e_ms = timed(e2e_step, e2e_steps) / e2e_steps
     clocks = sampler.stop(windows) if sampler else None
+    # the all-reduce alone, on buffers of the buckets' sizes (context for the overlap)
+    allreduce_ms = None
+    if reducer is not None:
+        allreduce_ms = timed(lambda: [dist.all_reduce(f) for f in reducer._flat], 3) / 3
+        for f in reducer._flat:
+            f.zero_()
     if rank == 0:
-        line = {"metric": "gpt2_medium_dp_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": world,
+        tok_s = world * micro_batch * seq / (ms_per_step * 1e-3)
+        line = {"metric": "llama7b_shaped_dp_tokens_per_s", "value": tok_s, "unit": "tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-                "data": "synthetic",
-                "config": {"workload": args.workload, "layers": args.layers, "d_model": 1024, "heads": 16,
-                           "seq_len": seq, "micro_batch_per_gpu": micro_batch, "global_batch": micro_batch * world,
-                           "dp_wrapped": not args.no_dp, "gemm_impl": args.gemm_impl, "optimizer": "Adam lr 1e-4 (fused)", "C": 1.0,
-                           "noise_multiplier": 1.0, "parallelism": f"dp{world}",
-                           "l2": "activations and weights (GBs) far larger than the 126 MB L2"},
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                "config": {"workload": args.workload, "layers": args.llama_layers, "d_model": 4096, "heads": 32,
+                           "ffn": 11008, "vocab": vocab, "seq_len": seq, "micro_batch_per_gpu": micro_batch,
+                           "global_batch": micro_batch * world, "parameters": n_params, "dp_parameters": n_dp,
+                           "dp_wrapped": not args.no_dp, "gemm_impl": args.gemm_impl,
+                           "optimizer": "Adam lr 1e-4 (fused, bf16 moments)", "C": 1.0, "noise_multiplier": 1.0,
+                           "parallelism": f"dp{world}",
+                           "grad_buckets": "bf16, 256 MB, gradients are views of the buckets" if world > 1 else None,
+                           "allreduce_bytes_per_step": 2 * sum(p.numel() for p in model.parameters()) if world > 1 else 0,
+                           "l2": "activations and weights (tens of GB) far larger than the 126 MB L2"},
                 "e2e": {"value": world * micro_batch * seq / (e2e_ms * 1e-3), "unit": "tokens/s",
-                        "h2d_bytes_per_step": tokens_h.numel() * 8, "d2h_bytes_per_step": 4,
-                        "ms_per_step": e2e_ms, "steps": e2e_steps},
-                "gpu_launches": int(launches), "clocks": clocks, "loss": float(loss_h)}
+                        "h2d_bytes_per_step": tokens_h.numel() * 8, "d2h_bytes_per_step": 4, "ms_per_step": e2e_ms,
+                        "steps": e2e_steps},
+                "gpu_launches": int(launches), "clocks": clocks, "loss": float(loss_h),
+                "peak_memory_bytes": int(torch.cuda.max_memory_allocated(dev)), "allreduce_alone_ms": allreduce_ms}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -590,7 +886,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
-    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + ["gpt2_medium", "hbm_kernels_bf16_b16_t1024"])
+    ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS) + ["gpt2_medium", "hbm_kernels_bf16_b16_t1024", "llama7b_shaped"])
+    ap.add_argument("--llama-layers", type=int, default=32, help="llama7b_shaped: number of decoder blocks")
+    ap.add_argument("--llama-seq", type=int, default=2048)
+    ap.add_argument("--llama-micro-batch", type=int, default=4)
     ap.add_argument("--layers", type=int, default=24, help="gpt2_medium: number of transformer blocks")
     ap.add_argument("--micro-batch", type=int, default=8, help="gpt2_medium: samples per GPU and step")
     ap.add_argument("--gemm-impl", default="native", choices=["native", "library"],
@@ -600,9 +899,20 @@ def main():
     ap.add_argument("--sigma", type=float, default=1.0, help="noise_multiplier of the DP-Linear workloads")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work for cpu_baseline")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-full", action="store_true", default=True,
+                    help="cpu_baseline also times the workload's whole batch (two steps)")
+    ap.add_argument("--no-cpu-full", dest="cpu_full", action="store_false")
+    ap.add_argument("--no-gpt2", action="store_true", help="default workload: skip the GPT-2-medium leg")
+    ap.add_argument("--no-check", action="store_true", help="skip the untimed N-rank == single-rank check")
     args = ap.parse_args()
     if args.workload == "hbm_kernels_bf16_b16_t1024":
         return run_hbm(args)
+    if args.workload == "llama7b_shaped":
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference's per-sample path has no CPU-"
+                              "feasible whole-model run; the per-layer CPU baseline is the default workload's"}))
+            return
+        return run_llama(args)
     if args.workload == "gpt2_medium":
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the reference's per-sample path has no CPU-"

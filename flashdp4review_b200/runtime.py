@@ -21,7 +21,7 @@ class _Run:
     world = 1
     rank = 0
     # SMs the persistent GEMM grids leave free while a gradient all-reduce is in flight (world > 1)
-    reserve_sms = int(os.environ.get("FDP_DP_RESERVE_SMS", "8"))
+    reserve_sms = int(os.environ.get("FDP_DP_RESERVE_SMS", "12"))
     input_grad_impl = "library"   # "library": cuBLAS via torch (as the reference); "native": fdp_linear_dgrad
     micro_index = 0               # gradient accumulation: which micro-step of `micro_steps` runs now
     micro_steps = 1
