@@ -18,6 +18,7 @@ FDP_STATIC_SCRATCH_BYTES = 8 << 20
 FDP_F32, FDP_BF16, FDP_F16 = 0, 1, 2
 FDP_OUT_IN, FDP_IN_OUT = 0, 1
 FDP_NORM_AUTO, FDP_NORM_DIRECT, FDP_NORM_GRAM = 0, 1, 2
+FDP_FP32_TENSOR = 16
 
 c_void_p, c_int, c_size_t, c_float = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t, ctypes.c_float
 
@@ -59,6 +60,9 @@ SIGNATURES = {
                        [c_void_p, c_size_t, c_void_p]),
     "fdp_layernorm_fwd": (c_int, [c_void_p] * 6 + [c_int, c_int, c_float, c_int, c_int, c_void_p]),
     "fdp_layernorm_bwd_workspace_bytes": (c_size_t, [c_int] * 3),
+    "fdp_layernorm_saturate_workspace_bytes": (c_size_t, [c_int, c_int]),
+    "fdp_layernorm_saturate_groups": (c_int, [c_int, c_int]),
+    "fdp_layernorm_bwd_saturate": (c_int, [c_void_p] * 6 + [c_int] * 4 + [c_float, c_float, c_void_p, c_size_t, c_void_p]),
     "fdp_layernorm_bwd": (c_int, [c_void_p] * 10 + [c_int] * 5 +
                           [ctypes.POINTER(DPParams), c_void_p, c_size_t, c_void_p]),
 }

@@ -83,7 +83,8 @@ def _params(C, clamp_value, batch_divisor, noise):
 # weight gradient
 # ------------------------------------------------------------------------------------------------
 def dp_linear_weight_grad(input, grad_output, C, clamp_value, *, batch_divisor=None, noise=None,
-                          layout="out_in", out_dtype=None, norm_algo="auto", return_norms=False, out=None):
+                          layout="out_in", out_dtype=None, norm_algo="auto", return_norms=False, out=None,
+                          fp32_tensor=None):
     """Clipped, averaged, noised weight gradient of a Linear/Conv1D layer in one library call.
 
     input (B,T,in), grad_output (B,T,out).  Returns dW [out,in] (layout='out_in', nn.Linear) or
@@ -92,6 +93,8 @@ def dp_linear_weight_grad(input, grad_output, C, clamp_value, *, batch_divisor=N
     (1/divisor) * sum_b min(clamp, C/(||G_b^T X_b||+1e-10)) * G_b^T X_b + N(0, noise.std^2).
     `out`: a contiguous tensor of the result's shape to write into (e.g. a slice of a gradient
     bucket) instead of a fresh allocation.
+    `fp32_tensor` (default: runtime.fp32_mode() == "tensor"): fp32 inputs with 64-aligned shapes run on
+    the tensor cores as three bf16 products -- much faster, accurate to about 1e-4 instead of 1e-5.
     """
     lib = _lib.load()
     _require_cuda(input, grad_output)
@@ -112,6 +115,11 @@ def dp_linear_weight_grad(input, grad_output, C, clamp_value, *, batch_divisor=N
     norms = torch.empty(B, dtype=torch.float32, device=G.device) if return_norms else None
     factors = torch.empty(B, dtype=torch.float32, device=G.device) if return_norms else None
     algo = NORM_ALGOS[norm_algo]
+    if fp32_tensor is None:
+        from .. import runtime
+        fp32_tensor = runtime.fp32_mode() == "tensor"
+    if fp32_tensor and G.dtype == torch.float32:
+        algo |= _lib.FDP_FP32_TENSOR
     nbytes = lib.fdp_linear_wgrad_workspace_bytes(B, T, n_in, n_out, _dt(G.dtype), algo)
     ws = _workspace(nbytes, G.device)
     p = _params(C, clamp_value, batch_divisor, noise)
@@ -296,6 +304,45 @@ def dp_layernorm_backward(grad_output, input, weight, mean, rstd, C, clamp_value
     if return_norms:
         return dx, dgamma, dbeta, ng, nb
     return dx, dgamma, dbeta
+
+
+def layernorm_bwd_clip_fused(grad_output, input, weight, bias, clip_args, buffer, args=None):
+    """Compatibility drop-in for flashdp/core/layernorm_clip.py:241-286: returns (dx, dw_, db_, args)
+    with dw_ / db_ the [G, d] buffers of the reference's element-wise saturating accumulation
+    (buf <- partial + buf * min(clamp, C / (|buf| + 1e-10)), flashdp/core/layernorm_clip.py:109-131).
+    The reference adds the rows of a buffer in the order its row programs win a spin lock; here they are
+    added in increasing row order, so the result is reproducible.  This is NOT per-sample clipping and
+    carries no noise: DP training uses dp_layernorm_backward."""
+    lib = _lib.load()
+    _require_cuda(grad_output, input, weight)
+    C, clamp = (float(v) for v in clip_args.tolist())
+    dy = grad_output.contiguous()
+    x = input.contiguous()
+    w = weight.contiguous()
+    d = x.shape[-1]
+    rows = x.numel() // d
+    mean, rstd = buffer["mean"], buffer["rstd"]
+    # dx: the standard LayerNorm input gradient (flashdp/core/layernorm_clip.py:95-103)
+    dx, _, _ = dp_layernorm_backward(dy.reshape(1, rows, d), x.reshape(1, rows, d), w, mean, rstd, 1.0, 1.0,
+                                     need_dx=True, need_dbeta=False)
+    G = lib.fdp_layernorm_saturate_groups(rows, d)
+    ws = torch.empty(2, G, d, dtype=torch.float32, device=x.device)
+    dw = torch.empty(d, dtype=w.dtype, device=x.device)
+    db = torch.empty(d, dtype=w.dtype, device=x.device)
+    with torch.cuda.device(x.device):
+        st = lib.fdp_layernorm_bwd_saturate(_ptr(dy), _ptr(x), _ptr(mean), _ptr(rstd), _ptr(dw), _ptr(db), rows, d,
+                                            _dt(x.dtype), _dt(w.dtype), C, clamp, _ptr(ws), ws.numel() * 4,
+                                            _stream(x.device))
+    _lib.check(st, "fdp_layernorm_bwd_saturate")
+    return dx.reshape(input.shape), ws[0], ws[1], {"GROUP_SIZE_M": G, "M": rows, "dw": dw, "db": db}
+
+
+def layernorm_dwdb_fused(weight, bias, _dw, _db, args=None):
+    """Compatibility drop-in for flashdp/core/layernorm_clip.py:289-315: the column sums of the G
+    buffers (already formed by layernorm_bwd_clip_fused, which passes them on in `args`)."""
+    if args is not None and "dw" in args:
+        return args["dw"], args["db"]
+    return _dw.sum(0).to(weight.dtype), _db.sum(0).to(weight.dtype)
 
 
 def _ln_identity_stats(rows, device):

@@ -88,7 +88,7 @@ struct WgradWs {
 WgradWs wgrad_ws(void* base, int B, int T, int n_in, int n_out, int dt, int norm_algo) {
   WgradWs w;
   w.tc = tc_plan(B, T, n_in, n_out, dt, norm_algo);
-  w.short_seq = T < SHORT_SEQ && norm_algo != FDP_NORM_DIRECT;
+  w.short_seq = T < SHORT_SEQ && (norm_algo & FDP_NORM_MASK) != FDP_NORM_DIRECT;
   w.nparts = w.tc.ok ? w.tc.nparts : (w.short_seq ? 1 : simt_norm_tiles(n_in, n_out));
   Carver c(base);
   w.status = c.take<int>(64);
@@ -217,7 +217,8 @@ int fdp_linear_wgrad(const void* G, const void* X, void* dW, float* norms_out, f
   if (G == nullptr || X == nullptr || dW == nullptr) return FDP_ERR_ARG;
   if (B <= 0 || T <= 0 || n_in <= 0 || n_out <= 0) return FDP_ERR_ARG;
   if (layout != FDP_OUT_IN && layout != FDP_IN_OUT) return FDP_ERR_ARG;
-  if (norm_algo < FDP_NORM_AUTO || norm_algo > FDP_NORM_GRAM) return FDP_ERR_ARG;
+  if (norm_algo < 0 || (norm_algo & ~(FDP_NORM_MASK | FDP_FP32_TENSOR)) != 0 || (norm_algo & FDP_NORM_MASK) > FDP_NORM_GRAM)
+    return FDP_ERR_ARG;
   if (!valid_dtype(in_dtype) || !valid_dtype(out_dtype)) return FDP_ERR_DTYPE;
   if (static_cast<long long>(B) * T >= (1ll << 31) / 2 || B > 65535) return FDP_ERR_SHAPE;  // B is a grid dimension
   int st = check_params(p);
@@ -239,10 +240,21 @@ int fdp_linear_wgrad(const void* G, const void* X, void* dW, float* norms_out, f
   // the scaled epilogue of the clipped-sum GEMM reduces the norm partials itself: no clip-factor launch
   const bool fused_factors = w.tc.ok && w.tc.scaled_epilogue && tc_fused_factors_ok(B);
   prof_mark(0, s);
+  // fp32 inputs on the tensor cores: split G and X into bf16 halves first, then run as bf16
+  const void* Gt = G;
+  const void* Xt = X;
+  int tdt = in_dtype;
+  if (w.tc.ok && w.tc.split3) {
+    char* sg = static_cast<char*>(w.tc_extra) + w.tc.split_bytes;
+    char* sx = sg + w.tc.split3_g_bytes;
+    if ((st = tc_split3(G, sg, static_cast<size_t>(B) * T, n_out, s)) != FDP_OK) return st;
+    if ((st = tc_split3(X, sx, static_cast<size_t>(B) * T, n_in, s)) != FDP_OK) return st;
+    Gt = sg; Xt = sx; tdt = FDP_BF16;
+  }
   if (w.short_seq) {
     simt_norm_gram_small(G, X, w.partials, B, T, n_in, n_out, in_dtype, s);
   } else if (w.tc.ok) {
-    if ((st = tc_norms(G, X, w.partials, w.status, B, T, n_in, n_out, in_dtype, w.tc, s)) != FDP_OK) return st;
+    if ((st = tc_norms(Gt, Xt, w.partials, w.status, B, T, n_in, n_out, tdt, w.tc, s)) != FDP_OK) return st;
   } else {
     simt_norm_direct(G, X, w.partials, B, T, n_in, n_out, in_dtype, s);
   }
@@ -264,9 +276,9 @@ int fdp_linear_wgrad(const void* G, const void* X, void* dW, float* norms_out, f
     } else {
       fs.factors = w.factors;
     }
-    if ((st = tc_clipped_wgrad(w.tc.scaled_epilogue ? G : gs, X, w.tc.scaled_epilogue ? &fs : nullptr, split_ws,
-                               dW, w.status, B, T, n_in, n_out, in_dtype, out_dtype, layout, inv_div, nk,
-                               s)) != FDP_OK) return st;
+    if ((st = tc_clipped_wgrad(w.tc.scaled_epilogue ? Gt : gs, Xt, w.tc.scaled_epilogue ? &fs : nullptr, split_ws,
+                               dW, w.status, B, T, n_in, n_out, tdt, out_dtype, layout, inv_div, nk,
+                               s, w.tc.split3 ? 3 : 1)) != FDP_OK) return st;
   } else {
     prof_mark(3, s);
     simt_clipped_wgrad(G, X, w.factors, dW, B, T, n_in, n_out, in_dtype, out_dtype, layout, inv_div, nk, s);
@@ -427,6 +439,31 @@ int fdp_layernorm_bwd(const void* dy, const void* x, const void* gamma, const fl
   ln_clip_finalize(part, sumsq, ln_sumsq_parts(d), p->C, p->clamp_value, factors, norms_gamma, norms_beta, dgamma,
                    dbeta, B, pl.chunks, d, param_dtype, inv_div, make_noise_key(p, p->param_id),
                    make_noise_key(p, p->param_id2), s);
+  FDP_LAUNCH_OK();
+  return FDP_OK;
+}
+
+size_t fdp_layernorm_saturate_workspace_bytes(int rows, int d) {
+  if (rows <= 0 || d <= 0) return 0;
+  return static_cast<size_t>(2) * ln_saturate_groups(rows, d) * d * sizeof(float);
+}
+
+int fdp_layernorm_saturate_groups(int rows, int d) { return (rows <= 0 || d <= 0) ? 0 : ln_saturate_groups(rows, d); }
+
+int fdp_layernorm_bwd_saturate(const void* dy, const void* x, const float* mean, const float* rstd, void* dgamma,
+                               void* dbeta, int rows, int d, int dtype, int param_dtype, float C, float clamp_value,
+                               void* workspace, size_t workspace_bytes, fdp_stream_t stream) {
+  if (dy == nullptr || x == nullptr || mean == nullptr || rstd == nullptr || dgamma == nullptr) return FDP_ERR_ARG;
+  if (rows <= 0 || d <= 0) return FDP_ERR_ARG;
+  if (!valid_dtype(dtype) || !valid_dtype(param_dtype)) return FDP_ERR_DTYPE;
+  int st = current_device_ok();
+  if (st != FDP_OK) return st;
+  if (workspace == nullptr || !aligned16(workspace) || workspace_bytes < fdp_layernorm_saturate_workspace_bytes(rows, d))
+    return FDP_ERR_WORKSPACE;
+  float* dw_buf = static_cast<float*>(workspace);
+  float* db_buf = dw_buf + static_cast<size_t>(ln_saturate_groups(rows, d)) * d;
+  ln_saturate(dy, x, mean, rstd, dw_buf, db_buf, dgamma, dbeta, rows, d, dtype, param_dtype, C, clamp_value,
+              static_cast<cudaStream_t>(stream));
   FDP_LAUNCH_OK();
   return FDP_OK;
 }

@@ -73,6 +73,12 @@ void ln_clip_finalize(const float* part, const float* sumsq, int nparts, float C
                       float* norms0, float* norms1, void* out0, void* out1, int B, int chunks, int d, int out_dt,
                       float inv_div, NoiseKey nk0, NoiseKey nk1, cudaStream_t s);
 
+// compatibility mode: the element-wise saturating accumulation of the reference's fused backward with
+// a fixed row order; dw_buf / db_buf are [ln_saturate_groups(rows, d), d] floats
+int ln_saturate_groups(int rows, int d);
+void ln_saturate(const void* dy, const void* x, const float* mean, const float* rstd, float* dw_buf, float* db_buf,
+                 void* dgamma, void* dbeta, int rows, int d, int dt, int pdt, float C, float clamp, cudaStream_t s);
+
 // ---- tcgen05 / TMEM / TMA kernels (bf16 / fp16, aligned shapes) ---------------------------------
 struct TcPlan {
   bool ok;          // shapes admit the tensor-core path
@@ -82,8 +88,15 @@ struct TcPlan {
   int nparts;       // norm partials per sample
   bool scaled_epilogue;  // clip factors applied per sample in the GEMM epilogue, no pre-scale pass
   bool short_seq;        // T < SHORT_SEQ: norms by simt_norm_gram_small, clipped sum over the pre-scaled G
+  // fp32 inputs: G and X are first split into high and low bf16 halves ([rows, 2n] each, behind the
+  // parking area in the workspace), and every contraction runs as three bf16 products
+  bool split3;
+  size_t split3_g_bytes, split3_x_bytes;
 };
 TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo);
+// fp32 [rows, n] -> bf16 [rows, 2n]: high halves, then low halves (x - hi rounded to bf16)
+int tc_split3(const void* src, void* dst, size_t rows, int n, cudaStream_t s);
+// With pl.split3, G and X are the split matrices and dt is FDP_BF16.
 int tc_norms(const void* G, const void* X, float* partials, int* dev_status, int B, int T, int n_in,
              int n_out, int dt, const TcPlan& pl, cudaStream_t s);
 // Gs[r,:] = factors[r / T] * G[r,:]
@@ -103,7 +116,7 @@ bool tc_fused_factors_ok(int B);
 // otherwise Gs is G itself and c_b is applied per sample in the epilogue.
 int tc_clipped_wgrad(const void* Gs, const void* X, const TcFactorSource* fs, float* split_ws,
                      void* dW, int* dev_status, int B, int T, int n_in, int n_out, int dt, int out_dt,
-                     int layout, float inv_div, NoiseKey nk, cudaStream_t s);
+                     int layout, float inv_div, NoiseKey nk, cudaStream_t s, int terms = 1);
 // test aid: one warp waits `limit_cycles` on a barrier nobody arrives on and reports the timeout
 int tc_wait_selftest(int* status, long long limit_cycles, cudaStream_t s);
 bool tc_dgrad_ok(int rows, int n_in, int n_out, int dt);

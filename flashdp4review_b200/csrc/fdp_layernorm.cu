@@ -784,4 +784,77 @@ void ln_clip_finalize(const float* part, const float* sumsq, int nparts, float C
   ln_psgrad_finalize(part, factors_ws, out0, out1, B, chunks, d, out_dt, inv_div, nk0, nk1, s);
 }
 
+// ---------------------------------------------------------------------------------------------
+// Compatibility: the "clipped" dgamma / dbeta of the reference's fused LayerNorm backward
+// (flashdp/core/layernorm_clip.py:109-131, summed by :134-160).  Row r adds its dy*xhat and dy to
+// buffer r % G; every addition after a buffer's first one first saturates the buffer element by
+// element, buf <- partial + buf * min(clamp, C / (|buf| + 1e-10)).  In the reference the rows of a
+// buffer arrive in whatever order the row programs win a spin lock; here they are taken in
+// increasing row order, which makes the result a function of the inputs.  One thread owns one
+// (buffer, column) pair and walks that buffer's rows; no locks, no atomics.  No division by the
+// batch and no noise (the reference's fused path has neither, flashdp/layers/layernorm.py:179-203).
+// ---------------------------------------------------------------------------------------------
+template <typename Tin>
+__global__ void __launch_bounds__(128) ln_saturate_kernel(const Tin* __restrict__ dy, const Tin* __restrict__ x,
+                                                          const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                          float* __restrict__ dw_buf, float* __restrict__ db_buf,
+                                                          int rows, int d, int groups, int pdt, float C, float clamp) {
+  const int c = blockIdx.x * 128 + threadIdx.x;
+  const int g = blockIdx.y;
+  if (c >= d) return;
+  float bw = 0.f, bb = 0.f;
+  bool first = true;
+  for (int r = g; r < rows; r += groups) {
+    const size_t i = static_cast<size_t>(r) * d + c;
+    const float dv = to_f32<Tin>(dy[i]);
+    const float xh = (to_f32<Tin>(x[i]) - mean[r]) * rstd[r];
+    // the partial sums are rounded to the parameter dtype before they are accumulated (:106-107)
+    float pw = dv * xh, pb = dv;
+    if (pdt == FDP_BF16) { pw = __bfloat162float(__float2bfloat16_rn(pw)); pb = __bfloat162float(__float2bfloat16_rn(pb)); }
+    else if (pdt == FDP_F16) { pw = __half2float(__float2half_rn(pw)); pb = __half2float(__float2half_rn(pb)); }
+    if (first) { bw = pw; bb = pb; first = false; }
+    else {
+      bw = pw + bw * clip_factor(fabsf(bw), C, clamp);
+      bb = pb + bb * clip_factor(fabsf(bb), C, clamp);
+    }
+  }
+  dw_buf[static_cast<size_t>(g) * d + c] = bw;
+  db_buf[static_cast<size_t>(g) * d + c] = bb;
+}
+
+__global__ void __launch_bounds__(128) ln_saturate_sum_kernel(const float* __restrict__ dw_buf, const float* __restrict__ db_buf,
+                                                              void* __restrict__ dgamma, void* __restrict__ dbeta, int d,
+                                                              int groups, int out_dt) {
+  const int c = blockIdx.x * 128 + threadIdx.x;
+  if (c >= d) return;
+  float sw = 0.f, sb = 0.f;
+  for (int g = 0; g < groups; ++g) { sw += dw_buf[static_cast<size_t>(g) * d + c]; sb += db_buf[static_cast<size_t>(g) * d + c]; }
+  store_as(dgamma, out_dt, c, sw);
+  if (dbeta != nullptr) store_as(dbeta, out_dt, c, sb);
+}
+
+int ln_saturate_groups(int rows, int d) {
+  // flashdp/core/layernorm_clip.py:261-264, and min(GROUP_SIZE_M, M) of :309
+  int g = 64;
+  if (d <= 8192) g = 96;
+  if (d <= 4096) g = 128;
+  if (d <= 1024) g = 256;
+  return g < rows ? g : rows;
+}
+
+void ln_saturate(const void* dy, const void* x, const float* mean, const float* rstd, float* dw_buf, float* db_buf,
+                 void* dgamma, void* dbeta, int rows, int d, int dt, int pdt, float C, float clamp, cudaStream_t s) {
+  const int groups = ln_saturate_groups(rows, d);
+  dim3 grid(ceil_div(d, 128), groups);
+  if (dt == FDP_F32)
+    ln_saturate_kernel<float><<<grid, 128, 0, s>>>((const float*)dy, (const float*)x, mean, rstd, dw_buf, db_buf, rows, d, groups, pdt, C, clamp);
+  else if (dt == FDP_BF16)
+    ln_saturate_kernel<__nv_bfloat16><<<grid, 128, 0, s>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, mean, rstd, dw_buf, db_buf, rows, d, groups, pdt, C, clamp);
+  else
+    ln_saturate_kernel<__half><<<grid, 128, 0, s>>>((const __half*)dy, (const __half*)x, mean, rstd, dw_buf, db_buf, rows, d, groups, pdt, C, clamp);
+  note_launch();
+  ln_saturate_sum_kernel<<<ceil_div(d, 128), 128, 0, s>>>(dw_buf, db_buf, dgamma, dbeta, d, groups, pdt);
+  note_launch();
+}
+
 }  // namespace fdp

@@ -83,6 +83,14 @@ struct TcArgs {
   uint32_t idesc_half;
   // store epilogue: optional bias[N] (same 16-bit type as the operands) added to every row
   const void* bias; int bias_dt;
+  // fp32 inputs as three bf16 products.  Both operand matrices are then [rows, 2n]: the high bf16
+  // halves of the n columns, then the low halves (x = hi + lo up to 2^-18 |x|).  With terms = 3 the K
+  // loop visits every K range three times -- hi*hi, hi*lo, lo*hi -- into the same accumulator (lo*lo,
+  // 2^-18 of the product, is dropped).  term_stages: K stages of one term before the next term of the
+  // same range begins (a sample's rows for the per-sample kernels; pair 2 of EPI_GRAM: term_stages2).
+  // plane_*: columns of one half of the A / B matrix, i.e. the column offset of its low halves.
+  int terms, term_stages, term_stages2;
+  int plane_a, plane_b, plane_a2, plane_b2;
   // store GEMMs: tiles are walked in groups of m_group tile rows (0 = plain order), so that the CTAs
   // running together cover a squarer patch of the output and re-read less of the operands
   int m_group;
@@ -362,6 +370,18 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     return e < ks1 ? e : ks1;
   };
 
+  // K stage `kl` of an operand pair's K order -> stage within the K range, and which term it belongs to
+  // (0: hi*hi, 1: hi*lo, 2: lo*hi); a no-op for 16-bit inputs (terms == 1)
+  auto term_of = [&](int& kl, bool second) {
+    if (args.terms <= 1) return 0;
+    const int ts = second ? args.term_stages2 : args.term_stages;
+    const int run = args.terms * ts;
+    const int blk = kl / run, w = kl - blk * run;
+    const int term = w / ts;
+    kl = blk * ts + (w - term * ts);
+    return term;
+  };
+
   if (warp == 0) {
     // ================= TMA producer =================
     if (lane == 0) {
@@ -377,31 +397,36 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           const bool second = (EPI == EPI_GRAM) && ks >= args.k_stages;
           const CUtensorMap* ma = second ? &tmA2 : &tmA;
           const CUtensorMap* mb = second ? &tmB2 : &tmB;
-          const int k0 = (second ? ks - args.k_stages : ks) * BK;
+          int kl = second ? ks - args.k_stages : ks;
+          const int term = term_of(kl, second);
+          const int k0 = kl * BK;
+          // column offsets of the planes this term reads (A low halves in term 2, B low halves in term 1)
+          const int ca = term == 2 ? (second ? args.plane_a2 : args.plane_a) : 0;
+          const int cb = term == 1 ? (second ? args.plane_b2 : args.plane_b) : 0;
           const uint32_t sa = base + stage * STG, sb = sa + A_STAGE_BYTES;
           if (EPI == EPI_GRAM) {
             // A: the t-block; B: two independent 128-row s-blocks, one per half of the stage
             // (a unit that contains the diagonal block (i, i) has its t-block in the B stage already:
             // the MMA warp points the A descriptor there and no A copy is made)
             constexpr uint32_t HALF_B = B_STAGE_BYTES / 2;
-            const bool a_in_b = (n0 == m0) || (gram_n1 == m0);
+            const bool a_in_b = term == 0 && ((n0 == m0) || (gram_n1 == m0));
             mbar_expect_tx(full_bar(stage), (a_in_b ? 0 : A_STAGE_BYTES) + (gram_n1 >= 0 ? 2 : 1) * HALF_B);
-            if (!a_in_b) tma_load_2d(sa, ma, k0, row0 + m0, full_bar(stage));
-            tma_load_2d(sb, mb, k0, row0 + n0, full_bar(stage));
-            if (gram_n1 >= 0) tma_load_2d(sb + HALF_B, mb, k0, row0 + gram_n1, full_bar(stage));
+            if (!a_in_b) tma_load_2d(sa, ma, k0 + ca, row0 + m0, full_bar(stage));
+            tma_load_2d(sb, mb, k0 + cb, row0 + n0, full_bar(stage));
+            if (gram_n1 >= 0) tma_load_2d(sb + HALF_B, mb, k0 + cb, row0 + gram_n1, full_bar(stage));
           } else if (CTAS == 1) {
             mbar_expect_tx(full_bar(stage), STG);
             if (A_MN) {
 #pragma unroll
-              for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * (BK * 128), ma, m0 + 64 * i, row0 + k0, full_bar(stage));
+              for (int i = 0; i < BM / 64; ++i) tma_load_2d(sa + i * (BK * 128), ma, m0 + 64 * i + ca, row0 + k0, full_bar(stage));
             } else {
-              tma_load_2d(sa, ma, k0, row0 + m0, full_bar(stage));
+              tma_load_2d(sa, ma, k0 + ca, row0 + m0, full_bar(stage));
             }
             if (B_MN) {
 #pragma unroll
-              for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), mb, n0 + 64 * j, row0 + k0, full_bar(stage));
+              for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * (BK * 128), mb, n0 + 64 * j + cb, row0 + k0, full_bar(stage));
             } else {
-              tma_load_2d(sb, mb, k0, row0 + n0, full_bar(stage));
+              tma_load_2d(sb, mb, k0 + cb, row0 + n0, full_bar(stage));
             }
           } else {
             // both CTAs' copies complete on the leader's barrier, which expects the bytes of both
@@ -410,15 +435,15 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int nb0 = n0 + static_cast<int>(cta_rank) * BN_CTA;
             if (A_MN) {
 #pragma unroll
-              for (int i = 0; i < BM / 64; ++i) tma_load_2d_pair(sa + i * (BK * 128), ma, m0 + 64 * i, row0 + k0, lbar);
+              for (int i = 0; i < BM / 64; ++i) tma_load_2d_pair(sa + i * (BK * 128), ma, m0 + 64 * i + ca, row0 + k0, lbar);
             } else {
-              tma_load_2d_pair(sa, ma, k0, row0 + m0, lbar);
+              tma_load_2d_pair(sa, ma, k0 + ca, row0 + m0, lbar);
             }
             if (B_MN) {
 #pragma unroll
-              for (int j = 0; j < BN_CTA / 64; ++j) tma_load_2d_pair(sb + j * (BK * 128), mb, nb0 + 64 * j, row0 + k0, lbar);
+              for (int j = 0; j < BN_CTA / 64; ++j) tma_load_2d_pair(sb + j * (BK * 128), mb, nb0 + 64 * j + cb, row0 + k0, lbar);
             } else {
-              tma_load_2d_pair(sb, mb, k0, row0 + nb0, lbar);
+              tma_load_2d_pair(sb, mb, k0 + cb, row0 + nb0, lbar);
             }
           }
           if (++stage == NST) { stage = 0; phase ^= 1u; }
@@ -463,8 +488,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             uint32_t sa = base + stage * STG;
             const uint32_t sb = sa + A_STAGE_BYTES;
             if (EPI == EPI_GRAM) {   // diagonal block in this unit: A is the matching half of the B stage
-              if (tn0 == tm0) sa = sb;
-              else if (gram_n1 == tm0) sa = sb + B_STAGE_BYTES / 2;
+              int kl = second ? ks - args.k_stages : ks;
+              if (term_of(kl, second) == 0) {
+                if (tn0 == tm0) sa = sb;
+                else if (gram_n1 == tm0) sa = sb + B_STAGE_BYTES / 2;
+              }
             }
 #pragma unroll
             for (int k16 = 0; k16 < BK / UMMA_K; ++k16) {
@@ -749,6 +777,28 @@ __global__ void __launch_bounds__(256) prescale_kernel(const Tin* __restrict__ G
   }
 }
 
+// ---- fp32 -> (hi, lo) bf16 halves: dst[r, c] = bf16(x), dst[r, n + c] = bf16(x - hi) ---------------------
+__global__ void __launch_bounds__(256) split3_kernel(const float4* __restrict__ src, uint2* __restrict__ dst,
+                                                     size_t nvec, int vec_per_row) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    const float4 v = __ldg(src + i);
+    const float f[4] = {v.x, v.y, v.z, v.w};
+    uint16_t hi[4], lo[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const __nv_bfloat16 h = __float2bfloat16_rn(f[e]);
+      const __nv_bfloat16 l = __float2bfloat16_rn(f[e] - __bfloat162float(h));
+      hi[e] = *reinterpret_cast<const uint16_t*>(&h);
+      lo[e] = *reinterpret_cast<const uint16_t*>(&l);
+    }
+    const size_t row = i / vec_per_row, cv = i - row * vec_per_row;
+    uint2* o = dst + row * (2 * static_cast<size_t>(vec_per_row)) + cv;
+    o[0] = make_uint2(hi[0] | (static_cast<uint32_t>(hi[1]) << 16), hi[2] | (static_cast<uint32_t>(hi[3]) << 16));
+    o[vec_per_row] = make_uint2(lo[0] | (static_cast<uint32_t>(lo[1]) << 16), lo[2] | (static_cast<uint32_t>(lo[3]) << 16));
+  }
+}
+
 // ---- host side ------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -916,7 +966,23 @@ int tc_wait_selftest(int* status, long long limit_cycles, cudaStream_t s) {
 TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo) {
   TcPlan p; p.ok = false; p.algo = FDP_NORM_DIRECT; p.ws_bytes = 0; p.nparts = 0; p.scaled_epilogue = false;
   p.short_seq = false; p.split_bytes = 0;
-  if (dt != FDP_BF16 && dt != FDP_F16) return p;
+  p.split3 = false; p.split3_g_bytes = p.split3_x_bytes = 0;
+  const bool fp32_tensor = (norm_algo & FDP_FP32_TENSOR) != 0;
+  norm_algo &= FDP_NORM_MASK;
+  if (dt == FDP_F32) {
+    // fp32 on the tensor cores as three bf16 products (hi*hi + hi*lo + lo*hi, fp32 accumulation), on
+    // request only: the tensor cores add into their fp32 accumulators by truncation, a one-sided error
+    // of about 2^-24 per K=16 step that a few hundred steps carry past the fp32 tolerance of 1e-5
+    // (measured 3e-5 on the norms at 4096 columns).  Needs whole 64-column K stages per half (the Gram
+    // pass contracts over the columns), samples made of whole 64-row stages, and the per-sample
+    // epilogue (a pre-scaled copy would round c_b * G to bf16 again).
+    if (!fp32_tensor || n_in % BK != 0 || n_out % BK != 0 || n_in < 128 || n_out < 128 || T % BK != 0 || T < 2 * BK) return p;
+    p.split3 = true;
+    p.split3_g_bytes = align256(static_cast<size_t>(B) * T * n_out * 4);
+    p.split3_x_bytes = align256(static_cast<size_t>(B) * T * n_in * 4);
+  } else if (dt != FDP_BF16 && dt != FDP_F16) {
+    return p;
+  }
   if (n_in % 8 != 0 || n_out % 8 != 0 || n_in < 128 || n_out < 128) return p;
   if (T < SHORT_SEQ) {
     // short sequences: the norms come from the small Gram kernel (one partial per sample); the
@@ -927,7 +993,9 @@ TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo) {
     p.ws_bytes = p.split_bytes + align256(static_cast<size_t>(B) * T * n_out * 2);
     return p;
   }
-  const bool direct_ok = (T % BK == 0);   // a K stage must not run into the next sample's rows
+  // direct: a K stage must not run into the next sample's rows; with split operands the tile must also
+  // stay inside its half of the columns (the sum-of-squares epilogue does not mask columns)
+  const bool direct_ok = (T % BK == 0) && (!p.split3 || (n_out % BM == 0 && n_in % BN == 0));
   // Cost of the two norm algorithms in K stages on the critical path: both kernels deal equal work
   // units (128x256 tiles) round-robin to one CTA per SM, so a pass takes
   // ceil(units / SMs) * (stages per unit + a fixed cost per unit of about four stages).  The SM
@@ -935,9 +1003,10 @@ TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo) {
   constexpr long long PLAN_SMS = 148, UNIT_FIXED_STAGES = 4;
   const long long units_d = static_cast<long long>(B) * ceil_div(n_out, BM) * ceil_div(n_in, BN);
   const long long units_g = static_cast<long long>(B) * gram_tiles(T);
-  const double direct = static_cast<double>((units_d + PLAN_SMS - 1) / PLAN_SMS) * (ceil_div(T, BK) + UNIT_FIXED_STAGES);
+  const int terms = p.split3 ? 3 : 1;
+  const double direct = static_cast<double>((units_d + PLAN_SMS - 1) / PLAN_SMS) * (terms * ceil_div(T, BK) + UNIT_FIXED_STAGES);
   const double gram = static_cast<double>((units_g + PLAN_SMS - 1) / PLAN_SMS) *
-                      (ceil_div(n_in, BK) + ceil_div(n_out, BK) + UNIT_FIXED_STAGES);
+                      (terms * (ceil_div(n_in, BK) + ceil_div(n_out, BK)) + UNIT_FIXED_STAGES);
   int algo = norm_algo;
   if (algo == FDP_NORM_AUTO) algo = (direct_ok && direct <= gram) ? FDP_NORM_DIRECT : FDP_NORM_GRAM;
   if (algo == FDP_NORM_DIRECT && !direct_ok) algo = FDP_NORM_GRAM;
@@ -947,40 +1016,58 @@ TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo) {
   // inside one sample and a sample's main loop is long enough to hide the per-sample drain;
   // FDP_WGRAD_PRESCALE=1 forces the pre-scale pass (for A/B measurements)
   static const bool force_prescale = [] { const char* e = getenv("FDP_WGRAD_PRESCALE"); return e && e[0] == '1'; }();
-  p.scaled_epilogue = !force_prescale && (T % BK == 0) && T >= 256;
+  p.scaled_epilogue = p.split3 || (!force_prescale && (T % BK == 0) && T >= 256);
   // one partial per work unit and epilogue warp
   p.nparts = 4 * ((algo == FDP_NORM_DIRECT) ? ceil_div(n_out, BM) * ceil_div(n_in, BN) : gram_tiles(T));
   // the parked accumulators of the split-K tail, then (pre-scale path only) the c_b-scaled copy of G
   p.split_bytes = split_ws_bytes();
-  p.ws_bytes = p.split_bytes + (p.scaled_epilogue ? 0 : align256(static_cast<size_t>(B) * T * n_out * 2));
+  p.ws_bytes = p.split_bytes + (p.scaled_epilogue ? 0 : align256(static_cast<size_t>(B) * T * n_out * 2)) +
+               p.split3_g_bytes + p.split3_x_bytes;
   return p;
+}
+
+int tc_split3(const void* src, void* dst, size_t rows, int n, cudaStream_t s) {
+  const size_t nvec = rows * n / 4;
+  size_t blocks = (nvec + 255) / 256;
+  const size_t cap = static_cast<size_t>(sm_count()) * 16;
+  split3_kernel<<<static_cast<unsigned>(blocks < cap ? blocks : cap), 256, 0, s>>>(
+      static_cast<const float4*>(src), static_cast<uint2*>(dst), nvec, n / 4);
+  note_launch();
+  return cudaPeekAtLastError() == cudaSuccess ? FDP_OK : (cudaGetLastError(), FDP_ERR_LAUNCH);
 }
 
 int tc_norms(const void* G, const void* X, float* partials, int* dev_status, int B, int T, int n_in,
              int n_out, int dt, const TcPlan& pl, cudaStream_t s) {
   const uint64_t rows = static_cast<uint64_t>(B) * T;
+  const int terms = pl.split3 ? 3 : 1;
+  const int wo = pl.split3 ? 2 * n_out : n_out, wi = pl.split3 ? 2 * n_in : n_in;   // matrix widths
   CUtensorMap a, b, a2, b2;
   TcArgs args{};
   args.batch = B; args.batch_rows = T; args.partials = partials; args.status = dev_status; args.T = T;
+  args.terms = terms;
   if (pl.algo == FDP_NORM_DIRECT) {
-    if (!make_map(&a, G, rows, n_out, 64, BK, dt) || !make_map(&b, X, rows, n_in, 64, BK, dt)) return FDP_ERR_LAUNCH;
+    if (!make_map(&a, G, rows, wo, 64, BK, dt) || !make_map(&b, X, rows, wi, 64, BK, dt)) return FDP_ERR_LAUNCH;
     args.M = n_out; args.N = n_in;
     args.tiles_m = ceil_div(n_out, BM); args.tiles_n = ceil_div(n_in, BN);
     args.tiles_per_batch = args.tiles_m * args.tiles_n;
-    args.k_stages = T / BK;
+    args.term_stages = T / BK;
+    args.k_stages = terms * (T / BK);
+    args.plane_a = n_out; args.plane_b = n_in;
     args.idesc = make_idesc(dt, true, true);
     return launch<true, true, EPI_SUMSQ>(a, b, a, b, args, s);
   }
   // A and B boxes are both 128 rows: a B stage is filled by two independent copies
-  if (!make_map(&a, G, rows, n_out, BK, BM, dt) || !make_map(&b, G, rows, n_out, BK, BN / 2, dt) ||
-      !make_map(&a2, X, rows, n_in, BK, BM, dt) || !make_map(&b2, X, rows, n_in, BK, BN / 2, dt))
+  if (!make_map(&a, G, rows, wo, BK, BM, dt) || !make_map(&b, G, rows, wo, BK, BN / 2, dt) ||
+      !make_map(&a2, X, rows, wi, BK, BM, dt) || !make_map(&b2, X, rows, wi, BK, BN / 2, dt))
     return FDP_ERR_LAUNCH;
   args.M = T; args.N = T;
   args.gram_nb = ceil_div(T, BM);
   args.tiles_m = args.gram_nb; args.tiles_n = args.gram_nb;
   args.tiles_per_batch = gram_tiles(T);
   args.idesc_half = make_idesc(dt, false, false, 1, BN / 2);
-  args.k_stages = ceil_div(n_out, BK); args.k_stages2 = ceil_div(n_in, BK);
+  args.term_stages = ceil_div(n_out, BK); args.term_stages2 = ceil_div(n_in, BK);
+  args.k_stages = terms * args.term_stages; args.k_stages2 = terms * args.term_stages2;
+  args.plane_a = args.plane_b = n_out; args.plane_a2 = args.plane_b2 = n_in;
   args.idesc = make_idesc(dt, false, false);
   return launch<false, false, EPI_GRAM>(a, b, a2, b2, args, s);
 }
@@ -1001,19 +1088,23 @@ bool tc_fused_factors_ok(int B) { return B <= MAX_SMEM_FACTORS; }
 
 int tc_clipped_wgrad(const void* Gs, const void* X, const TcFactorSource* fs, float* split_ws,
                      void* dW, int* dev_status, int B, int T, int n_in, int n_out, int dt, int out_dt,
-                     int layout, float inv_div, NoiseKey nk, cudaStream_t s) {
+                     int layout, float inv_div, NoiseKey nk, cudaStream_t s, int terms) {
   const uint64_t rows = static_cast<uint64_t>(B) * T;
   const bool scaled = fs != nullptr;  // Gs is then the unscaled G
+  if (terms != 1 && !(terms == 3 && scaled)) return FDP_ERR_ARG;
   CUtensorMap mg, mx;
-  if (!make_map(&mg, Gs, rows, n_out, 64, BK, dt) || !make_map(&mx, X, rows, n_in, 64, BK, dt)) return FDP_ERR_LAUNCH;
+  if (!make_map(&mg, Gs, rows, terms == 3 ? 2 * n_out : n_out, 64, BK, dt) ||
+      !make_map(&mx, X, rows, terms == 3 ? 2 * n_in : n_in, 64, BK, dt)) return FDP_ERR_LAUNCH;
   TcArgs args{};
   args.batch = 1; args.batch_rows = 0; args.status = dev_status;
-  args.k_stages = static_cast<int>((rows + BK - 1) / BK);
+  args.terms = terms;
+  args.term_stages = T / BK;      // used when terms == 3: every sample's rows are visited three times
+  args.k_stages = terms * static_cast<int>((rows + BK - 1) / BK);
   args.out = dW; args.out_dt = out_dt; args.scale = inv_div; args.nk = nk;
   const int ctas = ctas_per_tile();
   args.idesc = make_idesc(dt, true, true, ctas);
   if (scaled) {
-    args.segs = B; args.seg_stages = T / BK;
+    args.segs = B; args.seg_stages = terms * (T / BK);
     args.factors = fs->factors;
     if (fs->factors == nullptr) {
       if (!tc_fused_factors_ok(B) || fs->norm_partials == nullptr) return FDP_ERR_ARG;
@@ -1025,6 +1116,7 @@ int tc_clipped_wgrad(const void* Gs, const void* X, const TcFactorSource* fs, fl
   // [out,in]: A = G (M = n_out), B = X (N = n_in); [in,out]: operands swap roles, no transpose pass
   const bool oi = (layout == FDP_OUT_IN);
   args.M = oi ? n_out : n_in; args.N = oi ? n_in : n_out; args.ld_out = args.N;
+  args.plane_a = args.M; args.plane_b = args.N;
   args.tiles_m = ceil_div(args.M, BM * ctas); args.tiles_n = ceil_div(args.N, BN);
   args.tiles_per_batch = args.tiles_m * args.tiles_n;
   static const int m_group = [] { const char* e = getenv("FDP_TC_MGROUP"); return e ? atoi(e) : 8; }();

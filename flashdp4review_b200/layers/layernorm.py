@@ -8,6 +8,11 @@ flashdp/core/layernorm_clip.py:163-198, called from flashdp/layers/layernorm.py:
 spin lock, adds no noise and depends on block order (flashdp/core/layernorm_clip.py:109-131), so
 it cannot be reproduced or relied on; and the per-sample path's second noise draw, which the
 reference adds to grad_weight (flashdp/layers/layernorm.py:150), goes to grad_bias here.
+
+`compat_fused_saturation=True` (with use_fused) reproduces the reference's fused arithmetic instead --
+element-wise saturation of 64..256 row-group buffers, no division by the batch, no noise
+(flashdp/layers/layernorm.py:170-204) -- with the rows of a buffer taken in increasing order.  It is
+there for comparisons with the reference's default; it is not differentially private.
 """
 import numbers
 
@@ -33,6 +38,13 @@ class _DPLayerNormFunc(Function):
     def backward(ctx, grad_output):
         input, weight, mean, rstd = ctx.saved_tensors
         layer = ctx.layer
+        if layer.compat_fused_saturation:
+            clip_args = torch.tensor([layer.C, layer.clamp_value])
+            dx, dw_, db_, args = ops.layernorm_bwd_clip_fused(grad_output, input, weight, None, clip_args,
+                                                             {"mean": mean, "rstd": rstd})
+            dw, db = ops.layernorm_dwdb_fused(weight, None, dw_, db_, args)
+            return (dx if ctx.needs_input_grad[0] else None, dw if ctx.needs_input_grad[1] else None,
+                    db if ctx.has_bias and ctx.needs_input_grad[2] else None, None)
         B = input.shape[0] if input.dim() > 1 else 1
         step = layer._next_step()
         div, noise = dp_scalars(B, layer.noise_multiplier, layer._dp_param_ids[0], step,
@@ -51,7 +63,8 @@ class _DPLayerNormFunc(Function):
 class DPLayerNorm(nn.LayerNorm, DPLayerMixin):
     def __init__(self, normalized_shape, eps: float = 1e-5, elementwise_affine: bool = True,
                  bias: bool = True, device=None, dtype=None, use_fused: bool = True, C: float = 1.0,
-                 clamp_value: float = 1.0, noise_multiplier: float = 1.0) -> None:
+                 clamp_value: float = 1.0, noise_multiplier: float = 1.0,
+                 compat_fused_saturation: bool = False) -> None:
         if isinstance(normalized_shape, numbers.Integral):
             normalized_shape = (normalized_shape,)
         use_bias = bias is not None   # the reference's rule (flashdp/layers/layernorm.py:42)
@@ -59,6 +72,7 @@ class DPLayerNorm(nn.LayerNorm, DPLayerMixin):
             raise NotImplementedError("In fused mode, bias must be enabled. Set use_fused=False to use the default implementation.")
         super().__init__(normalized_shape, eps, elementwise_affine, use_bias, device=device, dtype=dtype)
         self.use_fused = use_fused
+        self.compat_fused_saturation = bool(compat_fused_saturation) and use_fused
         self._init_dp(C, clamp_value, noise_multiplier)
         if self.elementwise_affine:
             self.weight = Parameter(self.weight.data)

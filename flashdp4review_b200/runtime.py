@@ -22,6 +22,7 @@ class _Run:
     rank = 0
     # SMs the persistent GEMM grids leave free while a gradient all-reduce is in flight (world > 1)
     reserve_sms = int(os.environ.get("FDP_DP_RESERVE_SMS", "12"))
+    fp32_mode = "exact"           # "exact": fp32 FMA kernels; "tensor": three bf16 tensor-core products
     input_grad_impl = "library"   # "library": cuBLAS via torch (as the reference); "native": fdp_linear_dgrad
     micro_index = 0               # gradient accumulation: which micro-step of `micro_steps` runs now
     micro_steps = 1
@@ -146,6 +147,20 @@ def accumulate(micro_index: int, micro_steps: int):
         yield
     finally:
         set_accumulation(0, 1)
+
+
+def set_fp32_mode(name: str):
+    """How fp32 layers compute their DP weight gradients: "exact" (default) keeps true fp32 arithmetic,
+    the reference's own, within 1e-5 of it; "tensor" runs 64-aligned shapes on the tensor cores as three
+    bf16 products (hi*hi + hi*lo + lo*hi) -- 10 to 25 times faster, within about 1e-4 (the tensor cores
+    add into their fp32 accumulators by truncation)."""
+    if name not in ("exact", "tensor"):
+        raise ValueError("fp32_mode must be 'exact' or 'tensor'")
+    _run.fp32_mode = name
+
+
+def fp32_mode():
+    return _run.fp32_mode
 
 
 def set_input_grad_impl(name: str):

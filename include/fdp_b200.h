@@ -59,7 +59,15 @@ enum fdp_norm_algo {
   FDP_NORM_AUTO = 0,   /* pick per shape; sequences shorter than 64 rows use the Gram identity on T x T
                         * blocks (for T = 1, i.e. 2-D layer inputs, that is ||g_b|| * ||x_b||) */
   FDP_NORM_DIRECT = 1, /* per-sample GEMM tiles, squared and reduced in the epilogue, never stored */
-  FDP_NORM_GRAM = 2    /* sum_{t,s} (G_b G_b^T)_{ts} (X_b X_b^T)_{ts} */
+  FDP_NORM_GRAM = 2,   /* sum_{t,s} (G_b G_b^T)_{ts} (X_b X_b^T)_{ts} */
+  FDP_NORM_MASK = 15,
+  /* flag, OR-ed into the norm_algo argument of fdp_linear_wgrad and of its workspace query: fp32 inputs
+   * with 64-aligned shapes (n_in, n_out and T multiples of 64, T >= 128) run on the tensor cores as
+   * three bf16 products (x = hi + lo: hi*hi + hi*lo + lo*hi) instead of fp32 FMAs -- 10 to 25 times
+   * faster, but the tensor cores' truncating fp32 accumulation leaves norms and gradients within about
+   * 1e-4 of the exact result, not 1e-5.  Without the flag fp32 inputs keep exact fp32 arithmetic, the
+   * reference's own (flashdp/core/utils.py:9-12: fp32 accumulates in fp32). */
+  FDP_FP32_TENSOR = 16
 };
 
 /* DP hyper-parameters of one call.  C / clamp_value are the arguments of
@@ -203,6 +211,25 @@ int fdp_layernorm_bwd(const void* dy, const void* x, const void* gamma, const fl
                       float* norms_beta, int B, int T, int d, int dtype, int param_dtype,
                       const fdp_dp_params* p, void* workspace, size_t workspace_bytes,
                       fdp_stream_t stream);
+
+/* ---- LayerNorm, compatibility mode --------------------------------------------------------------
+ * The dgamma / dbeta of the reference's FUSED backward: _layer_norm_bwd_dx_fused_clip accumulates row
+ * r's dy*xhat and dy into buffer r % G under a spin lock, saturating the buffer element by element
+ * before every addition but the first -- buf <- partial + buf * min(clamp, C / (|buf| + 1e-10)) --
+ * and _layer_norm_bwd_dwdb sums the G buffers (flashdp/core/layernorm_clip.py:109-131, :134-160; G from
+ * :261-264).  No division by the batch, no noise (flashdp/layers/layernorm.py:179-203).  In the
+ * reference the rows of a buffer are added in lock-acquisition order, so its result varies from run
+ * to run; this entry point takes them in increasing row order.  It is not per-sample clipping: use
+ * fdp_layernorm_bwd for DP training.  dx comes from fdp_layernorm_bwd.
+ *   dy, x [rows,d] in `dtype`; mean, rstd float[rows]; dgamma, dbeta (may be NULL) [d] in `param_dtype`.
+ *   The workspace holds the G buffers of both tensors, [G,d] floats each, dgamma's first: a caller may
+ *   read them after the call (they are the reference's dw_ / db_).
+ */
+size_t fdp_layernorm_saturate_workspace_bytes(int rows, int d);
+int fdp_layernorm_saturate_groups(int rows, int d);
+int fdp_layernorm_bwd_saturate(const void* dy, const void* x, const float* mean, const float* rstd, void* dgamma,
+                               void* dbeta, int rows, int d, int dtype, int param_dtype, float C, float clamp_value,
+                               void* workspace, size_t workspace_bytes, fdp_stream_t stream);
 
 #ifdef __cplusplus
 }

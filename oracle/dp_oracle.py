@@ -150,6 +150,48 @@ def layernorm_affine_grads(dy, xhat, C: float, clamp_value: float,
     return dgamma, dbeta, nw, nb
 
 
+def layernorm_saturate_groups(rows: int, d: int) -> int:
+    """GROUP_SIZE_M of flashdp/core/layernorm_clip.py:261-264, capped by the row count (:309)."""
+    g = 64
+    if d <= 8192:
+        g = 96
+    if d <= 4096:
+        g = 128
+    if d <= 1024:
+        g = 256
+    return min(g, rows)
+
+
+def layernorm_fused_saturation(dy, xhat, C: float, clamp_value: float, round_to=None):
+    """The reference's FUSED dgamma / dbeta (flashdp/core/layernorm_clip.py:104-131, :134-160) with the
+    rows of each of the G buffers added in increasing row order (the reference's order is whatever its
+    spin lock yields): row r goes to buffer r % G; the first row of a buffer is stored, every later one
+    is added to the buffer after the buffer was scaled element-wise by min(clamp, C / (|buf| + 1e-10)).
+    Arithmetic in float32 like the reference's accumulation dtype; `round_to` (a torch dtype) rounds
+    the per-row partials as the reference's `.to(w.dtype)` does.  Returns (dgamma, dbeta, dw_, db_)."""
+    import torch
+    dy = torch.as_tensor(_f64(dy)).float()
+    xh = torch.as_tensor(_f64(xhat)).float()
+    d = dy.shape[-1]
+    dy, xh = dy.reshape(-1, d), xh.reshape(-1, d)
+    rows = dy.shape[0]
+    G = layernorm_saturate_groups(rows, d)
+    bw = torch.zeros(G, d)
+    bb = torch.zeros(G, d)
+    f = lambda b: torch.clamp(C / (b.abs() + EPS_NORM), max=clamp_value)
+    for k, r0 in enumerate(range(0, rows, G)):
+        pw, pb = dy[r0:r0 + G] * xh[r0:r0 + G], dy[r0:r0 + G].clone()
+        if round_to is not None:
+            pw, pb = pw.to(round_to).float(), pb.to(round_to).float()
+        n = pw.shape[0]
+        if k == 0:
+            bw[:n], bb[:n] = pw, pb
+        else:
+            bw[:n] = pw + bw[:n] * f(bw[:n])
+            bb[:n] = pb + bb[:n] * f(bb[:n])
+    return bw.sum(0).numpy(), bb.sum(0).numpy(), bw.numpy(), bb.numpy()
+
+
 # --------------------------------------------------------------------------------------
 # Gaussian noise: counter-based restatement of what the CUDA epilogues draw.
 # The reference draws torch.normal(std=noise_multiplier/sqrt(B)) from the global generator

@@ -95,3 +95,37 @@ def test_layernorm_shape_limit(ops):
     m = torch.zeros(4, device=dev())
     with pytest.raises(RuntimeError):
         ops.dp_layernorm_backward(x, x, torch.ones(8200, device=dev()), m, m, 1.0, 1.0)
+
+
+@pytest.mark.parametrize("shape,dtype", [((4, 300, 256), torch.float32), ((2, 1024, 1024), torch.bfloat16),
+                                         ((3, 50, 72), torch.float32), ((1, 40, 2048), torch.float16)])
+def test_fused_saturation_compat_mode(shape, dtype, ops):
+    """`compat_fused_saturation`: the reference's fused dgamma / dbeta arithmetic with a fixed row order
+    (flashdp/core/layernorm_clip.py:109-131) against its CPU restatement; bit-equal reruns; dx is the
+    ordinary LayerNorm input gradient."""
+    import flashdp4review_b200 as fdp
+    B, T, d = shape
+    gen = torch.Generator().manual_seed(sum(shape))
+    X = (torch.randn(B, T, d, generator=gen) * 1.5 + 0.3).to(dtype)
+    DY = (torch.randn(B, T, d, generator=gen) * 0.2).to(dtype)
+    C = 0.05                                         # |buffer| passes C within a few rows: the saturation acts
+    ln = fdp.DPLayerNorm(d, C=C, clamp_value=1.0, compat_fused_saturation=True).to(dev())
+    x = X.to(dev()).requires_grad_(True)
+    ln(x).backward(DY.to(dev()))
+    g1, b1 = ln.weight.grad.clone(), ln.bias.grad.clone()
+    _, wmean, wrstd = O.layernorm_fwd(X, np.ones(d), np.zeros(d), 1e-5)
+    xhat = (X.double().numpy() - wmean[..., None]) * wrstd[..., None]
+    wg, wb, _, _ = O.layernorm_fused_saturation(DY, xhat, C, 1.0)
+    tol = 1e-4 if dtype == torch.float32 else 2e-2   # xhat from the kernel's own fp32 statistics; saturating recurrences amplify
+    assert rel_err(g1.cpu().numpy(), wg) < tol and rel_err(b1.cpu().numpy(), wb) < tol
+    assert rel_err(x.grad.float().cpu().numpy(), O.layernorm_bwd_dx(DY, X, np.ones(d), wmean, wrstd)) < (1e-5 if dtype == torch.float32 else 1e-2)
+    ln.weight.grad = None
+    ln.bias.grad = None
+    x2 = X.to(dev()).requires_grad_(True)
+    ln(x2).backward(DY.to(dev()))
+    assert torch.equal(ln.weight.grad, g1) and torch.equal(ln.bias.grad, b1)
+    # not the per-sample clipping of the default mode
+    ref = fdp.DPLayerNorm(d, C=C, clamp_value=1.0, noise_multiplier=0.0).to(dev())
+    x3 = X.to(dev()).requires_grad_(True)
+    ref(x3).backward(DY.to(dev()))
+    assert rel_err(ref.weight.grad.cpu().numpy(), g1.cpu().numpy()) > 1e-2
