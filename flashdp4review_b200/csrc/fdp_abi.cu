@@ -220,7 +220,7 @@ int fdp_linear_wgrad(const void* G, const void* X, void* dW, float* norms_out, f
   if (norm_algo < 0 || (norm_algo & ~(FDP_NORM_MASK | FDP_FP32_TENSOR)) != 0 || (norm_algo & FDP_NORM_MASK) > FDP_NORM_GRAM)
     return FDP_ERR_ARG;
   if (!valid_dtype(in_dtype) || !valid_dtype(out_dtype)) return FDP_ERR_DTYPE;
-  if (static_cast<long long>(B) * T >= (1ll << 31) / 2 || B > 65535) return FDP_ERR_SHAPE;  // B is a grid dimension
+  if (static_cast<long long>(B) * T >= (1ll << 31) / 2) return FDP_ERR_SHAPE;   // row indices are 32-bit
   int st = check_params(p);
   if (st != FDP_OK) return st;
   if ((st = current_device_ok()) != FDP_OK) return st;
@@ -304,7 +304,7 @@ int fdp_bias_grad(const void* G, void* db, float* norms_out, float* factors_out,
                   size_t workspace_bytes, fdp_stream_t stream) {
   if (G == nullptr || db == nullptr) return FDP_ERR_ARG;
   if (B <= 0 || T <= 0 || n_out <= 0) return FDP_ERR_ARG;
-  if (B > 65535) return FDP_ERR_SHAPE;  // B is a grid dimension
+  if (static_cast<long long>(B) * T >= (1ll << 31) / 2) return FDP_ERR_SHAPE;   // row indices are 32-bit
   if (!valid_dtype(in_dtype) || !valid_dtype(out_dtype)) return FDP_ERR_DTYPE;
   int st = check_params(p);
   if (st != FDP_OK) return st;
@@ -416,7 +416,7 @@ int fdp_layernorm_bwd(const void* dy, const void* x, const void* gamma, const fl
     return FDP_ERR_ARG;
   if (B <= 0 || T <= 0 || d <= 0) return FDP_ERR_ARG;
   if (!valid_dtype(dtype) || !valid_dtype(param_dtype)) return FDP_ERR_DTYPE;
-  if (d > 8192 || B > 32767) return FDP_ERR_SHAPE;  // 2*B is a grid dimension
+  if (d > 8192 || static_cast<long long>(B) * T >= (1ll << 31) / 2) return FDP_ERR_SHAPE;
   int st = check_params(p);
   if (st != FDP_OK) return st;
   if ((st = current_device_ok()) != FDP_OK) return st;

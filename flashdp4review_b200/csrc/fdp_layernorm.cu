@@ -419,7 +419,8 @@ __global__ void __launch_bounds__(STAGED ? CW + 32 : CW) ln_bwd_kernel(
   const WaitCtx wctx{&abort_flag_s, nullptr, sticky, WAIT_LIMIT_CYCLES};
   const int rg = (threadIdx.x % CW) / TPR, t = threadIdx.x % TPR;
   const int lane = threadIdx.x & 31, wig = (threadIdx.x % TPR) >> 5;
-  const int b = blockIdx.y, chunk = blockIdx.x;
+  // one-dimensional grid (the batch may exceed 65535): block = b * chunks + chunk
+  const int b = blockIdx.x / chunks, chunk = blockIdx.x % chunks;
   const int r0 = chunk * rows_per_block, r1 = min(T, r0 + rows_per_block);
   const int n_iter = (r1 - r0 + RG - 1) / RG;
   const uint32_t row_bytes = static_cast<uint32_t>(d) * sizeof(Tin);
@@ -621,7 +622,7 @@ template <typename Tin, int VEC, int NV, int TPRV, bool STAGED, int CW>
 static bool ln_bwd_launch_one(const void* dy, const void* x, const void* gamma, const float* mean,
                               const float* rstd, void* dx, float* dg_part, float* db_part, int B, int T,
                               int d, int pdt, const LnPlan& pl, int n_stages, cudaStream_t s) {
-  dim3 grid(pl.chunks, B);
+  const unsigned grid = static_cast<unsigned>(static_cast<size_t>(B) * pl.chunks);
   constexpr int RG = CW / TPRV;
   const size_t reduce_bytes = static_cast<size_t>(CW) * NV * VEC * sizeof(float);
   const size_t stage_bytes = static_cast<size_t>(2) * RG * d * sizeof(Tin);
@@ -691,9 +692,11 @@ __global__ void __launch_bounds__(256) ln_psgrad_reduce_kernel(float* __restrict
                                                                float* __restrict__ sumsq, int chunks,
                                                                int d) {
   __shared__ float red[32];
-  // blockIdx.y = tensor*B + b, blockIdx.x = block of 256 columns
-  float* p = part + static_cast<size_t>(blockIdx.y) * chunks * d;
-  const int c = blockIdx.x * 256 + threadIdx.x;
+  // one-dimensional grid: block = (tensor*B + b) * column blocks + block of 256 columns
+  const int nblk = (d + 255) / 256;
+  const int sample = blockIdx.x / nblk, cblk = blockIdx.x % nblk;
+  float* p = part + static_cast<size_t>(sample) * chunks * d;
+  const int c = cblk * 256 + threadIdx.x;
   float sq = 0.f;
   if (c < d) {
     float t = 0.f;
@@ -702,13 +705,13 @@ __global__ void __launch_bounds__(256) ln_psgrad_reduce_kernel(float* __restrict
     sq = t * t;
   }
   sq = block_sum(sq, red);
-  if (threadIdx.x == 0) sumsq[blockIdx.y * gridDim.x + blockIdx.x] = sq;
+  if (threadIdx.x == 0) sumsq[blockIdx.x] = sq;
 }
 
 int ln_sumsq_parts(int d) { return ceil_div(d, 256); }
 
 void ln_psgrad_reduce(float* part, float* sumsq, int B, int chunks, int d, cudaStream_t s) {
-  dim3 grid(ln_sumsq_parts(d), 2 * B);
+  const unsigned grid = static_cast<unsigned>(static_cast<size_t>(2) * B * ln_sumsq_parts(d));
   ln_psgrad_reduce_kernel<<<grid, 256, 0, s>>>(part, sumsq, chunks, d);
   note_launch();
 }

@@ -58,14 +58,16 @@ template <typename Tin>
 __global__ void __launch_bounds__(256) simt_norm_direct_kernel(const Tin* __restrict__ G,
                                                                const Tin* __restrict__ X,
                                                                float* __restrict__ partials, int T,
-                                                               int n_in, int n_out) {
+                                                               int n_in, int n_out, int tiles_n, int tiles_m) {
   __shared__ float red[32];
-  const int b = blockIdx.z;
+  // one-dimensional grid (the batch may exceed the 65535 limit of the other grid dimensions):
+  // block = (b * tiles_m + tile row) * tiles_n + tile column
+  const int bx = blockIdx.x % tiles_n, by = (blockIdx.x / tiles_n) % tiles_m;
+  const int b = blockIdx.x / (tiles_n * tiles_m);
   const Tin* Gb = G + static_cast<size_t>(b) * T * n_out;
   const Tin* Xb = X + static_cast<size_t>(b) * T * n_in;
   float acc[4][4] = {};
-  simt_tile<Tin, false>(Gb, n_out, 1, Xb, n_in, 1, T, n_out, n_in, blockIdx.y * TM, blockIdx.x * TN,
-                        nullptr, 1, acc);
+  simt_tile<Tin, false>(Gb, n_out, 1, Xb, n_in, 1, T, n_out, n_in, by * TM, bx * TN, nullptr, 1, acc);
   float s = 0.f;
 #pragma unroll
   for (int i = 0; i < 4; ++i)
@@ -73,20 +75,21 @@ __global__ void __launch_bounds__(256) simt_norm_direct_kernel(const Tin* __rest
     for (int j = 0; j < 4; ++j) s = fmaf(acc[i][j], acc[i][j], s);
   s = block_sum(s, red);
   if (threadIdx.x == 0)
-    partials[(static_cast<size_t>(b) * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x] = s;
+    partials[blockIdx.x] = s;
 }
 
 int simt_norm_tiles(int n_in, int n_out) { return ceil_div(n_in, TN) * ceil_div(n_out, TM); }
 
 void simt_norm_direct(const void* G, const void* X, float* partials, int B, int T, int n_in,
                       int n_out, int dt, cudaStream_t s) {
-  dim3 grid(ceil_div(n_in, TN), ceil_div(n_out, TM), B);
+  const int tn = ceil_div(n_in, TN), tm = ceil_div(n_out, TM);
+  const unsigned grid = static_cast<unsigned>(static_cast<size_t>(B) * tn * tm);
   if (dt == FDP_F32)
-    simt_norm_direct_kernel<float><<<grid, 256, 0, s>>>((const float*)G, (const float*)X, partials, T, n_in, n_out);
+    simt_norm_direct_kernel<float><<<grid, 256, 0, s>>>((const float*)G, (const float*)X, partials, T, n_in, n_out, tn, tm);
   else if (dt == FDP_BF16)
-    simt_norm_direct_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)G, (const __nv_bfloat16*)X, partials, T, n_in, n_out);
+    simt_norm_direct_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)G, (const __nv_bfloat16*)X, partials, T, n_in, n_out, tn, tm);
   else
-    simt_norm_direct_kernel<__half><<<grid, 256, 0, s>>>((const __half*)G, (const __half*)X, partials, T, n_in, n_out);
+    simt_norm_direct_kernel<__half><<<grid, 256, 0, s>>>((const __half*)G, (const __half*)X, partials, T, n_in, n_out, tn, tm);
   note_launch();
 }
 
@@ -331,12 +334,14 @@ template <typename Tin, int VEC>
 __global__ void __launch_bounds__(256) gstats_kernel(const Tin* __restrict__ G,
                                                      float* __restrict__ colsum_part,
                                                      float* __restrict__ sq_part, int T, int n_out,
-                                                     int rows_per_chunk, int vec_ok) {
+                                                     int rows_per_chunk, int vec_ok, int col_chunks, int row_chunks) {
   __shared__ float cs[8][32 * VEC];
   __shared__ float red[32];
   const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
-  const int b = blockIdx.z, rc = blockIdx.y;
-  const int c0 = (blockIdx.x * 32 + x) * VEC;
+  // one-dimensional grid (the batch may exceed 65535): block = (b * row_chunks + rc) * col_chunks + cc
+  const int cc = blockIdx.x % col_chunks, rc = (blockIdx.x / col_chunks) % row_chunks;
+  const int b = blockIdx.x / (col_chunks * row_chunks);
+  const int c0 = (cc * 32 + x) * VEC;
   const int r0 = rc * rows_per_chunk, r1 = min(T, r0 + rows_per_chunk);
   const Tin* Gb = G + static_cast<size_t>(b) * T * n_out;
   float acc[VEC];
@@ -381,14 +386,14 @@ __global__ void __launch_bounds__(256) gstats_kernel(const Tin* __restrict__ G,
   for (int v = 0; v < VEC; ++v) cs[y][x * VEC + v] = acc[v];
   sq = block_sum(sq, red);  // contains the __syncthreads that publishes cs
   if (threadIdx.x == 0)
-    sq_part[(static_cast<size_t>(b) * gridDim.y + rc) * gridDim.x + blockIdx.x] = sq;
+    sq_part[blockIdx.x] = sq;
   for (int c = threadIdx.x; c < 32 * VEC; c += 256) {
-    const int col = blockIdx.x * 32 * VEC + c;
+    const int col = cc * 32 * VEC + c;
     if (col < n_out) {
       float t = 0.f;
 #pragma unroll
       for (int yy = 0; yy < 8; ++yy) t += cs[yy][c];
-      colsum_part[(static_cast<size_t>(b) * gridDim.y + rc) * n_out + col] = t;
+      colsum_part[(static_cast<size_t>(b) * row_chunks + rc) * n_out + col] = t;
     }
   }
 }
@@ -409,14 +414,14 @@ GstatsPlan gstats_plan(int B, int T, int n_out, int dt) {
 
 void gstats(const void* G, float* colsum_part, float* sq_part, int B, int T, int n_out, int dt,
             const GstatsPlan& pl, cudaStream_t s) {
-  dim3 grid(pl.col_chunks, pl.row_chunks, B);
+  const unsigned grid = static_cast<unsigned>(static_cast<size_t>(B) * pl.row_chunks * pl.col_chunks);
   const int vec_ok = (n_out % pl.vec == 0) && aligned16(G);
   if (dt == FDP_F32)
-    gstats_kernel<float, 4><<<grid, 256, 0, s>>>((const float*)G, colsum_part, sq_part, T, n_out, pl.rows_per_chunk, vec_ok);
+    gstats_kernel<float, 4><<<grid, 256, 0, s>>>((const float*)G, colsum_part, sq_part, T, n_out, pl.rows_per_chunk, vec_ok, pl.col_chunks, pl.row_chunks);
   else if (dt == FDP_BF16)
-    gstats_kernel<__nv_bfloat16, 8><<<grid, 256, 0, s>>>((const __nv_bfloat16*)G, colsum_part, sq_part, T, n_out, pl.rows_per_chunk, vec_ok);
+    gstats_kernel<__nv_bfloat16, 8><<<grid, 256, 0, s>>>((const __nv_bfloat16*)G, colsum_part, sq_part, T, n_out, pl.rows_per_chunk, vec_ok, pl.col_chunks, pl.row_chunks);
   else
-    gstats_kernel<__half, 8><<<grid, 256, 0, s>>>((const __half*)G, colsum_part, sq_part, T, n_out, pl.rows_per_chunk, vec_ok);
+    gstats_kernel<__half, 8><<<grid, 256, 0, s>>>((const __half*)G, colsum_part, sq_part, T, n_out, pl.rows_per_chunk, vec_ok, pl.col_chunks, pl.row_chunks);
   note_launch();
 }
 

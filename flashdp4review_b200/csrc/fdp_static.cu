@@ -65,7 +65,7 @@ extern "C" int fdp_bias_grad_static(const void* G, void* db, float* norms_out, f
                                     fdp_stream_t stream) {
   if (G == nullptr || db == nullptr || p == nullptr) return FDP_ERR_ARG;
   if (B <= 0 || T <= 0 || n_out <= 0) return FDP_ERR_ARG;
-  if (B > 65535) return FDP_ERR_SHAPE;  // B is a grid dimension
+  if (static_cast<long long>(B) * T >= (1ll << 31) / 2) return FDP_ERR_SHAPE;   // row indices are 32-bit
   if (!ok_dtype(in_dtype) || !ok_dtype(out_dtype)) return FDP_ERR_DTYPE;
   if (!(p->noise_std >= 0.f)) return FDP_ERR_ARG;
   if (p->noise_world > 1 && (p->noise_rank < 0 || p->noise_rank >= p->noise_world)) return FDP_ERR_ARG;

@@ -1,6 +1,6 @@
 """Generate the golden fixtures by running the REFERENCE's own pure-PyTorch per-sample path.
 
-Run where the reference checkout is available (it is not on a GPU box):
+Run where a checkout of the reference is available:
 
     python tests/golden/make_golden.py /path/to/FlashDP4Review
 

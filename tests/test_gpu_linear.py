@@ -258,6 +258,36 @@ def test_views_with_a_storage_offset(ops):
     assert rel_err(got.cpu().numpy(), want) < 1e-2
 
 
+def test_two_dimensional_inputs_with_more_than_65535_rows(ops):
+    """A 2-D layer input is `rows` samples of one row each (flashdp/layers/linear.py:51-53); the batch is
+    not a grid dimension of any kernel, so it may exceed 65535."""
+    B = 70001
+    gen = torch.Generator().manual_seed(8)
+    X = torch.randn(B, 1, 40, generator=gen)
+    G = torch.randn(B, 1, 24, generator=gen) * 0.05
+    G[::7] *= 30
+    dW, norms, _ = ops.dp_linear_weight_grad(X.to(dev()), G.to(dev()), 0.5, 1.0, return_norms=True)
+    want, wn = O.linear_weight_grad(G, X, 0.5, 1.0)
+    # the clipped sum runs over 70001 signed terms per element in fp32: its rounding alone reaches 1e-5
+    assert norm_err(norms.cpu().numpy(), wn) < 1e-5 and rel_err(dW.cpu().numpy(), want) < 3e-5
+    dWd, nd, _ = ops.dp_linear_weight_grad(X.to(dev()), G.to(dev()), 0.5, 1.0, return_norms=True, norm_algo="direct")
+    assert norm_err(nd.cpu().numpy(), wn) < 1e-5 and rel_err(dWd.cpu().numpy(), want) < 3e-5
+    db, nb, _ = ops.dp_bias_grad(G.to(dev()), 0.5, 1.0, return_norms=True)
+    wdb, wnb, _ = O.linear_bias_grad(G, 0.5, 1.0)
+    assert norm_err(nb.cpu().numpy(), wnb) < 1e-5 and rel_err(db.cpu().numpy(), wdb) < 1e-5
+    # LayerNorm with as many samples
+    d = 32
+    xl = torch.randn(B, d, generator=gen)
+    dy = torch.randn(B, d, generator=gen) * 0.1
+    y, buf, _ = ops.layernorm_fwd_fused(xl.to(dev()), torch.ones(d, device=dev()), torch.zeros(d, device=dev()), 1e-5)
+    _, dg, dbt = ops.dp_layernorm_backward(dy.to(dev()), xl.to(dev()), torch.ones(d, device=dev()), buf["mean"], buf["rstd"],
+                                           0.2, 1.0)
+    _, wmean, wrstd = O.layernorm_fwd(xl, np.ones(d), np.zeros(d), 1e-5)
+    xhat = (xl.double().numpy() - wmean[..., None]) * wrstd[..., None]
+    wdg, wdbt, _, _ = O.layernorm_affine_grads(dy.reshape(B, 1, d), xhat.reshape(B, 1, d), 0.2, 1.0)
+    assert rel_err(dg.cpu().numpy(), wdg) < 2e-5 and rel_err(dbt.cpu().numpy(), wdbt) < 2e-5
+
+
 def test_bounded_wait_that_runs_out_is_reported_and_sticky():
     """A one-warp kernel waits about a millisecond on a barrier nobody arrives on.  It must return
     normally, leave its code in the workspace word and in the device's host-visible word, make every
