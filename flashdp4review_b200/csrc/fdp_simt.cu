@@ -53,6 +53,126 @@ __device__ __forceinline__ void simt_tile(const Tin* __restrict__ A, long sAk, l
   }
 }
 
+// ---- fp32 fast path: 128 x 128 block tiles, 8 x 8 outputs per thread, double-buffered stages --------
+// For fp32 operands whose contraction runs over rows (the weight gradient and its per-sample norm):
+// A(k, m) = A[k * lda + m], B(k, n) = Bm[k * ldb + n], both row pitches multiples of four elements and
+// both bases 16-byte aligned, so a stage (16 rows x 128 columns of each operand) is fetched with
+// 16-byte loads; the next stage is prefetched into registers while the current one is multiplied.
+// A thread owns rows {4ty..4ty+3, 64+4ty..} and columns {4tx..4tx+3, 64+4tx..} of the tile: its
+// shared-memory reads are broadcasts (A) or conflict-free 16-byte reads (B), four per 64 FMAs.
+constexpr int FM = 128, FN = 128, FK = 16;
+
+template <bool SCALED>
+__device__ __forceinline__ void fast_tile(const float* __restrict__ A, int lda, const float* __restrict__ Bm, int ldb,
+                                          int K, int M, int N, int m0, int n0,
+                                          const float* __restrict__ factors, int T, float acc[8][8]) {
+  __shared__ __align__(16) float As[2][FK][FM];
+  __shared__ __align__(16) float Bs[2][FK][FN];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int lk = tid >> 5, lc = (tid & 31) * 4;       // this thread's rows lk, lk + 8 and columns lc..lc+3 of a stage
+  float4 ra[2], rb[2];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int k = k0 + lk + 8 * i;
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+      if (k < K) {
+        if (m0 + lc < M) a = __ldg(reinterpret_cast<const float4*>(A + static_cast<size_t>(k) * lda + m0 + lc));
+        if (n0 + lc < N) b = __ldg(reinterpret_cast<const float4*>(Bm + static_cast<size_t>(k) * ldb + n0 + lc));
+        if (SCALED) { const float f = factors[k / T]; a.x *= f; a.y *= f; a.z *= f; a.w *= f; }
+      }
+      ra[i] = a; rb[i] = b;
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      *reinterpret_cast<float4*>(&As[buf][lk + 8 * i][lc]) = ra[i];
+      *reinterpret_cast<float4*>(&Bs[buf][lk + 8 * i][lc]) = rb[i];
+    }
+  };
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  int buf = 0;
+  for (int k0 = 0; k0 < K; k0 += FK) {
+    const bool more = k0 + FK < K;
+    if (more) fetch(k0 + FK);
+#pragma unroll
+    for (int kk = 0; kk < FK; ++kk) {
+      const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][kk][ty * 4]);
+      const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][kk][64 + ty * 4]);
+      const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][kk][tx * 4]);
+      const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][kk][64 + tx * 4]);
+      const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    if (more) stash(buf ^ 1);     // the other buffer was last read before the previous barrier
+    __syncthreads();
+    buf ^= 1;
+  }
+}
+
+// fp32 operands that the fast path can take
+inline bool fast_ok(const void* G, const void* X, int n_in, int n_out, int dt) {
+  return dt == FDP_F32 && n_in % 4 == 0 && n_out % 4 == 0 && aligned16(G) && aligned16(X);
+}
+
+__global__ void __launch_bounds__(256) fast_norm_direct_kernel(const float* __restrict__ G, const float* __restrict__ X,
+                                                               float* __restrict__ partials, int T, int n_in,
+                                                               int n_out, int tiles_n, int tiles_m) {
+  __shared__ float red[32];
+  const int bx = blockIdx.x % tiles_n, by = (blockIdx.x / tiles_n) % tiles_m;
+  const int b = blockIdx.x / (tiles_n * tiles_m);
+  float acc[8][8] = {};
+  fast_tile<false>(G + static_cast<size_t>(b) * T * n_out, n_out, X + static_cast<size_t>(b) * T * n_in, n_in, T,
+                   n_out, n_in, by * FM, bx * FN, nullptr, 1, acc);
+  float s = 0.f;     // rows and columns outside the matrix were fetched as zeros
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s = fmaf(acc[i][j], acc[i][j], s);
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) partials[blockIdx.x] = s;
+}
+
+__global__ void __launch_bounds__(256) fast_clipped_wgrad_kernel(const float* __restrict__ G, const float* __restrict__ X,
+                                                                 const float* __restrict__ factors, void* __restrict__ dW,
+                                                                 int B, int T, int n_in, int n_out, int out_dt,
+                                                                 int layout, float inv_div, NoiseKey nk) {
+  float acc[8][8] = {};
+  const int m0 = blockIdx.y * FM, n0 = blockIdx.x * FN;
+  fast_tile<true>(G, n_out, X, n_in, B * T, n_out, n_in, m0, n0, factors, T, acc);
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+#pragma unroll
+  for (int ih = 0; ih < 2; ++ih)
+#pragma unroll
+    for (int jh = 0; jh < 2; ++jh) {
+      const int mb = m0 + 64 * ih + ty * 4, nb = n0 + 64 * jh + tx * 4;   // a 4 x 4 patch; M, N multiples of 4
+      if (mb >= n_out || nb >= n_in) continue;
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        // four elements adjacent in the output: along n for [out,in], along m for [in,out]
+        const bool oi = layout == FDP_OUT_IN;
+        const size_t idx0 = oi ? static_cast<size_t>(mb + q) * n_in + nb : static_cast<size_t>(nb + q) * n_out + mb;
+        float v[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v[e] = (oi ? acc[4 * ih + q][4 * jh + e] : acc[4 * ih + e][4 * jh + q]) * inv_div;
+        if (nk.std != 0.f) {      // idx0 is a multiple of 4
+          float z[4];
+          noise_group(nk, idx0 >> 2, z);
+          v[0] += z[0]; v[1] += z[1]; v[2] += z[2]; v[3] += z[3];
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) store_as(dW, out_dt, idx0 + e, v[e]);
+      }
+    }
+}
+
 // ---- per-sample norm, direct: one block = one 64x64 tile of G_b^T X_b, squared and summed -------
 template <typename Tin>
 __global__ void __launch_bounds__(256) simt_norm_direct_kernel(const Tin* __restrict__ G,
@@ -80,8 +200,15 @@ __global__ void __launch_bounds__(256) simt_norm_direct_kernel(const Tin* __rest
 
 int simt_norm_tiles(int n_in, int n_out) { return ceil_div(n_in, TN) * ceil_div(n_out, TM); }
 
-void simt_norm_direct(const void* G, const void* X, float* partials, int B, int T, int n_in,
-                      int n_out, int dt, cudaStream_t s) {
+int simt_norm_direct(const void* G, const void* X, float* partials, int B, int T, int n_in,
+                     int n_out, int dt, cudaStream_t s) {
+  if (fast_ok(G, X, n_in, n_out, dt)) {
+    const int tn = ceil_div(n_in, FN), tm = ceil_div(n_out, FM);
+    fast_norm_direct_kernel<<<static_cast<unsigned>(static_cast<size_t>(B) * tn * tm), 256, 0, s>>>(
+        (const float*)G, (const float*)X, partials, T, n_in, n_out, tn, tm);
+    note_launch();
+    return tn * tm;
+  }
   const int tn = ceil_div(n_in, TN), tm = ceil_div(n_out, TM);
   const unsigned grid = static_cast<unsigned>(static_cast<size_t>(B) * tn * tm);
   if (dt == FDP_F32)
@@ -91,6 +218,7 @@ void simt_norm_direct(const void* G, const void* X, float* partials, int B, int 
   else
     simt_norm_direct_kernel<__half><<<grid, 256, 0, s>>>((const __half*)G, (const __half*)X, partials, T, n_in, n_out, tn, tm);
   note_launch();
+  return tn * tm;
 }
 
 // ---- per-sample norm for short sequences (T < 64), through the T x T Gram matrices ---------------
@@ -244,6 +372,13 @@ __global__ void __launch_bounds__(256) simt_clipped_wgrad_kernel(
 void simt_clipped_wgrad(const void* G, const void* X, const float* factors, void* dW, int B, int T,
                         int n_in, int n_out, int dt, int out_dt, int layout, float inv_div,
                         NoiseKey nk, cudaStream_t s) {
+  if (fast_ok(G, X, n_in, n_out, dt) && (out_dt != FDP_F32 || aligned16(dW))) {
+    dim3 fgrid(ceil_div(n_in, FN), ceil_div(n_out, FM));
+    fast_clipped_wgrad_kernel<<<fgrid, 256, 0, s>>>((const float*)G, (const float*)X, factors, dW, B, T, n_in, n_out,
+                                                    out_dt, layout, inv_div, nk);
+    note_launch();
+    return;
+  }
   dim3 grid(ceil_div(n_in, TN), ceil_div(n_out, TM));
   if (dt == FDP_F32)
     simt_clipped_wgrad_kernel<float><<<grid, 256, 0, s>>>((const float*)G, (const float*)X, factors, dW, B, T, n_in, n_out, out_dt, layout, inv_div, nk);
