@@ -246,6 +246,22 @@ def linear_forward(input, weight, bias=None, w_layout="out_in", out_dtype=None):
     return Y
 
 
+def mm_fused(tensor1, tensor2):
+    """Drop-in for flashdp/core/linear_clip.py:64-91 (exported by flashdp.core, called by no layer):
+    tensor1 (..., K) @ tensor2 (K, ...) with fp32 accumulation, returned in the accumulation dtype
+    (fp32), leading / trailing axes kept."""
+    if tensor1.dtype not in _DT:
+        raise KeyError("The type of input mat is not supported.")
+    if tensor1.dim() < 2 or tensor2.dim() < 2:
+        raise KeyError("The dimensions of input tensors must be at least 2.")
+    if tensor1.shape[-1] != tensor2.shape[0]:
+        raise ValueError("tensor1 last dimension must match tensor2 first dimension")
+    a = tensor1.reshape(-1, tensor1.shape[-1])
+    b = tensor2.reshape(tensor2.shape[0], -1)
+    out = linear_forward(a, b, None, "in_out", out_dtype=torch.float32)
+    return out.reshape(tensor1.shape[:-1] + tensor2.shape[1:])
+
+
 # ------------------------------------------------------------------------------------------------
 # LayerNorm
 # ------------------------------------------------------------------------------------------------

@@ -235,7 +235,9 @@ int fdp_linear_wgrad(const void* G, const void* X, void* dW, float* norms_out, f
   const int div = p->batch_divisor > 0 ? p->batch_divisor : B;
   const float inv_div = 1.0f / static_cast<float>(div);
   const NoiseKey nk = make_noise_key(p, p->param_id);
-  FDP_CUDA_OK(cudaMemsetAsync(w.status, 0, sizeof(int), s));
+  // the status word: cleared by the first tensor-core launch of the call itself, or here when the call
+  // starts with a kernel that does not know it
+  if (!w.tc.ok || w.short_seq) FDP_CUDA_OK(cudaMemsetAsync(w.status, 0, sizeof(int), s));
 
   // the scaled epilogue of the clipped-sum GEMM reduces the norm partials itself: no clip-factor launch
   const bool fused_factors = w.tc.ok && w.tc.scaled_epilogue && tc_fused_factors_ok(B);
@@ -346,10 +348,10 @@ int fdp_linear_dgrad(const void* G, const void* W, void* dX, int rows, int n_in,
   if (workspace == nullptr || workspace_bytes < 256 || !aligned16(workspace)) return FDP_ERR_WORKSPACE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int* status = static_cast<int*>(workspace);
-  FDP_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), s));
   if (tc_dgrad_ok(rows, n_in, n_out, dtype) && aligned16(G) && aligned16(W) && aligned16(dX)) {
     if ((st = tc_dgrad(G, W, dX, status, rows, n_in, n_out, dtype, out_dtype, w_layout, s)) != FDP_OK) return st;
   } else {
+    FDP_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), s));
     simt_dgrad(G, W, dX, rows, n_in, n_out, dtype, out_dtype, w_layout, s);
   }
   FDP_LAUNCH_OK();
@@ -369,11 +371,11 @@ int fdp_linear_fwd(const void* X, const void* W, const void* bias, void* Y, int 
   if (workspace == nullptr || workspace_bytes < 256 || !aligned16(workspace)) return FDP_ERR_WORKSPACE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int* status = static_cast<int*>(workspace);
-  FDP_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), s));
   // same shape rules as the input gradient with the roles of n_in and n_out exchanged
   if (tc_dgrad_ok(rows, n_out, n_in, dtype) && aligned16(X) && aligned16(W) && aligned16(Y)) {
     if ((st = tc_fwd(X, W, bias, Y, status, rows, n_in, n_out, dtype, out_dtype, w_layout, s)) != FDP_OK) return st;
   } else {
+    FDP_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), s));
     simt_fwd(X, W, bias, Y, rows, n_in, n_out, dtype, out_dtype, w_layout, s);
   }
   FDP_LAUNCH_OK();

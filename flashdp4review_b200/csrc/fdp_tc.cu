@@ -55,6 +55,7 @@ struct TcArgs {
   float* partials;      // norm passes: one partial per (work unit, epilogue warp)
   int T;
   int* status;          // status word of the call (workspace)
+  int zero_status;      // this launch is the first of its call: its first thread clears the status word
   int* sticky;          // this device's slot of the host-visible status array, or null
   uint32_t idesc;
   // split-K (store epilogues): work units [0, units_full) are whole tiles; each later tile is cut into
@@ -295,6 +296,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   const int total_units = args.units_full + (total_tiles - args.units_full) * args.split;
 
   if (threadIdx.x == 0) {
+    // (a wait can only run out a second from now, so no report of this call can precede the clearing)
+    if (args.zero_status && blockIdx.x == 0 && args.status != nullptr) *args.status = 0;
     for (int s = 0; s < NST; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
     for (int a = 0; a < 2; ++a) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), EPI_WARPS * CTAS); }
     mbar_init(drain_bar, 1);
@@ -911,11 +914,15 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, co
   return cudaPeekAtLastError() == cudaSuccess ? FDP_OK : (cudaGetLastError(), FDP_ERR_LAUNCH);
 }
 
-// CTA pairs (cta_group::2) for the store-epilogue GEMMs unless FDP_TC_CTAS=1
-int ctas_per_tile() {
-  static const int v = [] { const char* e = getenv("FDP_TC_CTAS"); return (e && e[0] == '1') ? 1 : 2; }();
+// CTA pairs (cta_group::2) for the store-epilogue GEMMs; FDP_TC_CTAS=1 / 2 forces single CTAs / pairs
+int forced_ctas() {
+  static const int v = [] { const char* e = getenv("FDP_TC_CTAS"); return (e && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0; }();
   return v;
 }
+int ctas_per_tile() { return forced_ctas() == 1 ? 1 : 2; }
+// (Tried for the clipped-sum GEMM of small layers: single-CTA 128 x 256 tiles run whole, without K split,
+// parked accumulators or fix-up, whenever the pair tiles do not fill one wave of CTA pairs.  At the four
+// GPT-2-medium layer shapes that was 1-3 % slower than pairs with the K split, so pairs stay.)
 
 // K-split of the tail wave: `rem` tiles left after the full waves (all of them when there are fewer
 // tiles than workers) are cut into s parts of equal K-stage count, so that the last round keeps more
@@ -1044,6 +1051,7 @@ int tc_norms(const void* G, const void* X, float* partials, int* dev_status, int
   CUtensorMap a, b, a2, b2;
   TcArgs args{};
   args.batch = B; args.batch_rows = T; args.partials = partials; args.status = dev_status; args.T = T;
+  args.zero_status = 1;      // the norm pass is the first launch of a weight-gradient call
   args.terms = terms;
   if (pl.algo == FDP_NORM_DIRECT) {
     if (!make_map(&a, G, rows, wo, 64, BK, dt) || !make_map(&b, X, rows, wi, 64, BK, dt)) return FDP_ERR_LAUNCH;
@@ -1101,6 +1109,9 @@ int tc_clipped_wgrad(const void* Gs, const void* X, const TcFactorSource* fs, fl
   args.term_stages = T / BK;      // used when terms == 3: every sample's rows are visited three times
   args.k_stages = terms * static_cast<int>((rows + BK - 1) / BK);
   args.out = dW; args.out_dt = out_dt; args.scale = inv_div; args.nk = nk;
+  // [out,in]: A = G (M = n_out), B = X (N = n_in); [in,out]: operands swap roles, no transpose pass
+  const bool oi = (layout == FDP_OUT_IN);
+  args.M = oi ? n_out : n_in; args.N = oi ? n_in : n_out; args.ld_out = args.N;
   const int ctas = ctas_per_tile();
   args.idesc = make_idesc(dt, true, true, ctas);
   if (scaled) {
@@ -1113,9 +1124,6 @@ int tc_clipped_wgrad(const void* Gs, const void* X, const TcFactorSource* fs, fl
       args.norms_out = fs->norms_out; args.factors_out = fs->factors_out;
     }
   }
-  // [out,in]: A = G (M = n_out), B = X (N = n_in); [in,out]: operands swap roles, no transpose pass
-  const bool oi = (layout == FDP_OUT_IN);
-  args.M = oi ? n_out : n_in; args.N = oi ? n_in : n_out; args.ld_out = args.N;
   args.plane_a = args.M; args.plane_b = args.N;
   args.tiles_m = ceil_div(args.M, BM * ctas); args.tiles_n = ceil_div(args.N, BN);
   args.tiles_per_batch = args.tiles_m * args.tiles_n;
@@ -1158,7 +1166,7 @@ int tc_dgrad(const void* G, const void* W, void* dX, int* dev_status, int rows, 
   const int ctas = ctas_per_tile();
   if (!make_map(&mg, G, rows, n_out, BK, BM, dt)) return FDP_ERR_LAUNCH;
   TcArgs args{};
-  args.batch = 1; args.batch_rows = 0; args.status = dev_status;
+  args.batch = 1; args.batch_rows = 0; args.status = dev_status; args.zero_status = 1;
   args.M = rows; args.N = n_in; args.ld_out = n_in;
   args.tiles_m = ceil_div(rows, BM * ctas); args.tiles_n = ceil_div(n_in, BN);
   args.tiles_per_batch = args.tiles_m * args.tiles_n;
@@ -1188,7 +1196,7 @@ int tc_fwd(const void* X, const void* W, const void* bias, void* Y, int* dev_sta
   const int ctas = ctas_per_tile();
   if (!make_map(&mx, X, rows, n_in, BK, BM, dt)) return FDP_ERR_LAUNCH;
   TcArgs args{};
-  args.batch = 1; args.batch_rows = 0; args.status = dev_status;
+  args.batch = 1; args.batch_rows = 0; args.status = dev_status; args.zero_status = 1;
   args.M = rows; args.N = n_out; args.ld_out = n_out;
   args.tiles_m = ceil_div(rows, BM * ctas); args.tiles_n = ceil_div(n_out, BN);
   args.tiles_per_batch = args.tiles_m * args.tiles_n;

@@ -288,6 +288,25 @@ def test_two_dimensional_inputs_with_more_than_65535_rows(ops):
     assert rel_err(dg.cpu().numpy(), wdg) < 2e-5 and rel_err(dbt.cpu().numpy(), wdbt) < 2e-5
 
 
+def test_core_exports_match_the_reference_and_mm_fused(ops):
+    """Every name flashdp.core exports (flashdp/core/__init__.py:1-11) exists here; mm_fused is the plain
+    product with fp32 accumulation and output (flashdp/core/linear_clip.py:64-91)."""
+    from flashdp4review_b200 import core
+    for name in ("mm_clip", "bmm_clip", "bmtm_clip", "mm_fused", "linear_weight_flashdp", "linear_bias_grad_clip",
+                 "layernorm_dw_clip", "layernorm_db_clip", "layernorm_fwd_fused", "layernorm_bwd_clip_fused",
+                 "layernorm_dwdb_fused"):
+        assert callable(getattr(core, name)), name
+    gen = torch.Generator().manual_seed(2)
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 1e-2)):
+        A = torch.randn(3, 50, 136, generator=gen).to(dtype)
+        Bm = (torch.randn(136, 264, generator=gen) * 0.1).to(dtype)
+        out = core.mm_fused(A.to(dev()), Bm.to(dev()))
+        assert out.dtype == torch.float32 and out.shape == (3, 50, 264)
+        assert rel_err(out.cpu().numpy(), A.double().numpy() @ Bm.double().numpy()) < tol
+    with pytest.raises(ValueError):
+        core.mm_fused(torch.zeros(4, 5, device=dev()), torch.zeros(6, 3, device=dev()))
+
+
 def test_bounded_wait_that_runs_out_is_reported_and_sticky():
     """A one-warp kernel waits about a millisecond on a barrier nobody arrives on.  It must return
     normally, leave its code in the workspace word and in the device's host-visible word, make every
