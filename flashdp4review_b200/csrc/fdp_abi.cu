@@ -3,6 +3,8 @@
 #include <atomic>
 #include <mutex>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "fdp_kernels.h"
 
 using namespace fdp;
@@ -40,6 +42,13 @@ int* sticky_status_slot() {
 }  // namespace fdp
 
 namespace {
+
+// An NVTX range around every compute entry point, so that a timeline tool shows which library call
+// a kernel belongs to.  Header-only NVTX: a no-op unless a tool has injected itself into the process.
+struct NvtxRange {
+  explicit NvtxRange(const char* name) { nvtxRangePushA(name); }
+  ~NvtxRange() { nvtxRangePop(); }
+};
 
 bool valid_dtype(int dt) { return dt == FDP_F32 || dt == FDP_BF16 || dt == FDP_F16; }
 
@@ -214,6 +223,7 @@ int fdp_linear_wgrad(const void* G, const void* X, void* dW, float* norms_out, f
                      int B, int T, int n_in, int n_out, int in_dtype, int out_dtype, int layout,
                      int norm_algo, const fdp_dp_params* p, void* workspace, size_t workspace_bytes,
                      fdp_stream_t stream) {
+  NvtxRange nvtx_range("fdp_linear_wgrad");
   if (G == nullptr || X == nullptr || dW == nullptr) return FDP_ERR_ARG;
   if (B <= 0 || T <= 0 || n_in <= 0 || n_out <= 0) return FDP_ERR_ARG;
   if (layout != FDP_OUT_IN && layout != FDP_IN_OUT) return FDP_ERR_ARG;
@@ -304,6 +314,7 @@ size_t fdp_bias_grad_workspace_bytes(int B, int T, int n_out, int in_dtype) {
 int fdp_bias_grad(const void* G, void* db, float* norms_out, float* factors_out, int B, int T,
                   int n_out, int in_dtype, int out_dtype, const fdp_dp_params* p, void* workspace,
                   size_t workspace_bytes, fdp_stream_t stream) {
+  NvtxRange nvtx_range("fdp_bias_grad");
   if (G == nullptr || db == nullptr) return FDP_ERR_ARG;
   if (B <= 0 || T <= 0 || n_out <= 0) return FDP_ERR_ARG;
   if (static_cast<long long>(B) * T >= (1ll << 31) / 2) return FDP_ERR_SHAPE;   // row indices are 32-bit
@@ -339,6 +350,7 @@ size_t fdp_linear_dgrad_workspace_bytes(int rows, int n_in, int n_out, int dtype
 int fdp_linear_dgrad(const void* G, const void* W, void* dX, int rows, int n_in, int n_out,
                      int dtype, int out_dtype, int w_layout, void* workspace, size_t workspace_bytes,
                      fdp_stream_t stream) {
+  NvtxRange nvtx_range("fdp_linear_dgrad");
   if (G == nullptr || W == nullptr || dX == nullptr) return FDP_ERR_ARG;
   if (rows <= 0 || n_in <= 0 || n_out <= 0) return FDP_ERR_ARG;
   if (w_layout != FDP_OUT_IN && w_layout != FDP_IN_OUT) return FDP_ERR_ARG;
@@ -362,6 +374,7 @@ int fdp_linear_dgrad(const void* G, const void* W, void* dX, int rows, int n_in,
 int fdp_linear_fwd(const void* X, const void* W, const void* bias, void* Y, int rows, int n_in, int n_out,
                    int dtype, int out_dtype, int w_layout, void* workspace, size_t workspace_bytes,
                    fdp_stream_t stream) {
+  NvtxRange nvtx_range("fdp_linear_fwd");
   if (X == nullptr || W == nullptr || Y == nullptr) return FDP_ERR_ARG;
   if (rows <= 0 || n_in <= 0 || n_out <= 0) return FDP_ERR_ARG;
   if (w_layout != FDP_OUT_IN && w_layout != FDP_IN_OUT) return FDP_ERR_ARG;
@@ -386,6 +399,7 @@ int fdp_linear_fwd(const void* X, const void* W, const void* bias, void* Y, int 
 int fdp_layernorm_fwd(const void* x, const void* gamma, const void* beta, void* y, float* mean,
                       float* rstd, int rows, int d, float eps, int dtype, int param_dtype,
                       fdp_stream_t stream) {
+  NvtxRange nvtx_range("fdp_layernorm_fwd");
   if (x == nullptr || gamma == nullptr || beta == nullptr || y == nullptr || mean == nullptr || rstd == nullptr)
     return FDP_ERR_ARG;
   if (rows <= 0 || d <= 0) return FDP_ERR_ARG;
@@ -414,6 +428,7 @@ int fdp_layernorm_bwd(const void* dy, const void* x, const void* gamma, const fl
                       float* norms_beta, int B, int T, int d, int dtype, int param_dtype,
                       const fdp_dp_params* p, void* workspace, size_t workspace_bytes,
                       fdp_stream_t stream) {
+  NvtxRange nvtx_range("fdp_layernorm_bwd");
   if (dy == nullptr || x == nullptr || gamma == nullptr || mean == nullptr || rstd == nullptr || dgamma == nullptr)
     return FDP_ERR_ARG;
   if (B <= 0 || T <= 0 || d <= 0) return FDP_ERR_ARG;
@@ -455,6 +470,7 @@ int fdp_layernorm_saturate_groups(int rows, int d) { return (rows <= 0 || d <= 0
 int fdp_layernorm_bwd_saturate(const void* dy, const void* x, const float* mean, const float* rstd, void* dgamma,
                                void* dbeta, int rows, int d, int dtype, int param_dtype, float C, float clamp_value,
                                void* workspace, size_t workspace_bytes, fdp_stream_t stream) {
+  NvtxRange nvtx_range("fdp_layernorm_bwd_saturate");
   if (dy == nullptr || x == nullptr || mean == nullptr || rstd == nullptr || dgamma == nullptr) return FDP_ERR_ARG;
   if (rows <= 0 || d <= 0) return FDP_ERR_ARG;
   if (!valid_dtype(dtype) || !valid_dtype(param_dtype)) return FDP_ERR_DTYPE;

@@ -118,6 +118,9 @@ int fdp_selftest_wait_timeout(long long limit_cycles, void* workspace, size_t wo
  * reference (single GPU, example/gpt2/train.py:33). */
 int fdp_set_sm_reserve(int n);
 
+/* Every compute entry point below opens an NVTX range named after itself (header-only NVTX: nothing
+ * happens unless a timeline tool is attached), so a trace shows which call each kernel belongs to. */
+
 /* ---- instrumentation (no counterpart in the reference, which only wall-clocks whole functions in
  * RuntimeAutoTuner._measure_time, flashdp/core/utils.py:42-47) ---------------------------------------
  * fdp_launch_count: kernels launched by this library in this process so far.
