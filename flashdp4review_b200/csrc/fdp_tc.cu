@@ -8,8 +8,8 @@
 //   gram    K,  K,  GRAM, 1           sum_{t,s} (G_b G_b^T)_{ts} (X_b X_b^T)_{ts}, two accumulators in TMEM
 //   dgrad   K,  MN or K, STORE, 2     dX = G W
 //   forward K,  K or MN, STORE, 2     Y = X W^T + bias
-// Roles in a CTA: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2-5 (2-9 for
-// STORE_SCALED) = epilogue, each on the TMEM lane quarter warp % 4.  With two CTAs per tile the
+// Roles in a CTA: warp 0 = TMA producer, warp 1 = MMA issuer and TMEM owner, warps 2-5 (2-9 for the
+// store epilogues) = epilogue, each on the TMEM lane quarter warp % 4.  With two CTAs per tile the
 // even CTA of a 2-CTA cluster issues tcgen05.mma.cta_group::2 for both.  Every mbarrier wait is
 // bounded: when one runs out the CTA records a code in the status word, drains and leaves.
 // No TMA load here uses cluster multicast.
@@ -40,7 +40,12 @@ constexpr int MAX_SMS = 148;           // workers the split-K parking area is si
 // EPI_STORE_SCALED: the accumulator of each sample (K segment) is drained on its own and added, times
 // that sample's clip factor, to fp32 registers of eight epilogue warps; G needs no scaled copy.
 enum { EPI_STORE = 0, EPI_SUMSQ = 1, EPI_GRAM = 2, EPI_STORE_SCALED = 3 };
-constexpr int threads_for(int epi) { return epi == EPI_STORE_SCALED ? 320 : 192; }
+// eight epilogue warps (two per TMEM lane quarter, 128 columns each) for the store epilogues, four for the norms
+#ifndef FDP_EPI_STORE_WARPS
+#define FDP_EPI_STORE_WARPS 8
+#endif
+__host__ __device__ constexpr int epi_warps_for(int epi) { return epi == EPI_STORE_SCALED ? 8 : (epi == EPI_STORE ? FDP_EPI_STORE_WARPS : 4); }
+constexpr int threads_for(int epi) { return 64 + 32 * epi_warps_for(epi); }
 constexpr int smem_for(int epi) { return epi == EPI_STORE_SCALED ? SMEM_BYTES_SCALED : SMEM_BYTES; }
 
 struct TcArgs {
@@ -268,7 +273,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   constexpr int B_BYTES = B_STAGE_BYTES / CTAS;          // this CTA's share of the B stage
   constexpr int STG = A_STAGE_BYTES + B_BYTES;
   constexpr int BN_CTA = BN / CTAS;                      // B columns (rows if K-major) loaded by this CTA
-  constexpr int EPI_WARPS = (EPI == EPI_STORE_SCALED) ? 8 : 4;
+  constexpr int EPI_WARPS = epi_warps_for(EPI);
   static_assert(NST * STG <= STAGES * STAGE_BYTES, "ring size");
   static_assert(CTAS == 1 || EPI == EPI_STORE || EPI == EPI_STORE_SCALED, "pairs: store epilogues only");
   const uint32_t cta_rank = (CTAS == 2) ? cluster_ctarank() : 0u;
@@ -635,11 +640,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
       tc_fence_after();
       const uint32_t tbase = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + (EPI == EPI_GRAM ? 0 : acc * BN);
       float part = 0.f;
+      constexpr int C_SPAN = BN * 4 / EPI_WARPS;     // store epilogue: this warp's share of the tile's columns
+      const int c_begin = (ew >> 2) * C_SPAN;
       if (EPI == EPI_STORE && slot >= 0) {
         // K-split unit: park the raw accumulator for the fix-up kernel
         float4* dst = reinterpret_cast<float4*>(args.split_ws + ((static_cast<size_t>(slot) * CTAS + cta_rank) * BM + row) * BN);
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = c_begin; c < c_begin + C_SPAN; c += 32) {
           uint32_t r[32];
           tc_ld32(tbase + c, r);
           tc_wait_ld();
@@ -650,7 +657,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         }
       } else if (EPI == EPI_STORE) {
 #pragma unroll 1
-        for (int c = 0; c < BN; c += 32) {
+        for (int c = c_begin; c < c_begin + C_SPAN; c += 32) {
           uint32_t r[32];
           tc_ld32(tbase + c, r);
           tc_wait_ld();
