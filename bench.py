@@ -36,6 +36,7 @@ WORKLOADS = {
     "linear_bf16_b32_t1024_4096x4096": (32, 1024, 4096, 4096, "bf16", 1e-3),
     "conv1d_bf16_b16_t1024_1024x3072": (16, 1024, 1024, 3072, "bf16", 1e-3),
     "linear_bf16_b8_t1024_1024x3072": (8, 1024, 1024, 3072, "bf16", 1e-3),     # a GPT-2-medium c_attn call
+    "linear_bf16_b4_t2048_4096x4096": (4, 2048, 4096, 4096, "bf16", 1e-3),     # a Llama-2-7B attention projection
     "linear_fp32_b4_t128_768x768": (4, 128, 768, 768, "f32", 1e-2),
     "small_bf16_b4_t256_512x512": (4, 256, 512, 512, "bf16", 1e-3),
 }

@@ -23,3 +23,23 @@ def test_wgrad_fuzz(B, T, n_in, n_out, dtype, layout, C, clamp):
     if B > 1:
         G[0] *= 25.0
     check_wgrad(X, G, C, clamp, dtype, layout=layout)
+
+
+@settings(max_examples=20, deadline=None, suppress_health_check=list(HealthCheck), derandomize=True)
+@given(B=st.integers(1, 5), T=st.sampled_from([64, 128, 192, 256, 320, 512]), n_in=st.sampled_from([64, 128, 192, 256, 320, 576]),
+       n_out=st.sampled_from([128, 192, 256, 384, 640]), layout=st.sampled_from(["out_in", "in_out"]),
+       algo=st.sampled_from(["auto", "gram", "direct"]), C=st.sampled_from([1e-3, 0.05, 1e6]))
+def test_fp32_tensor_mode_fuzz(B, T, n_in, n_out, layout, algo, C):
+    """fp32 inputs with `fp32_tensor=True`: shapes on both sides of what the three-product tensor-core
+    path takes (64-aligned features of at least 128, T a multiple of 64 and at least 128); the others
+    fall back to the exact kernels.  Tolerance 1e-4 either way."""
+    from flashdp4review_b200.core import ops
+    from conftest import rel_err, norm_err
+    from gpu_util import dev
+    X, G, _ = O.make_linear_inputs(B, T, n_in, n_out, 2e-2, seed=B + T + n_in + n_out)
+    if B > 1:
+        G[0] *= 25.0
+    dW, norms, _ = ops.dp_linear_weight_grad(X.to(dev()), G.to(dev()), C, 1.0, layout=layout, norm_algo=algo,
+                                             return_norms=True, fp32_tensor=True)
+    want, wn = O.linear_weight_grad(G, X, C, 1.0, layout=layout)
+    assert norm_err(norms.cpu().numpy(), wn) < 1e-4 and rel_err(dW.cpu().numpy(), want) < 1e-4
