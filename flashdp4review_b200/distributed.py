@@ -175,9 +175,9 @@ class DPGradReducer:
                 sc = self._scale(p, self.world)
                 parts.append((p.grad if sc == 1.0 else p.grad * sc).reshape(-1))
             flat = torch.cat(parts)
-        if not self._inflight and self.world > 1 and flat.is_cuda:
+        if not self._inflight and self.world > 1 and flat.is_cuda and runtime.reserve_sms() > 0:
             # from the first collective of this step until finish(): the library's GEMM grids leave a
-            # few SMs free so the all-reduce kernels run beside them instead of behind them
+            # few SMs free for the all-reduce kernels (off unless FDP_DP_RESERVE_SMS asks for it)
             self._reserve_prev = self._set_reserve(runtime.reserve_sms())
         work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
         self._inflight[i] = (work, flat, bucket)
