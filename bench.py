@@ -16,6 +16,7 @@ cores instead (rank 0 only), a step being the whole batch of the workload.
 `--workload llama7b_shaped` runs a Llama-2-7B-shaped decoder with every Linear but lm_head wrapped.
 """
 import argparse
+import contextlib
 import ctypes
 import datetime
 import json
@@ -614,8 +615,9 @@ def gpt2_measure(args, steps, with_no_dp=False, no_dp=False):
         torch.manual_seed(0)
         model = GPT2LMHeadModel(cfg).to(dev)
         if dp:
-            fdp.wrap_with_flashdp_layers(model, target_modules=[Conv1D, torch.nn.Linear, torch.nn.LayerNorm],
-                                         skip_layers=["lm_head"], C=1.0, noise_multiplier=1.0, feedback=False)
+            with contextlib.redirect_stdout(sys.stderr):     # stdout carries the JSON line only
+                fdp.wrap_with_flashdp_layers(model, target_modules=[Conv1D, torch.nn.Linear, torch.nn.LayerNorm],
+                                             skip_layers=["lm_head"], C=1.0, noise_multiplier=1.0, feedback=False)
         # fused=True: one multi-tensor kernel; the default would fall back to ~300 per-parameter kernel chains
         # because DPParameter is a Parameter subclass (torch's foreach/fused auto-selection wants exact types)
         opt = torch.optim.Adam(model.parameters(), lr=1e-4, fused=True)
@@ -792,8 +794,9 @@ def run_llama(args):
     model = build_llama(layers=args.llama_layers, dtype=torch.bfloat16, device=dev)
     n_params = sum(p.numel() for p in model.parameters())
     if not args.no_dp:
-        fdp.wrap_with_flashdp_layers(model, target_modules=[torch.nn.Linear], skip_layers=["lm_head"], C=1.0,
-                                     noise_multiplier=1.0, feedback=False)
+        with contextlib.redirect_stdout(sys.stderr):         # stdout carries the JSON line only
+            fdp.wrap_with_flashdp_layers(model, target_modules=[torch.nn.Linear], skip_layers=["lm_head"], C=1.0,
+                                         noise_multiplier=1.0, feedback=False)
     n_dp = sum(p.numel() for p in model.parameters() if getattr(p, "requires_dp", False))
     opt = torch.optim.Adam(model.parameters(), lr=1e-4, fused=True)
     reducer = DPGradReducer(model, grad_as_bucket_view=True, bucket_bytes=256 << 20) if world > 1 else None
