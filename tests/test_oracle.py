@@ -125,3 +125,32 @@ def test_noise_stream_statistics(golden):
     assert np.array_equal(z[:64], O.gaussian_noise(64, 0.5, 7, 3, 11))
     g = golden("noise_stats.npz")   # the reference's own noise: std = noise_multiplier/sqrt(B)
     assert abs(float(g["resid_std"]) / float(g["expected_std"]) - 1) < 0.03
+
+
+def test_fused_saturation_restatement_against_a_row_by_row_loop():
+    """The vectorised restatement of the reference's fused LayerNorm accumulation
+    (flashdp/core/layernorm_clip.py:104-131 with a fixed row order) against the same recurrence written
+    row by row, as the Triton program of one row would apply it."""
+    import numpy as np
+    from oracle import dp_oracle as O
+    rng = np.random.default_rng(0)
+    rows, d, C, clamp = 600, 8, 0.05, 1.0
+    dy = rng.normal(size=(rows, d)).astype(np.float32) * 0.2
+    xh = rng.normal(size=(rows, d)).astype(np.float32)
+    G = O.layernorm_saturate_groups(rows, d)
+    assert G == 256
+    bw = np.zeros((G, d), np.float32)
+    bb = np.zeros((G, d), np.float32)
+    seen = np.zeros(G, bool)
+    f = lambda b: np.minimum(np.float32(C) / (np.abs(b) + np.float32(1e-10)), np.float32(clamp))
+    for r in range(rows):
+        g = r % G
+        pw, pb = dy[r] * xh[r], dy[r]
+        if seen[g]:
+            pw = pw + bw[g] * f(bw[g])
+            pb = pb + bb[g] * f(bb[g])
+        bw[g], bb[g], seen[g] = pw, pb, True
+    dg, db, dw_, db_ = O.layernorm_fused_saturation(dy, xh, C, clamp)
+    assert np.allclose(dw_, bw, rtol=1e-6, atol=1e-8) and np.allclose(db_, bb, rtol=1e-6, atol=1e-8)
+    assert np.allclose(dg, bw.sum(0), rtol=1e-5, atol=1e-5) and np.allclose(db, bb.sum(0), rtol=1e-5, atol=1e-5)   # fp32 sums of 256 signed terms, two orders
+    assert O.layernorm_saturate_groups(40, 2048) == 40 and O.layernorm_saturate_groups(10 ** 6, 8192) == 96
