@@ -268,7 +268,7 @@ int fdp_linear_wgrad(const void* G, const void* X, void* dW, float* norms_out, f
   } else if (w.tc.ok) {
     if ((st = tc_norms(Gt, Xt, w.partials, w.status, B, T, n_in, n_out, tdt, w.tc, s)) != FDP_OK) return st;
   } else {
-    w.nparts = simt_norm_direct(G, X, w.partials, B, T, n_in, n_out, in_dtype, s);
+    w.nparts = simt_norm_direct(G, X, w.partials, B, T, n_in, n_out, in_dtype, norm_algo & FDP_NORM_MASK, s);
   }
   prof_mark(1, s);
   if (!fused_factors)

@@ -16,10 +16,11 @@ int sm_reserve_exchange(int n);
 
 // ---- generic-shape kernels (any dtype, any size; fp32 FMA accumulation) -----------------------
 int simt_norm_tiles(int n_in, int n_out);
-// partials[b*ntiles + tile] = sum of squares of one tile of G_b^T X_b; returns ntiles, which is at
-// most simt_norm_tiles (64 x 64 tiles; aligned fp32 operands take 128 x 128 tiles)
+// partials[b*nparts + part] add up to ||G_b^T X_b||_F^2; returns nparts, which is at most simt_norm_tiles
+// (64 x 64 tiles of the product; aligned fp32 operands take 128 x 128 tiles, or, when cheaper or asked for
+// by norm_algo, 128 x 128 blocks of the T x T Gram form)
 int simt_norm_direct(const void* G, const void* X, float* partials, int B, int T, int n_in,
-                      int n_out, int dt, cudaStream_t s);
+                     int n_out, int dt, int norm_algo, cudaStream_t s);
 // short sequences (T < SHORT_SEQ): sumsq[b] = ||G_b^T X_b||_F^2 through the T x T Gram matrices
 constexpr int SHORT_SEQ = 64;
 void simt_norm_gram_small(const void* G, const void* X, float* sumsq, int B, int T, int n_in, int n_out,

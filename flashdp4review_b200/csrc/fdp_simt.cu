@@ -173,6 +173,92 @@ __global__ void __launch_bounds__(256) fast_clipped_wgrad_kernel(const float* __
     }
 }
 
+// ---- fp32 fast path, Gram form of the per-sample norm ----------------------------------------------
+// ||G_b^T X_b||_F^2 = sum_{t,s} (G_b G_b^T)[t,s] (X_b X_b^T)[t,s] on 128 x 128 blocks of the T x T
+// plane, blocks j >= i only (off-diagonal ones count twice): 128^2 (in + out) FMAs per block instead of
+// T in out per sample for the direct form.  Here both operands of a product are row blocks of the same
+// matrix and the contraction runs along the rows' contiguous columns, so a stage is fetched with
+// 16-byte loads along K and written to shared memory transposed (K-major rows of 128 + 4 floats).
+constexpr int GK_PITCH = FM + 4;
+
+// acc[i][j] += sum_k M[row_a + r_i][k] * M[row_b + r_j][k]; rows at or beyond `row_end` read as zero
+__device__ __forceinline__ void gram_fast_tile(const float* __restrict__ Mx, int ld, int K, int row_a, int row_b,
+                                               int row_end, float (*As)[GK_PITCH], float (*Bs)[GK_PITCH],
+                                               float acc[8][8]) {
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  float4 ra[2], rb[2];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int idx = tid + 256 * i, r = idx >> 2, k = k0 + 4 * (idx & 3);
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f), b = a;
+      if (k < K) {
+        if (row_a + r < row_end) a = __ldg(reinterpret_cast<const float4*>(Mx + static_cast<size_t>(row_a + r) * ld + k));
+        if (row_b + r < row_end) b = __ldg(reinterpret_cast<const float4*>(Mx + static_cast<size_t>(row_b + r) * ld + k));
+      }
+      ra[i] = a; rb[i] = b;
+    }
+  };
+  auto stash = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int idx = tid + 256 * i, r = idx >> 2, kk = 4 * (idx & 3);
+      float (*A)[GK_PITCH] = As + buf * FK;
+      float (*Bq)[GK_PITCH] = Bs + buf * FK;
+      A[kk][r] = ra[i].x; A[kk + 1][r] = ra[i].y; A[kk + 2][r] = ra[i].z; A[kk + 3][r] = ra[i].w;
+      Bq[kk][r] = rb[i].x; Bq[kk + 1][r] = rb[i].y; Bq[kk + 2][r] = rb[i].z; Bq[kk + 3][r] = rb[i].w;
+    }
+  };
+  __syncthreads();              // the buffers may still be read by the previous call
+  fetch(0);
+  stash(0);
+  __syncthreads();
+  int buf = 0;
+  for (int k0 = 0; k0 < K; k0 += FK) {
+    const bool more = k0 + FK < K;
+    if (more) fetch(k0 + FK);
+#pragma unroll
+    for (int kk = 0; kk < FK; ++kk) {
+      const float* ar = As[buf * FK + kk];
+      const float* br = Bs[buf * FK + kk];
+      const float4 a0 = *reinterpret_cast<const float4*>(ar + ty * 4), a1 = *reinterpret_cast<const float4*>(ar + 64 + ty * 4);
+      const float4 b0 = *reinterpret_cast<const float4*>(br + tx * 4), b1 = *reinterpret_cast<const float4*>(br + 64 + tx * 4);
+      const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+      const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+    if (more) stash(buf ^ 1);
+    __syncthreads();
+    buf ^= 1;
+  }
+}
+
+__global__ void __launch_bounds__(256) fast_norm_gram_kernel(const float* __restrict__ G, const float* __restrict__ X,
+                                                             float* __restrict__ partials, int T, int n_in, int n_out,
+                                                             int nb, int nblk) {
+  __shared__ __align__(16) float As[2 * FK][GK_PITCH];
+  __shared__ __align__(16) float Bs[2 * FK][GK_PITCH];
+  __shared__ float red[32];
+  const int b = blockIdx.x / nblk;
+  int q = blockIdx.x - b * nblk, i = 0;
+  while (q >= nb - i) { q -= nb - i; ++i; }      // block (i, j = i + q) of the upper triangle
+  const int j = i + q;
+  const int row0 = b * T;
+  float p[8][8] = {}, x[8][8] = {};
+  gram_fast_tile(G, n_out, n_out, row0 + i * FM, row0 + j * FM, row0 + T, As, Bs, p);
+  gram_fast_tile(X, n_in, n_in, row0 + i * FM, row0 + j * FM, row0 + T, As, Bs, x);
+  float s = 0.f;       // rows past the sample's end were fetched as zeros
+#pragma unroll
+  for (int a = 0; a < 8; ++a)
+#pragma unroll
+    for (int c = 0; c < 8; ++c) s = fmaf(p[a][c], x[a][c], s);
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) partials[blockIdx.x] = (i == j) ? s : 2.f * s;
+}
+
 // ---- per-sample norm, direct: one block = one 64x64 tile of G_b^T X_b, squared and summed -------
 template <typename Tin>
 __global__ void __launch_bounds__(256) simt_norm_direct_kernel(const Tin* __restrict__ G,
@@ -201,8 +287,20 @@ __global__ void __launch_bounds__(256) simt_norm_direct_kernel(const Tin* __rest
 int simt_norm_tiles(int n_in, int n_out) { return ceil_div(n_in, TN) * ceil_div(n_out, TM); }
 
 int simt_norm_direct(const void* G, const void* X, float* partials, int B, int T, int n_in,
-                     int n_out, int dt, cudaStream_t s) {
+                     int n_out, int dt, int norm_algo, cudaStream_t s) {
   if (fast_ok(G, X, n_in, n_out, dt)) {
+    // Gram form when it is the cheaper one (long sequences) and its partials fit the workspace, which
+    // is sized for the 64 x 64 tiles of the direct form
+    const int nb = ceil_div(T, FM), nblk = nb * (nb + 1) / 2;
+    const double gram_cost = static_cast<double>(nblk) * FM * FM * (static_cast<double>(n_in) + n_out);
+    const double direct_cost = static_cast<double>(T) * n_in * n_out;
+    const bool want_gram = norm_algo == FDP_NORM_GRAM || (norm_algo == FDP_NORM_AUTO && gram_cost < 0.8 * direct_cost);
+    if (want_gram && nblk <= simt_norm_tiles(n_in, n_out)) {
+      fast_norm_gram_kernel<<<static_cast<unsigned>(static_cast<size_t>(B) * nblk), 256, 0, s>>>(
+          (const float*)G, (const float*)X, partials, T, n_in, n_out, nb, nblk);
+      note_launch();
+      return nblk;
+    }
     const int tn = ceil_div(n_in, FN), tm = ceil_div(n_out, FM);
     fast_norm_direct_kernel<<<static_cast<unsigned>(static_cast<size_t>(B) * tn * tm), 256, 0, s>>>(
         (const float*)G, (const float*)X, partials, T, n_in, n_out, tn, tm);

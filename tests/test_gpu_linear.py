@@ -258,6 +258,21 @@ def test_views_with_a_storage_offset(ops):
     assert rel_err(got.cpu().numpy(), want) < 1e-2
 
 
+@pytest.mark.parametrize("shape", [(3, 256, 768, 768), (2, 200, 520, 264), (2, 512, 256, 192), (1, 130, 1024, 512)])
+def test_fp32_exact_norm_algorithms_agree(shape):
+    """fp32 inputs on the exact (fp32 FMA) kernels: the product form and the Gram form of the per-sample
+    norm, and the automatic choice between them, all hold the fp32 tolerance; partial blocks (T not a
+    multiple of 128, features not multiples of 128) included."""
+    B, T, n_in, n_out = shape
+    X, G, _ = O.make_linear_inputs(B, T, n_in, n_out, 1e-2, seed=sum(shape))
+    G[0] *= 40.0
+    norms = {}
+    for algo in ("auto", "direct", "gram"):
+        _, n = check_wgrad(X, G, 0.05, 1.0, torch.float32, norm_algo=algo)
+        norms[algo] = n.cpu().numpy()
+    assert norm_err(norms["direct"], norms["gram"]) < 1e-5
+
+
 def test_two_dimensional_inputs_with_more_than_65535_rows(ops):
     """A 2-D layer input is `rows` samples of one row each (flashdp/layers/linear.py:51-53); the batch is
     not a grid dimension of any kernel, so it may exceed 65535."""
