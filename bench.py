@@ -247,6 +247,87 @@ def parity_check(dev, rank, world):
     return out
 
 
+def reference_gpu_leg(X, G, W, sigma, timed, own_dw):
+    """The UNMODIFIED reference package on this GPU, where `__graft_entry__.build()` installed it
+    (`baseline/_ref`, outside the history), run on the bench's own X and G.  Context for the headline
+    only: none of this library's code runs inside these timings.  Three entries, each on its own:
+      stock   its `DPLinear` autograd function (flashdp/layers/linear.py:40-104) run backward -- dX product,
+              `linear_weight_flashdp`, `.div_(B)`, `torch.normal` noise -- with the layer's default
+              `auto_tune=True`: the runtime tuner times the Triton per-sample loop
+              (flashdp/core/bmtm_clip_loop.py:162-173) against the `torch.jit.script` einsum loop
+              (flashdp/core/linear_clip.py:94-104) on the first backward and keeps the faster;
+      triton  the same with `auto_tune=False`, which always takes the Triton loop;
+      torch_candidate  the tuner's second candidate, `_weight_grad_block_clip`, called directly and
+              followed by the remaining operations of that backward, for the case that the Triton
+              kernels do not compile for this GPU (then `stock` fails too: the tuner runs them first)."""
+    import torch
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "flashdp")):
+        return {"unavailable": "no installed reference under baseline/_ref"}
+    B, T, n_in = X.shape
+    n_out = G.shape[-1]
+    out = {"what": "unmodified reference code for the DPLinear backward (dX + clipped dW + noise) on the same GPU",
+           "unit": UNIT}
+
+    def failure(e):
+        msg = str(e).splitlines()[0][:200] if str(e) else ""
+        return {"unavailable": "%s: %s" % (type(e).__name__, msg)}
+
+    def record(ms):
+        return {"value": flops_bwd(B, T, n_in, n_out) / (ms * 1e-3) / 1e12, "ms_per_step": ms}
+    try:
+        if ref_dir not in sys.path:
+            sys.path.insert(0, ref_dir)
+        import flashdp as ref
+        from flashdp.core.linear_clip import _weight_grad_block_clip
+    except Exception as e:
+        out.update(failure(e))
+        return out
+    for key, auto in (("stock", True), ("triton", False)):
+        try:
+            layer = ref.DPLinear(n_in, n_out, bias=None, device=X.device, dtype=X.dtype, C=1.0, clamp_value=1.0,
+                                 noise_multiplier=sigma, auto_tune=auto)
+            xr = X.detach().requires_grad_(True)
+            y = layer(xr)
+
+            def bwd():
+                return torch.autograd.grad(y, [xr, layer.weight], G, retain_graph=True)
+            for _ in range(3):          # the first call runs the layer's tuner (2 x 110 loops) when it is on
+                bwd()
+            out[key] = record(timed(bwd, 5) / 5)
+            if auto:
+                fn = layer.runtime_tuner.chosen_func
+                out[key]["tuner_chose"] = getattr(fn, "__name__", None) or getattr(fn, "name", None) or str(fn)
+            else:
+                # how far the Triton loop's clipped mean is from this library's on the same inputs; its
+                # per-sample norm accumulator starts from uninitialised memory (bmtm_clip_loop.py:146), so
+                # a difference is reported, not asserted (the noise differs too: compare at sigma = 0)
+                layer.noise_multiplier = 0.0
+                dw_ref = torch.autograd.grad(layer(xr), [layer.weight], G)[0].float()
+                out[key]["max_rel_diff_vs_this_library_sigma0"] = float((dw_ref - own_dw).abs().max() / own_dw.abs().max())
+            del layer, xr, y
+        except Exception as e:              # e.g. Triton cannot compile the reference's kernel for this GPU
+            out[key] = failure(e)
+            torch.cuda.synchronize()
+    try:
+        clip_args = torch.tensor([1.0, 1.0], device=X.device)
+
+        def candidate():
+            dx = G @ W                                                  # flashdp/layers/linear.py:62-64
+            dw = _weight_grad_block_clip(G, X, clip_args=clip_args).div_(B)
+            dw.add_(torch.normal(mean=0, std=sigma / math.sqrt(B), size=dw.shape, device=dw.device, dtype=dw.dtype))
+            return dx, dw
+        for _ in range(3):
+            candidate()
+        out["torch_candidate"] = record(timed(candidate, 5) / 5)
+        dw0 = _weight_grad_block_clip(G, X, clip_args=clip_args).div_(B).float()
+        out["torch_candidate"]["max_rel_diff_vs_this_library_sigma0"] = float((dw0 - own_dw).abs().max() / own_dw.abs().max())
+    except Exception as e:
+        out["torch_candidate"] = failure(e)
+    torch.cuda.synchronize()
+    return out
+
+
 def run_native(args, wl):
     import torch
     import torch.distributed as dist
@@ -448,6 +529,13 @@ def run_native(args, wl):
         gpu_loop = {"value": flops_bwd(B, T, n_in, n_out) / (loop_ms * 1e-3) / 1e12, "unit": UNIT,
                     "ms_per_step": loop_ms, "what": "per-sample loop of torch ops (cuBLAS) on the same GPU"}
 
+    ref_gpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.no_ref_gpu and dtn == "bf16":
+        noise0 = ops.NoiseSpec(std=0.0, seed=1234, param_id=1, step=1, rank=0, world=1)
+        own = ops.dp_linear_weight_grad(X, G, 1.0, 1.0, batch_divisor=B, noise=noise0, out_dtype=torch.float32)
+        ref_gpu = reference_gpu_leg(X, G, W, args.sigma, timed, own)
+        del own
+
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         full = cpu_port_rate(T, n_in, n_out, dtn, budget_s=0, sample_b=B, steps=2, warmup=1) if args.cpu_full else None
@@ -474,7 +562,7 @@ def run_native(args, wl):
                         "ms_per_step": e2e_ms, "steps": e2e_steps},
                 "gpu_launches": int(launches), "clocks": clocks, "roofline": roof, "cpu_baseline": cpu,
                 "step_frac_nominal": value / world / NOMINAL_BF16_TFLOPS, "step_frac_burst": value / world / pk["bf16"],
-                "parity_check": check, "gpu_loop_baseline": gpu_loop}
+                "parity_check": check, "gpu_loop_baseline": gpu_loop, "reference_on_gpu": ref_gpu}
     # the second headline metric on the same ranks: GPT-2-medium DP training tokens/s
     if args.workload == DEFAULT_WORKLOAD and not args.no_gpt2:
         del X, G, W, bufs, flush
@@ -909,6 +997,8 @@ def main():
     ap.add_argument("--no-cpu-full", dest="cpu_full", action="store_false")
     ap.add_argument("--no-gpt2", action="store_true", help="default workload: skip the GPT-2-medium leg")
     ap.add_argument("--no-check", action="store_true", help="skip the untimed N-rank == single-rank check")
+    ap.add_argument("--no-ref-gpu", action="store_true",
+                    help="skip the context leg that runs the installed reference package on the same GPU")
     args = ap.parse_args()
     if args.workload == "hbm_kernels_bf16_b16_t1024":
         return run_hbm(args)

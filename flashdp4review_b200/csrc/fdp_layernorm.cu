@@ -273,10 +273,17 @@ __global__ void __launch_bounds__(256, 4) ln_fwd_rows_kernel(const Tin* __restri
                                                              float* __restrict__ rstd, int rows, int d,
                                                              float eps, int pdt) {
   constexpr int VEC = 16 / sizeof(Tin);
-  extern __shared__ __align__(16) float ln_params[];   // gamma[d], beta[d]
+  // gamma[d] then beta[d] as fp32, stored so that a warp's 16-byte reads are adjacent: the four
+  // values k*4..k*4+3 of vector q (columns q*VEC ..) sit at float4 slot k*(d/VEC) + q.  With the
+  // plain column order a lane's two float4 reads would be 32 bytes apart and every read a two-way
+  // bank conflict.
+  extern __shared__ __align__(16) float ln_params[];
+  const int nvec = d / VEC;
   for (int c = threadIdx.x; c < d; c += 256) {
-    ln_params[c] = load_as(gamma, pdt, c);
-    ln_params[d + c] = load_as(beta, pdt, c);
+    const int q = c / VEC, i = c % VEC;
+    const int idx = ((i >> 2) * nvec + q) * 4 + (i & 3);
+    ln_params[idx] = load_as(gamma, pdt, c);
+    ln_params[d + idx] = load_as(beta, pdt, c);
   }
   __syncthreads();
   const int lane = threadIdx.x & 31;
@@ -293,18 +300,20 @@ __global__ void __launch_bounds__(256, 4) ln_fwd_rows_kernel(const Tin* __restri
     float sum = 0.f;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
-      const Tin* e = reinterpret_cast<const Tin*>(&raw[j]);
+      float f[VEC];
+      unpack16<Tin>(raw[j], f);
 #pragma unroll
-      for (int v = 0; v < VEC; ++v) sum += to_f32<Tin>(e[v]);     // padding vectors are zero
+      for (int v = 0; v < VEC; ++v) sum += f[v];     // padding vectors are zero
     }
     const float mu = warp_sum(sum) * inv_d;
     float q = 0.f;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
       if ((j * 32 + lane) * VEC < d) {
-        const Tin* e = reinterpret_cast<const Tin*>(&raw[j]);
+        float f[VEC];
+        unpack16<Tin>(raw[j], f);
 #pragma unroll
-        for (int v = 0; v < VEC; ++v) { const float t = to_f32<Tin>(e[v]) - mu; q = fmaf(t, t, q); }
+        for (int v = 0; v < VEC; ++v) { const float t = f[v] - mu; q = fmaf(t, t, q); }
       }
     }
     const float rs = 1.0f / sqrtf(warp_sum(q) * inv_d + eps);
@@ -312,21 +321,20 @@ __global__ void __launch_bounds__(256, 4) ln_fwd_rows_kernel(const Tin* __restri
     Tin* yr = y + static_cast<size_t>(row) * d;
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
-      const int c = (j * 32 + lane) * VEC;
-      if (c < d) {
-        const Tin* e = reinterpret_cast<const Tin*>(&raw[j]);
-        uint4 outv;
-        Tin* o = reinterpret_cast<Tin*>(&outv);
+      const int vq = j * 32 + lane;
+      if (vq * VEC < d) {
+        float f[VEC], o[VEC];
+        unpack16<Tin>(raw[j], f);
 #pragma unroll
         for (int v4 = 0; v4 < VEC / 4; ++v4) {
-          const float4 g = *reinterpret_cast<const float4*>(ln_params + c + 4 * v4);
-          const float4 b = *reinterpret_cast<const float4*>(ln_params + d + c + 4 * v4);
-          o[4 * v4 + 0] = from_f32<Tin>(fmaf((to_f32<Tin>(e[4 * v4 + 0]) - mu) * rs, g.x, b.x));
-          o[4 * v4 + 1] = from_f32<Tin>(fmaf((to_f32<Tin>(e[4 * v4 + 1]) - mu) * rs, g.y, b.y));
-          o[4 * v4 + 2] = from_f32<Tin>(fmaf((to_f32<Tin>(e[4 * v4 + 2]) - mu) * rs, g.z, b.z));
-          o[4 * v4 + 3] = from_f32<Tin>(fmaf((to_f32<Tin>(e[4 * v4 + 3]) - mu) * rs, g.w, b.w));
+          const float4 g = *reinterpret_cast<const float4*>(ln_params + (v4 * nvec + vq) * 4);
+          const float4 b = *reinterpret_cast<const float4*>(ln_params + d + (v4 * nvec + vq) * 4);
+          o[4 * v4 + 0] = fmaf((f[4 * v4 + 0] - mu) * rs, g.x, b.x);
+          o[4 * v4 + 1] = fmaf((f[4 * v4 + 1] - mu) * rs, g.y, b.y);
+          o[4 * v4 + 2] = fmaf((f[4 * v4 + 2] - mu) * rs, g.z, b.z);
+          o[4 * v4 + 3] = fmaf((f[4 * v4 + 3] - mu) * rs, g.w, b.w);
         }
-        *reinterpret_cast<uint4*>(yr + c) = outv;
+        *reinterpret_cast<uint4*>(yr + vq * VEC) = pack16<Tin>(o);
       }
     }
   }
@@ -400,8 +408,21 @@ void ln_fwd(const void* x, const void* gamma, const void* beta, void* y, float* 
 // STAGED: a ninth warp streams the rows of x and dy into a shared-memory ring with bulk async
 // copies (one stage = the RG rows the row groups work on at once), so several stages are in flight
 // per SM whatever the register-limited occupancy; the row groups read their row from the ring.
+#ifndef FDP_LN_BWD_PRODUCER_WARP
+#define FDP_LN_BWD_PRODUCER_WARP 0
+#endif
+// Who feeds the ring.  0: thread 0 of the block, between its own rows -- the block is then exactly
+// CW threads; with CW = 512 that is four warps per scheduler and 128 registers per thread.  1: an
+// extra warp -- a fifth warp on one scheduler, which caps every thread at 96 registers.
+constexpr bool LN_BWD_PW = FDP_LN_BWD_PRODUCER_WARP != 0;
+#ifndef FDP_LN_BWD_STAGES
+#define FDP_LN_BWD_STAGES (FDP_LN_BWD_PRODUCER_WARP ? 3 : 5)
+#endif
+#ifndef FDP_LN_BWD_RING_KB
+#define FDP_LN_BWD_RING_KB (FDP_LN_BWD_PRODUCER_WARP ? 96 : 160)
+#endif
 template <typename Tin, int VEC, int NV, int TPR, bool STAGED, int CW>
-__global__ void __launch_bounds__(STAGED ? CW + 32 : CW) ln_bwd_kernel(
+__global__ void __launch_bounds__((STAGED && LN_BWD_PW) ? CW + 32 : CW) ln_bwd_kernel(
     const Tin* __restrict__ dy, const Tin* __restrict__ x, const void* __restrict__ gamma,
     const float* __restrict__ mean, const float* __restrict__ rstd, Tin* __restrict__ dx,
     float* __restrict__ dg_part, float* __restrict__ db_part, int T, int d, int pdt,
@@ -449,24 +470,31 @@ __global__ void __launch_bounds__(STAGED ? CW + 32 : CW) ln_bwd_kernel(
     }
   const float inv_d = 1.0f / d;
 
-  if (STAGED && threadIdx.x >= CW) {
+  // the RG rows of iteration `it` (x, then dy) into stage `st`; one thread
+  auto issue_stage = [&](int it, int st) {
+    const int rb = r0 + it * RG;
+    const int nrows = min(RG, r1 - rb);
+    const size_t goff = (static_cast<size_t>(b) * T + rb) * d;
+    mbar_expect_tx(smem_u32(&bars[st]), 2 * nrows * row_bytes);
+    bulk_load(smem_u32(ln_smem + st * stage_bytes), x + goff, nrows * row_bytes, smem_u32(&bars[st]));
+    bulk_load(smem_u32(ln_smem + st * stage_bytes + RG * row_bytes), dy + goff, nrows * row_bytes, smem_u32(&bars[st]));
+  };
+  if (STAGED && LN_BWD_PW && threadIdx.x >= CW) {
     // ---- producer warp ----
     if (threadIdx.x == CW) {
       int s = 0; uint32_t ph = 0;
       for (int it = 0; it < n_iter; ++it) {
         if (!mbar_wait(smem_u32(&bars[LN_MAX_STAGES + s]), ph ^ 1u, wctx, 7)) break;
-        const int rb = r0 + it * RG;
-        const int nrows = min(RG, r1 - rb);
-        const size_t goff = (static_cast<size_t>(b) * T + rb) * d;
-        mbar_expect_tx(smem_u32(&bars[s]), 2 * nrows * row_bytes);
-        bulk_load(smem_u32(ln_smem + s * stage_bytes), x + goff, nrows * row_bytes, smem_u32(&bars[s]));
-        bulk_load(smem_u32(ln_smem + s * stage_bytes + RG * row_bytes), dy + goff, nrows * row_bytes, smem_u32(&bars[s]));
+        issue_stage(it, s);
         if (++s == n_stages) { s = 0; ph ^= 1u; }
       }
     }
   } else {
     // ---- row groups ----
+    if (STAGED && !LN_BWD_PW && threadIdx.x == 0)
+      for (int it = 0; it < n_stages && it < n_iter; ++it) issue_stage(it, it);
     int s = 0; uint32_t ph = 0;
+    int prev_s = 0; uint32_t prev_ph = 0;
     for (int it = 0; it < n_iter; ++it) {
       const int r = r0 + it * RG + rg;
       const bool valid = r < r1;
@@ -488,16 +516,15 @@ __global__ void __launch_bounds__(STAGED ? CW + 32 : CW) ln_bwd_kernel(
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
           const int c = (j * TPR + t) * VEC;
-          if (VEC > 1) {
+          if constexpr (VEC > 1) {
             if (c < d) {
-              const uint4 rx = *reinterpret_cast<const uint4*>(xr + c);
-              const uint4 rd = *reinterpret_cast<const uint4*>(dyr + c);
-              const Tin* ex = reinterpret_cast<const Tin*>(&rx);
-              const Tin* ed = reinterpret_cast<const Tin*>(&rd);
+              float ex[VEC], ed[VEC];
+              unpack16<Tin>(*reinterpret_cast<const uint4*>(xr + c), ex);
+              unpack16<Tin>(*reinterpret_cast<const uint4*>(dyr + c), ed);
 #pragma unroll
               for (int v = 0; v < VEC; ++v) {
                 const int i = j * VEC + v;
-                const float xv = (to_f32<Tin>(ex[v]) - mu) * rs, dv = to_f32<Tin>(ed[v]);
+                const float xv = (ex[v] - mu) * rs, dv = ed[v];
                 xh[i] = xv; wd[i] = dv * gam[i];
                 accg[i] = fmaf(dv, xv, accg[i]); accb[i] += dv;
                 s1 = fmaf(xv, wd[i], s1); s2 += wd[i];
@@ -521,6 +548,14 @@ __global__ void __launch_bounds__(STAGED ? CW + 32 : CW) ln_bwd_kernel(
         // the row is in registers: hand the stage back to the producer
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bars[LN_MAX_STAGES + s]));
+        if (!LN_BWD_PW && threadIdx.x == 0 && it >= 1 && it - 1 + n_stages < n_iter) {
+          // refill the stage of the PREVIOUS iteration: by now every warp has normally taken its row
+          // of that stage into registers, so this wait rarely spins, and no row group is tied to the
+          // slowest one of the current iteration.  If the wait runs out nothing is issued and the
+          // consumers' own bounded waits end the block.
+          if (mbar_wait(smem_u32(&bars[LN_MAX_STAGES + prev_s]), prev_ph, wctx, 7)) issue_stage(it - 1 + n_stages, prev_s);
+        }
+        prev_s = s; prev_ph = ph;
         if (++s == n_stages) { s = 0; ph ^= 1u; }
       }
       if (!valid) { if (!ok) break; continue; }     // `valid` is the same for the whole row group
@@ -542,15 +577,14 @@ __global__ void __launch_bounds__(STAGED ? CW + 32 : CW) ln_bwd_kernel(
         for (int j = 0; j < NV; ++j) {
           const int c = (j * TPR + t) * VEC;
           if (c >= d) continue;
-          if (VEC > 1) {
-            uint4 outv;
-            Tin* o = reinterpret_cast<Tin*>(&outv);
+          if constexpr (VEC > 1) {
+            float o[VEC];
 #pragma unroll
             for (int v = 0; v < VEC; ++v) {
               const int i = j * VEC + v;
-              o[v] = from_f32<Tin>(fmaf(xh[i], a1, fmaf(wd[i], rs, a2)));   // (wd - (xhat*c1 + c2)) * rs
+              o[v] = fmaf(xh[i], a1, fmaf(wd[i], rs, a2));   // (wd - (xhat*c1 + c2)) * rs
             }
-            *reinterpret_cast<uint4*>(dxr + c) = outv;
+            *reinterpret_cast<uint4*>(dxr + c) = pack16<Tin>(o);
           } else {
             dxr[c] = from_f32<Tin>(fmaf(xh[j], a1, fmaf(wd[j], rs, a2)));
           }
@@ -567,10 +601,19 @@ __global__ void __launch_bounds__(STAGED ? CW + 32 : CW) ln_bwd_kernel(
     __syncthreads();
     if (threadIdx.x < CW) {
 #pragma unroll
-      for (int j = 0; j < NV; ++j)
+      for (int j = 0; j < NV; ++j) {
+        if constexpr (VEC % 4 == 0) {
 #pragma unroll
-        for (int v = 0; v < VEC; ++v)
-          sm[rg * CPG + (j * TPR + t) * VEC + v] = which == 0 ? accg[j * VEC + v] : accb[j * VEC + v];
+          for (int v = 0; v < VEC; v += 4) {
+            const float* a = (which == 0 ? accg : accb) + j * VEC + v;
+            *reinterpret_cast<float4*>(&sm[rg * CPG + (j * TPR + t) * VEC + v]) = make_float4(a[0], a[1], a[2], a[3]);
+          }
+        } else {
+#pragma unroll
+          for (int v = 0; v < VEC; ++v)
+            sm[rg * CPG + (j * TPR + t) * VEC + v] = which == 0 ? accg[j * VEC + v] : accb[j * VEC + v];
+        }
+      }
     }
     __syncthreads();
     float* dst = outp[which] + (static_cast<size_t>(b) * chunks + chunk) * d;
@@ -631,7 +674,7 @@ static bool ln_bwd_launch_one(const void* dy, const void* x, const void* gamma, 
   static bool done[64];
   static std::mutex mu;
   if (smem > 48 * 1024 && !smem_opt_in(done, mu, ln_bwd_kernel<Tin, VEC, NV, TPRV, STAGED, CW>, LN_SMEM_BUDGET)) return false;
-  ln_bwd_kernel<Tin, VEC, NV, TPRV, STAGED, CW><<<grid, STAGED ? CW + 32 : CW, smem, s>>>(
+  ln_bwd_kernel<Tin, VEC, NV, TPRV, STAGED, CW><<<grid, (STAGED && LN_BWD_PW) ? CW + 32 : CW, smem, s>>>(
       (const Tin*)dy, (const Tin*)x, gamma, mean, rstd, (Tin*)dx, dg_part, db_part, T, d, pdt,
       pl.rows_per_block, pl.chunks, n_stages, sticky_status_slot());
   note_launch();
@@ -642,10 +685,11 @@ template <typename Tin, int VEC, int NV, int CW>
 static void ln_bwd_launch(const void* dy, const void* x, const void* gamma, const float* mean,
                           const float* rstd, void* dx, float* dg_part, float* db_part, int B, int T,
                           int d, int pdt, const LnPlan& pl, cudaStream_t s) {
-  // ring of up to 3 stages of at most 96 KiB in total; needs 16-byte rows, i.e. the vector path
+  // ring of up to FDP_LN_BWD_STAGES stages within FDP_LN_BWD_RING_KB (one block per SM, so most of the
+  // SM's shared memory is free for it); needs 16-byte rows, i.e. the vector path
   const size_t stage_bytes = static_cast<size_t>(2) * (CW / pl.tpr) * d * sizeof(Tin);
-  int n_stages = static_cast<int>((96 * 1024) / stage_bytes);
-  if (n_stages > 3) n_stages = 3;
+  int n_stages = static_cast<int>((static_cast<size_t>(FDP_LN_BWD_RING_KB) * 1024) / stage_bytes);
+  if (n_stages > FDP_LN_BWD_STAGES) n_stages = FDP_LN_BWD_STAGES;
   const int n_iter = ceil_div(pl.rows_per_block, CW / pl.tpr);
   if (n_stages > n_iter) n_stages = n_iter;
   const bool staged = VEC > 1 && n_stages >= 2;

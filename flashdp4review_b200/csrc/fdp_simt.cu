@@ -563,8 +563,11 @@ void simt_fwd(const void* X, const void* W, const void* bias, void* Y, int rows,
 // Block = 32 column-threads x 8 row-threads.  A column-thread owns VEC adjacent columns (one
 // 16-byte load per row); the 8 row-threads stride over the rows of the chunk.  Partials are
 // combined in a fixed order, so results are bit-reproducible.
+#ifndef FDP_GSTATS_UNROLL
+#define FDP_GSTATS_UNROLL 8
+#endif
 template <typename Tin, int VEC>
-__global__ void __launch_bounds__(256) gstats_kernel(const Tin* __restrict__ G,
+__global__ void __launch_bounds__(256, 4) gstats_kernel(const Tin* __restrict__ G,
                                                      float* __restrict__ colsum_part,
                                                      float* __restrict__ sq_part, int T, int n_out,
                                                      int rows_per_chunk, int vec_ok, int col_chunks, int row_chunks) {
@@ -583,25 +586,29 @@ __global__ void __launch_bounds__(256) gstats_kernel(const Tin* __restrict__ G,
   float sq = 0.f;
   if (vec_ok) {
     if (c0 < n_out) {
-      // four independent 16-byte loads in flight per thread before any of them is consumed
+      // U independent 16-byte loads in flight per thread before any of them is consumed: the kernel
+      // waits on memory latency, and four resident blocks of 256 threads with eight loads each keep
+      // about 128 KB in flight per SM
+      constexpr int U = FDP_GSTATS_UNROLL;
       int r = r0 + y;
-      for (; r + 24 < r1; r += 32) {
-        uint4 raw[4];
+      for (; r + 8 * (U - 1) < r1; r += 8 * U) {
+        uint4 raw[U];
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
+        for (int k = 0; k < U; ++k)
           raw[k] = __ldg(reinterpret_cast<const uint4*>(Gb + static_cast<size_t>(r + 8 * k) * n_out + c0));
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          const Tin* e = reinterpret_cast<const Tin*>(&raw[k]);
+        for (int k = 0; k < U; ++k) {
+          float f[VEC];
+          unpack16<Tin>(raw[k], f);
 #pragma unroll
-          for (int v = 0; v < VEC; ++v) { const float f = to_f32<Tin>(e[v]); acc[v] += f; sq = fmaf(f, f, sq); }
+          for (int v = 0; v < VEC; ++v) { acc[v] += f[v]; sq = fmaf(f[v], f[v], sq); }
         }
       }
       for (; r < r1; r += 8) {
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(Gb + static_cast<size_t>(r) * n_out + c0));
-        const Tin* e = reinterpret_cast<const Tin*>(&raw);
+        float f[VEC];
+        unpack16<Tin>(__ldg(reinterpret_cast<const uint4*>(Gb + static_cast<size_t>(r) * n_out + c0)), f);
 #pragma unroll
-        for (int v = 0; v < VEC; ++v) { const float f = to_f32<Tin>(e[v]); acc[v] += f; sq = fmaf(f, f, sq); }
+        for (int v = 0; v < VEC; ++v) { acc[v] += f[v]; sq = fmaf(f[v], f[v], sq); }
       }
     }
   } else {
@@ -631,6 +638,9 @@ __global__ void __launch_bounds__(256) gstats_kernel(const Tin* __restrict__ G,
   }
 }
 
+#ifndef FDP_GSTATS_BALANCE
+#define FDP_GSTATS_BALANCE 1
+#endif
 GstatsPlan gstats_plan(int B, int T, int n_out, int dt) {
   GstatsPlan pl;
   pl.vec = (dt == FDP_F32) ? 4 : 8;
@@ -642,6 +652,25 @@ GstatsPlan gstats_plan(int B, int T, int n_out, int dt) {
   pl.rows_per_chunk = 256;
   if (static_cast<long long>(B) * pl.col_chunks * ceil_div(T, 256) < 4 * 148) pl.rows_per_chunk = 128;
   pl.row_chunks = ceil_div(T, pl.rows_per_chunk);
+  // Blocks are handed to the 148 SMs as they free up, so the kernel ends when the SM with the most
+  // blocks ends: pick the number of row chunks (at most 4x finer than the rule above, each at least
+  // 64 rows) that minimises ceil(blocks / 148) * (rows per chunk + a fixed cost per block); ties go to
+  // fewer chunks (fewer partials).  B=16, T=1024, 3072 columns: 3 chunks of 342 rows (576 blocks,
+  // 4 on the fullest SM against 3.9 on average) instead of 4 of 256 (768 blocks, 6 against 5.2).
+  // The constant keeps the workspace query and the launch in agreement on every device.
+  if (FDP_GSTATS_BALANCE) {
+    constexpr int GS_SMS = 148, BLOCK_FIXED_ROWS = 8;
+    const long long strips = static_cast<long long>(B) * pl.col_chunks;
+    const int base = pl.row_chunks;
+    long long best = -1;
+    for (int rc = 1; rc <= 4 * base && ceil_div(T, rc) >= 64; ++rc) {
+      const long long blocks = strips * rc;
+      const long long cost = ((blocks + GS_SMS - 1) / GS_SMS) * (ceil_div(T, rc) + BLOCK_FIXED_ROWS);
+      if (best < 0 || cost < best) { best = cost; pl.row_chunks = rc; }
+    }
+    pl.rows_per_chunk = ceil_div(T, pl.row_chunks);
+    pl.row_chunks = ceil_div(T, pl.rows_per_chunk);
+  }
   return pl;
 }
 

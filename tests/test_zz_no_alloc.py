@@ -99,7 +99,7 @@ def test_static_scratch_bias_grad_matches_workspace_variant_twice_in_a_row():
 def test_static_scratch_limit_is_enforced():
     from flashdp4review_b200 import _lib
     lib = _lib.load()
-    B, T, n_out = 64, 4096, 8192
+    B, T, n_out = 256, 4096, 8192
     assert lib.fdp_bias_grad_workspace_bytes(B, T, n_out, 1) > _lib.FDP_STATIC_SCRATCH_BYTES
     dummy = torch.zeros(16, device=dev())
     p = _params(_lib, 0.0)
