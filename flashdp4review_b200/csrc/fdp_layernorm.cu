@@ -416,10 +416,10 @@ void ln_fwd(const void* x, const void* gamma, const void* beta, void* y, float* 
 // extra warp -- a fifth warp on one scheduler, which caps every thread at 96 registers.
 constexpr bool LN_BWD_PW = FDP_LN_BWD_PRODUCER_WARP != 0;
 #ifndef FDP_LN_BWD_STAGES
-#define FDP_LN_BWD_STAGES (FDP_LN_BWD_PRODUCER_WARP ? 3 : 5)
+#define FDP_LN_BWD_STAGES 3
 #endif
 #ifndef FDP_LN_BWD_RING_KB
-#define FDP_LN_BWD_RING_KB (FDP_LN_BWD_PRODUCER_WARP ? 96 : 160)
+#define FDP_LN_BWD_RING_KB 96
 #endif
 template <typename Tin, int VEC, int NV, int TPR, bool STAGED, int CW>
 __global__ void __launch_bounds__((STAGED && LN_BWD_PW) ? CW + 32 : CW) ln_bwd_kernel(
@@ -634,7 +634,9 @@ LnPlan ln_plan(int B, int T, int d, int dt) {
   pl.vec = (d % V == 0);
   const int vec = pl.vec ? V : 1;
   // Vector path up to d = 4096: 16 columns per thread and 512 consumer threads (16 warps hide the
-  // latency of the row arithmetic; about 100 registers each).  Otherwise 32 columns, 256 threads.
+  // latency of the row arithmetic; about 115 registers each).  Otherwise 32 columns, 256 threads
+  // (one warp per row at d = 1024, no exchange between warps, but only 8 warps per SM: 37.2 against
+  // 36.2 us per call at B=16, T=1024, d=1024, bf16).
   int nv_max = pl.vec ? (32 / V) : 32;
   pl.cw = 256;
   if (pl.vec && d <= 4096) { nv_max = 16 / V; pl.cw = 512; }
@@ -685,8 +687,9 @@ template <typename Tin, int VEC, int NV, int CW>
 static void ln_bwd_launch(const void* dy, const void* x, const void* gamma, const float* mean,
                           const float* rstd, void* dx, float* dg_part, float* db_part, int B, int T,
                           int d, int pdt, const LnPlan& pl, cudaStream_t s) {
-  // ring of up to FDP_LN_BWD_STAGES stages within FDP_LN_BWD_RING_KB (one block per SM, so most of the
-  // SM's shared memory is free for it); needs 16-byte rows, i.e. the vector path
+  // ring of up to FDP_LN_BWD_STAGES stages within FDP_LN_BWD_RING_KB (five stages in 160 KiB measured
+  // no faster than three in 96 KiB: 36.1 against 35.3 us per call at B=16, T=1024, d=1024, bf16);
+  // needs 16-byte rows, i.e. the vector path
   const size_t stage_bytes = static_cast<size_t>(2) * (CW / pl.tpr) * d * sizeof(Tin);
   int n_stages = static_cast<int>((static_cast<size_t>(FDP_LN_BWD_RING_KB) * 1024) / stage_bytes);
   if (n_stages > FDP_LN_BWD_STAGES) n_stages = FDP_LN_BWD_STAGES;
