@@ -1,5 +1,6 @@
 // extern "C" entry points: argument checks, workspace carving, kernel selection.
 // No allocation, no host synchronisation (except fdp_device_status), no exceptions.
+#include <cstdlib>
 #include <atomic>
 #include <mutex>
 
@@ -12,6 +13,13 @@ using namespace fdp;
 namespace fdp {
 static std::atomic<unsigned long long> g_launches{0};
 void note_launch(int n) { g_launches.fetch_add(static_cast<unsigned long long>(n), std::memory_order_relaxed); }
+bool pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("FDP_PDL");
+    return e == nullptr || e[0] != '0';
+  }();
+  return on;
+}
 
 // Host-visible status array: one int per device in mapped, pinned host memory (allocated once per
 // process; with unified addressing the host pointer is valid on every device).  Kernels store a

@@ -14,6 +14,38 @@ int* sticky_status_slot();
 // SMs persistent GEMM grids leave free (fdp_set_sm_reserve)
 int sm_reserve_exchange(int n);
 
+// Programmatic dependent launch for the second and later kernels of one entry point.  A kernel
+// launched with launch_dependent() may be scheduled as soon as every block of the kernel before it
+// in the stream has called pdl_trigger() (or exited), so its launch latency and prologue overlap
+// that kernel's tail; it must call pdl_wait() before it touches anything the earlier kernel wrote
+// (the wait returns when the earlier grid has completed and its writes are visible).  The first
+// kernel of an entry point is always launched the ordinary way, so nothing of the library ever
+// overtakes the caller's own work in the stream.  FDP_PDL=0 in the environment turns it off.
+bool pdl_enabled();
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+template <typename... KArgs, typename... Args>
+inline void launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s,
+                             Args&&... args) {
+  if (!pdl_enabled()) {
+    kernel<<<grid, block, smem, s>>>(static_cast<KArgs>(args)...);
+    return;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 // ---- generic-shape kernels (any dtype, any size; fp32 FMA accumulation) -----------------------
 int simt_norm_tiles(int n_in, int n_out);
 // partials[b*nparts + part] add up to ||G_b^T X_b||_F^2; returns nparts, which is at most simt_norm_tiles

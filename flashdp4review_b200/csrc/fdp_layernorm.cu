@@ -593,6 +593,7 @@ __global__ void __launch_bounds__((STAGED && LN_BWD_PW) ? CW + 32 : CW) ln_bwd_k
     }
   }
 
+  pdl_trigger();   // the reduction kernel may be scheduled while this block finishes
   // cross-row-group sum, fixed order, one tensor at a time through the same shared buffer
   constexpr int CPG = TPR * NV * VEC;  // columns covered by a row group
   float* outp[2] = {dg_part, db_part};
@@ -739,6 +740,8 @@ __global__ void __launch_bounds__(256) ln_psgrad_reduce_kernel(float* __restrict
                                                                float* __restrict__ sumsq, int chunks,
                                                                int d) {
   __shared__ float red[32];
+  pdl_trigger();
+  pdl_wait();
   // one-dimensional grid: block = (tensor*B + b) * column blocks + block of 256 columns
   const int nblk = (d + 255) / 256;
   const int sample = blockIdx.x / nblk, cblk = blockIdx.x % nblk;
@@ -759,7 +762,7 @@ int ln_sumsq_parts(int d) { return ceil_div(d, 256); }
 
 void ln_psgrad_reduce(float* part, float* sumsq, int B, int chunks, int d, cudaStream_t s) {
   const unsigned grid = static_cast<unsigned>(static_cast<size_t>(2) * B * ln_sumsq_parts(d));
-  ln_psgrad_reduce_kernel<<<grid, 256, 0, s>>>(part, sumsq, chunks, d);
+  launch_dependent(ln_psgrad_reduce_kernel, dim3(grid), dim3(256), 0, s, part, sumsq, chunks, d);
   note_launch();
 }
 
@@ -768,6 +771,7 @@ __global__ void __launch_bounds__(256) ln_psgrad_finalize_kernel(const float* __
                                                                  void* __restrict__ out0, void* __restrict__ out1,
                                                                  int B, int chunks, int d, int out_dt,
                                                                  float inv_div, NoiseKey nk0, NoiseKey nk1) {
+  pdl_wait();
   const int c = blockIdx.x * 256 + threadIdx.x;
   const int tensor = blockIdx.y;
   void* out = tensor == 0 ? out0 : out1;
@@ -785,7 +789,7 @@ __global__ void __launch_bounds__(256) ln_psgrad_finalize_kernel(const float* __
 void ln_psgrad_finalize(const float* part, const float* factors, void* out0, void* out1, int B, int chunks,
                         int d, int out_dt, float inv_div, NoiseKey nk0, NoiseKey nk1, cudaStream_t s) {
   dim3 grid(ceil_div(d, 256), 2);
-  ln_psgrad_finalize_kernel<<<grid, 256, 0, s>>>(part, factors, out0, out1, B, chunks, d, out_dt, inv_div, nk0, nk1);
+  launch_dependent(ln_psgrad_finalize_kernel, grid, dim3(256), 0, s, part, factors, out0, out1, B, chunks, d, out_dt, inv_div, nk0, nk1);
   note_launch();
 }
 
@@ -796,6 +800,7 @@ __global__ void __launch_bounds__(256) ln_clip_finalize_kernel(
   extern __shared__ float s_fac[];  // [B] factors of this block's tensor
   const int tensor = blockIdx.y;
   const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+  pdl_wait();
   for (int b = w; b < B; b += 8) {
     float sq = 0.f;
     for (int i = lane; i < nparts; i += 32) sq += sumsq[static_cast<size_t>(tensor * B + b) * nparts + i];
@@ -825,8 +830,8 @@ void ln_clip_finalize(const float* part, const float* sumsq, int nparts, float C
                       float inv_div, NoiseKey nk0, NoiseKey nk1, cudaStream_t s) {
   if (static_cast<size_t>(B) * sizeof(float) <= 32 * 1024) {
     dim3 grid(ceil_div(d, 256), 2);
-    ln_clip_finalize_kernel<<<grid, 256, B * sizeof(float), s>>>(part, sumsq, nparts, C, clamp, norms0, norms1, out0,
-                                                                 out1, B, chunks, d, out_dt, inv_div, nk0, nk1);
+    launch_dependent(ln_clip_finalize_kernel, grid, dim3(256), B * sizeof(float), s, part, sumsq, nparts, C, clamp,
+                     norms0, norms1, out0, out1, B, chunks, d, out_dt, inv_div, nk0, nk1);
     note_launch();
     return;
   }

@@ -622,6 +622,7 @@ __global__ void __launch_bounds__(256, 4) gstats_kernel(const Tin* __restrict__ 
       }
     }
   }
+  pdl_trigger();   // the finalisation kernel may be scheduled while this block reduces and stores
 #pragma unroll
   for (int v = 0; v < VEC; ++v) cs[y][x * VEC + v] = acc[v];
   sq = block_sum(sq, red);  // contains the __syncthreads that publishes cs
@@ -732,6 +733,7 @@ __global__ void __launch_bounds__(256) bias_finalize_fused_kernel(
   extern __shared__ float s_fac[];  // [B]
   __shared__ float part[8][32];
   const int col = threadIdx.x & 31, sl = threadIdx.x >> 5;
+  pdl_wait();
   for (int b = sl; b < B; b += 8) {
     float sq = 0.f;
     for (int i = col; i < nparts; i += 32) sq += sq_part[static_cast<size_t>(b) * nparts + i];
@@ -770,8 +772,9 @@ void bias_clip_finalize(const float* colsum_part, const float* sq_part, int npar
                         float* factors_ws, float* norms_out, float* factors_out, void* db, int B, int n_out,
                         int row_chunks, int out_dt, float inv_div, NoiseKey nk, cudaStream_t s) {
   if (static_cast<size_t>(B) * sizeof(float) <= 32 * 1024) {
-    bias_finalize_fused_kernel<<<ceil_div(n_out, 32), 256, B * sizeof(float), s>>>(
-        colsum_part, sq_part, nparts, C, clamp, norms_out, factors_out, db, B, n_out, row_chunks, out_dt, inv_div, nk);
+    launch_dependent(bias_finalize_fused_kernel, dim3(ceil_div(n_out, 32)), dim3(256), B * sizeof(float), s,
+                     colsum_part, sq_part, nparts, C, clamp, norms_out, factors_out, db, B, n_out, row_chunks, out_dt,
+                     inv_div, nk);
     note_launch();
     return;
   }

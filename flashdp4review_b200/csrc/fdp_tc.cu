@@ -61,6 +61,7 @@ struct TcArgs {
   int T;
   int* status;          // status word of the call (workspace)
   int zero_status;      // this launch is the first of its call: its first thread clears the status word
+  int dependent;        // host side: launch as a programmatic dependent of the kernel before it in the stream
   int* sticky;          // this device's slot of the host-visible status array, or null
   uint32_t idesc;
   // split-K (store epilogues): work units [0, units_full) are whole tiles; each later tile is cut into
@@ -328,6 +329,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  // Barriers, TMEM and the shared-memory carve-up are ready.  Let the kernel that follows in the
+  // stream be scheduled as SMs free up (it waits at this same point), and, if this launch is itself
+  // a programmatic dependent, wait here for the kernel before it: nothing above touched global
+  // memory that an earlier kernel writes.
+  pdl_trigger();
+  pdl_wait();
   // work is dealt to CTAs (or CTA pairs) round-robin
   const int wid = blockIdx.x / CTAS, wstep = gridDim.x / CTAS;
   const uint32_t tmem_base = *tmem_slot;
@@ -736,6 +743,7 @@ __global__ void __launch_bounds__(256) splitk_fixup_kernel(const float* __restri
                                                            int m_group,
                                                            void* __restrict__ out, int out_dt, long long ld_out,
                                                            float scale, NoiseKey nk) {
+  pdl_wait();
   const int t = blockIdx.y;  // index among the split tiles
   const int q = first_tile + t;
   int mi, ni;  // the tile order of tc_gemm_kernel's decode
@@ -900,7 +908,8 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, co
   int units = la.units_full + (total - la.units_full) * la.split;
   const int workers = launch_sms() / CTAS;   // CTAs, or CTA pairs
   const int grid = CTAS * (units < workers ? units : workers);
-  if (CTAS == 1) {
+  const bool dependent = la.dependent != 0 && pdl_enabled();
+  if (CTAS == 1 && !dependent) {
     tc_gemm_kernel<A_MN, B_MN, EPI, CTAS><<<grid, threads_for(EPI), SMEM, s>>>(a, b, a2, b2, la);
   } else {
     cudaLaunchConfig_t cfg = {};
@@ -908,10 +917,19 @@ int launch(const CUtensorMap& a, const CUtensorMap& b, const CUtensorMap& a2, co
     cfg.blockDim = dim3(threads_for(EPI));
     cfg.dynamicSmemBytes = SMEM;
     cfg.stream = s;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (CTAS == 2) {
+      attr[na].id = cudaLaunchAttributeClusterDimension;
+      attr[na].val.clusterDim.x = 2; attr[na].val.clusterDim.y = 1; attr[na].val.clusterDim.z = 1;
+      ++na;
+    }
+    if (dependent) {
+      attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[na].val.programmaticStreamSerializationAllowed = 1;
+      ++na;
+    }
+    cfg.attrs = attr; cfg.numAttrs = na;
     if (cudaLaunchKernelEx(&cfg, tc_gemm_kernel<A_MN, B_MN, EPI, CTAS>, a, b, a2, b2, la) != cudaSuccess) {
       cudaGetLastError();
       return FDP_ERR_LAUNCH;
@@ -1112,6 +1130,7 @@ int tc_clipped_wgrad(const void* Gs, const void* X, const TcFactorSource* fs, fl
       !make_map(&mx, X, rows, terms == 3 ? 2 * n_in : n_in, 64, BK, dt)) return FDP_ERR_LAUNCH;
   TcArgs args{};
   args.batch = 1; args.batch_rows = 0; args.status = dev_status;
+  args.dependent = 1;             // always follows a kernel of the same call (norm pass, clip factors or pre-scale)
   args.terms = terms;
   args.term_stages = T / BK;      // used when terms == 3: every sample's rows are visited three times
   args.k_stages = terms * static_cast<int>((rows + BK - 1) / BK);
@@ -1156,9 +1175,9 @@ int tc_clipped_wgrad(const void* Gs, const void* X, const TcFactorSource* fs, fl
   if (st != FDP_OK || split <= 1) return st;
   // the scaled epilogue parks its parts already divided by the batch
   dim3 grid(BM * ctas * BN / (256 * 4), n_split_tiles);
-  splitk_fixup_kernel<<<grid, 256, 0, s>>>(args.split_ws, args.units_full, split, BM * ctas, args.M, args.N,
-                                           args.tiles_m, args.tiles_n, args.n_fastest, args.m_group, dW, out_dt,
-                                           args.ld_out, scaled ? 1.0f : inv_div, nk);
+  launch_dependent(splitk_fixup_kernel, grid, dim3(256), 0, s, args.split_ws, args.units_full, split, BM * ctas, args.M,
+                   args.N, args.tiles_m, args.tiles_n, args.n_fastest, args.m_group, dW, out_dt, args.ld_out,
+                   scaled ? 1.0f : inv_div, nk);
   note_launch();
   return FDP_OK;
 }
