@@ -593,7 +593,9 @@ __global__ void __launch_bounds__((STAGED && LN_BWD_PW) ? CW + 32 : CW) ln_bwd_k
     }
   }
 
-  pdl_trigger();   // the reduction kernel may be scheduled while this block finishes
+  // the reduction kernel may be scheduled while this block finishes (triggering at the top of the kernel
+  // instead, so that its blocks sit waiting beside the row loop, cost 1.3 us per call)
+  pdl_trigger();
   // cross-row-group sum, fixed order, one tensor at a time through the same shared buffer
   constexpr int CPG = TPR * NV * VEC;  // columns covered by a row group
   float* outp[2] = {dg_part, db_part};
