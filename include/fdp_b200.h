@@ -121,6 +121,13 @@ int fdp_set_sm_reserve(int n);
 /* Every compute entry point below opens an NVTX range named after itself (header-only NVTX: nothing
  * happens unless a timeline tool is attached), so a trace shows which call each kernel belongs to. */
 
+/* Stream semantics.  Every entry point only enqueues work on `stream` and returns.  The first kernel
+ * of a call is an ordinary launch: it starts after everything the caller enqueued before it.  Later
+ * kernels of the same call are programmatic dependent launches (they are scheduled while the
+ * previous kernel of the call drains and wait for it before touching memory); whatever the caller
+ * enqueues after the call starts, as always, when the call's last kernel has completed.  FDP_PDL=0
+ * in the environment makes every launch an ordinary one. */
+
 /* ---- instrumentation (no counterpart in the reference, which only wall-clocks whole functions in
  * RuntimeAutoTuner._measure_time, flashdp/core/utils.py:42-47) ---------------------------------------
  * fdp_launch_count: kernels launched by this library in this process so far.
