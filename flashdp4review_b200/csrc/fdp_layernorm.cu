@@ -421,7 +421,8 @@ constexpr bool LN_BWD_PW = FDP_LN_BWD_PRODUCER_WARP != 0;
 #ifndef FDP_LN_BWD_RING_KB
 #define FDP_LN_BWD_RING_KB 96
 #endif
-template <typename Tin, int VEC, int NV, int TPR, bool STAGED, int CW>
+// EXACT: d == TPR * NV * VEC, every thread's columns exist (no column checks, no zero fill).
+template <typename Tin, int VEC, int NV, int TPR, bool STAGED, int CW, bool EXACT = false>
 __global__ void __launch_bounds__((STAGED && LN_BWD_PW) ? CW + 32 : CW) ln_bwd_kernel(
     const Tin* __restrict__ dy, const Tin* __restrict__ x, const void* __restrict__ gamma,
     const float* __restrict__ mean, const float* __restrict__ rstd, Tin* __restrict__ dx,
@@ -447,10 +448,23 @@ __global__ void __launch_bounds__((STAGED && LN_BWD_PW) ? CW + 32 : CW) ln_bwd_k
   const uint32_t row_bytes = static_cast<uint32_t>(d) * sizeof(Tin);
   const uint32_t stage_bytes = 2 * RG * row_bytes;
 
+  // the RG rows of iteration `it` (x, then dy) into stage `st`; one thread
+  auto issue_stage = [&](int it, int st) {
+    const int rb = r0 + it * RG;
+    const int nrows = min(RG, r1 - rb);
+    const size_t goff = (static_cast<size_t>(b) * T + rb) * d;
+    mbar_expect_tx(smem_u32(&bars[st]), 2 * nrows * row_bytes);
+    bulk_load(smem_u32(ln_smem + st * stage_bytes), x + goff, nrows * row_bytes, smem_u32(&bars[st]));
+    bulk_load(smem_u32(ln_smem + st * stage_bytes + RG * row_bytes), dy + goff, nrows * row_bytes, smem_u32(&bars[st]));
+  };
   if (STAGED && threadIdx.x == 0) {
     for (int s = 0; s < n_stages; ++s) { mbar_init(smem_u32(&bars[s]), 1); mbar_init(smem_u32(&bars[LN_MAX_STAGES + s]), CW / 32); }
     abort_flag_s = 0;
     mbar_fence_init();
+    // the first stages are on their way before anything else of the block touches global memory:
+    // their latency overlaps the fetch of the row statistics and of gamma below
+    if (!LN_BWD_PW)
+      for (int it = 0; it < n_stages && it < n_iter; ++it) issue_stage(it, it);
   }
   // one parallel fetch of the chunk's mean / rstd, so no row waits on a global load of its own
   if (threadIdx.x < r1 - r0) {
@@ -465,20 +479,11 @@ __global__ void __launch_bounds__((STAGED && LN_BWD_PW) ? CW + 32 : CW) ln_bwd_k
 #pragma unroll
     for (int v = 0; v < VEC; ++v) {
       const int c = (j * TPR + t) * VEC + v;
-      gam[j * VEC + v] = (c < d) ? load_as(gamma, pdt, c) : 0.f;
+      gam[j * VEC + v] = (EXACT || c < d) ? load_as(gamma, pdt, c) : 0.f;
       accg[j * VEC + v] = 0.f; accb[j * VEC + v] = 0.f;
     }
   const float inv_d = 1.0f / d;
 
-  // the RG rows of iteration `it` (x, then dy) into stage `st`; one thread
-  auto issue_stage = [&](int it, int st) {
-    const int rb = r0 + it * RG;
-    const int nrows = min(RG, r1 - rb);
-    const size_t goff = (static_cast<size_t>(b) * T + rb) * d;
-    mbar_expect_tx(smem_u32(&bars[st]), 2 * nrows * row_bytes);
-    bulk_load(smem_u32(ln_smem + st * stage_bytes), x + goff, nrows * row_bytes, smem_u32(&bars[st]));
-    bulk_load(smem_u32(ln_smem + st * stage_bytes + RG * row_bytes), dy + goff, nrows * row_bytes, smem_u32(&bars[st]));
-  };
   if (STAGED && LN_BWD_PW && threadIdx.x >= CW) {
     // ---- producer warp ----
     if (threadIdx.x == CW) {
@@ -491,8 +496,6 @@ __global__ void __launch_bounds__((STAGED && LN_BWD_PW) ? CW + 32 : CW) ln_bwd_k
     }
   } else {
     // ---- row groups ----
-    if (STAGED && !LN_BWD_PW && threadIdx.x == 0)
-      for (int it = 0; it < n_stages && it < n_iter; ++it) issue_stage(it, it);
     int s = 0; uint32_t ph = 0;
     int prev_s = 0; uint32_t prev_ph = 0;
     for (int it = 0; it < n_iter; ++it) {
@@ -517,7 +520,7 @@ __global__ void __launch_bounds__((STAGED && LN_BWD_PW) ? CW + 32 : CW) ln_bwd_k
         for (int j = 0; j < NV; ++j) {
           const int c = (j * TPR + t) * VEC;
           if constexpr (VEC > 1) {
-            if (c < d) {
+            if (EXACT || c < d) {
               float ex[VEC], ed[VEC];
               unpack16<Tin>(*reinterpret_cast<const uint4*>(xr + c), ex);
               unpack16<Tin>(*reinterpret_cast<const uint4*>(dyr + c), ed);
@@ -576,7 +579,7 @@ __global__ void __launch_bounds__((STAGED && LN_BWD_PW) ? CW + 32 : CW) ln_bwd_k
 #pragma unroll
         for (int j = 0; j < NV; ++j) {
           const int c = (j * TPR + t) * VEC;
-          if (c >= d) continue;
+          if (!EXACT && c >= d) continue;
           if constexpr (VEC > 1) {
             float o[VEC];
 #pragma unroll
@@ -666,7 +669,7 @@ LnPlan ln_plan(int B, int T, int d, int dt) {
   return pl;
 }
 
-template <typename Tin, int VEC, int NV, int TPRV, bool STAGED, int CW>
+template <typename Tin, int VEC, int NV, int TPRV, bool STAGED, int CW, bool EXACT = false>
 static bool ln_bwd_launch_one(const void* dy, const void* x, const void* gamma, const float* mean,
                               const float* rstd, void* dx, float* dg_part, float* db_part, int B, int T,
                               int d, int pdt, const LnPlan& pl, int n_stages, cudaStream_t s) {
@@ -678,8 +681,8 @@ static bool ln_bwd_launch_one(const void* dy, const void* x, const void* gamma, 
   if (STAGED && n_stages * stage_bytes > smem) smem = n_stages * stage_bytes;
   static bool done[64];
   static std::mutex mu;
-  if (smem > 48 * 1024 && !smem_opt_in(done, mu, ln_bwd_kernel<Tin, VEC, NV, TPRV, STAGED, CW>, LN_SMEM_BUDGET)) return false;
-  ln_bwd_kernel<Tin, VEC, NV, TPRV, STAGED, CW><<<grid, (STAGED && LN_BWD_PW) ? CW + 32 : CW, smem, s>>>(
+  if (smem > 48 * 1024 && !smem_opt_in(done, mu, ln_bwd_kernel<Tin, VEC, NV, TPRV, STAGED, CW, EXACT>, LN_SMEM_BUDGET)) return false;
+  ln_bwd_kernel<Tin, VEC, NV, TPRV, STAGED, CW, EXACT><<<grid, (STAGED && LN_BWD_PW) ? CW + 32 : CW, smem, s>>>(
       (const Tin*)dy, (const Tin*)x, gamma, mean, rstd, (Tin*)dx, dg_part, db_part, T, d, pdt,
       pl.rows_per_block, pl.chunks, n_stages, sticky_status_slot());
   note_launch();
@@ -700,6 +703,10 @@ static void ln_bwd_launch(const void* dy, const void* x, const void* gamma, cons
   if (n_stages > n_iter) n_stages = n_iter;
   const bool staged = VEC > 1 && n_stages >= 2;
 #define FDP_LN_CASE(TPRV)                                                                                      \
+  if (staged && d == TPRV * NV * VEC &&                                                                        \
+      ln_bwd_launch_one<Tin, VEC, NV, TPRV, (VEC > 1), CW, (VEC > 1)>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, \
+                                                                      B, T, d, pdt, pl, n_stages, s))          \
+    return;                                                                                                    \
   if (staged && ln_bwd_launch_one<Tin, VEC, NV, TPRV, (VEC > 1), CW>(dy, x, gamma, mean, rstd, dx, dg_part, db_part, \
                                                                      B, T, d, pdt, pl, n_stages, s))                 \
     return;                                                                                                    \
