@@ -430,11 +430,11 @@ __global__ void __launch_bounds__((STAGED && LN_BWD_PW) ? CW + 32 : CW) ln_bwd_k
     int rows_per_block, int chunks, int n_stages, int* sticky) {
   constexpr int RG = CW / TPR;
   constexpr int NWG = TPR / 32;  // warps per row group
-  // dynamic shared memory: the ring (STAGED), reused at the end as [RG][TPR*NV*VEC] floats for the
+  // dynamic shared memory: the ring (STAGED), reused at the end as [2][RG][TPR*NV*VEC] floats for the
   // cross-group sum
   extern __shared__ __align__(128) unsigned char ln_smem[];
   float* sm = reinterpret_cast<float*>(ln_smem);
-  __shared__ float2 xch[RG][NWG > 1 ? NWG : 1];
+  __shared__ float2 xch[2][RG][NWG > 1 ? NWG : 1];   // row sums of the group's warps, alternating by iteration
   __shared__ __align__(8) unsigned long long bars[2 * LN_MAX_STAGES];
   __shared__ int abort_flag_s;
   __shared__ float s_mean[LN_MAX_ROWS_PER_BLOCK], s_rstd[LN_MAX_ROWS_PER_BLOCK];  // this chunk's row statistics
@@ -564,14 +564,16 @@ __global__ void __launch_bounds__((STAGED && LN_BWD_PW) ? CW + 32 : CW) ln_bwd_k
       if (!valid) { if (!ok) break; continue; }     // `valid` is the same for the whole row group
       s1 = warp_sum(s1); s2 = warp_sum(s2);
       if (NWG > 1) {
-        if (lane == 0) xch[rg][wig] = make_float2(s1, s2);
+        // One barrier per row: the slot alternates, and a thread writes slot (it+1)&1 only after
+        // this iteration's barrier, which every thread of the group reaches after its reads of that
+        // slot in iteration it-1.
+        if (lane == 0) xch[it & 1][rg][wig] = make_float2(s1, s2);
         // the barrier also carries the row group's verdict on the wait: either all of its warps go
         // on or all of them leave, so none is left waiting at a barrier the others never reach
         if (!bar_red_and(1 + rg, TPR, ok)) break;
         s1 = 0.f; s2 = 0.f;
 #pragma unroll
-        for (int w = 0; w < NWG; ++w) { s1 += xch[rg][w].x; s2 += xch[rg][w].y; }
-        asm volatile("bar.sync %0, %1;" ::"r"(1 + rg), "r"(TPR) : "memory");
+        for (int w = 0; w < NWG; ++w) { s1 += xch[it & 1][rg][w].x; s2 += xch[it & 1][rg][w].y; }
       }
       if (dx != nullptr) {
         const float a1 = -(s1 * inv_d) * rs, a2 = -(s2 * inv_d) * rs;
@@ -599,37 +601,41 @@ __global__ void __launch_bounds__((STAGED && LN_BWD_PW) ? CW + 32 : CW) ln_bwd_k
   // the reduction kernel may be scheduled while this block finishes (triggering at the top of the kernel
   // instead, so that its blocks sit waiting beside the row loop, cost 1.3 us per call)
   pdl_trigger();
-  // cross-row-group sum, fixed order, one tensor at a time through the same shared buffer
+  // cross-row-group sum, fixed order, both tensors in one pass: [2][RG][CPG] floats in the buffer
+  // the ring occupied (every consumer is past its last stage once it is past the barrier below)
   constexpr int CPG = TPR * NV * VEC;  // columns covered by a row group
-  float* outp[2] = {dg_part, db_part};
+  __syncthreads();
+  if (threadIdx.x < CW) {
 #pragma unroll
-  for (int which = 0; which < 2; ++which) {
-    __syncthreads();
-    if (threadIdx.x < CW) {
+    for (int which = 0; which < 2; ++which) {
+      float* dstp = sm + which * RG * CPG + rg * CPG;
+      const float* acc = which == 0 ? accg : accb;
 #pragma unroll
       for (int j = 0; j < NV; ++j) {
         if constexpr (VEC % 4 == 0) {
 #pragma unroll
           for (int v = 0; v < VEC; v += 4) {
-            const float* a = (which == 0 ? accg : accb) + j * VEC + v;
-            *reinterpret_cast<float4*>(&sm[rg * CPG + (j * TPR + t) * VEC + v]) = make_float4(a[0], a[1], a[2], a[3]);
+            const float* a = acc + j * VEC + v;
+            *reinterpret_cast<float4*>(&dstp[(j * TPR + t) * VEC + v]) = make_float4(a[0], a[1], a[2], a[3]);
           }
         } else {
 #pragma unroll
-          for (int v = 0; v < VEC; ++v)
-            sm[rg * CPG + (j * TPR + t) * VEC + v] = which == 0 ? accg[j * VEC + v] : accb[j * VEC + v];
+          for (int v = 0; v < VEC; ++v) dstp[(j * TPR + t) * VEC + v] = acc[j * VEC + v];
         }
       }
     }
-    __syncthreads();
-    float* dst = outp[which] + (static_cast<size_t>(b) * chunks + chunk) * d;
-    if (threadIdx.x < CW) {
-      for (int c = threadIdx.x; c < d; c += CW) {
-        float tot = 0.f;
+  }
+  __syncthreads();
+  if (threadIdx.x < CW) {
+    const size_t off = (static_cast<size_t>(b) * chunks + chunk) * d;
+    for (int c2 = threadIdx.x; c2 < 2 * d; c2 += CW) {
+      const int which = c2 >= d ? 1 : 0;
+      const int c = c2 - which * d;
+      const float* src = sm + which * RG * CPG + c;
+      float tot = 0.f;
 #pragma unroll
-        for (int g = 0; g < RG; ++g) tot += sm[g * CPG + c];
-        dst[c] = tot;
-      }
+      for (int g = 0; g < RG; ++g) tot += src[g * CPG];
+      (which == 0 ? dg_part : db_part)[off + c] = tot;
     }
   }
 }
@@ -675,7 +681,7 @@ static bool ln_bwd_launch_one(const void* dy, const void* x, const void* gamma, 
                               int d, int pdt, const LnPlan& pl, int n_stages, cudaStream_t s) {
   const unsigned grid = static_cast<unsigned>(static_cast<size_t>(B) * pl.chunks);
   constexpr int RG = CW / TPRV;
-  const size_t reduce_bytes = static_cast<size_t>(CW) * NV * VEC * sizeof(float);
+  const size_t reduce_bytes = static_cast<size_t>(2) * CW * NV * VEC * sizeof(float);   // both tensors at once
   const size_t stage_bytes = static_cast<size_t>(2) * RG * d * sizeof(Tin);
   size_t smem = reduce_bytes;
   if (STAGED && n_stages * stage_bytes > smem) smem = n_stages * stage_bytes;
