@@ -365,7 +365,7 @@ def run_native(args, wl):
         # the all-reduce of this layer's gradient runs beside the input-gradient GEMM, which leaves a few
         # SMs free for it; the norm pass and the clipped-sum GEMM above had the whole GPU
         work = dist.all_reduce(dW, op=dist.ReduceOp.SUM, async_op=True)
-        with fdp.sm_reservation():
+        with fdp.sm_reservation(args.reserve_sms):
             dX = ops.linear_input_grad(Gd, W, "out_in")
         work.wait()
         return dW, dX
@@ -997,6 +997,8 @@ def main():
     ap.add_argument("--no-cpu-full", dest="cpu_full", action="store_false")
     ap.add_argument("--no-gpt2", action="store_true", help="default workload: skip the GPT-2-medium leg")
     ap.add_argument("--no-check", action="store_true", help="skip the untimed N-rank == single-rank check")
+    ap.add_argument("--reserve-sms", type=int, default=12,
+                    help="N > 1: SMs the input-gradient GEMM leaves to the all-reduce that runs beside it")
     ap.add_argument("--no-ref-gpu", action="store_true",
                     help="skip the context leg that runs the installed reference package on the same GPU")
     args = ap.parse_args()
