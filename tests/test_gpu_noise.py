@@ -125,7 +125,7 @@ print("WORST", worst)
 """
 
 
-@pytest.mark.parametrize("env", [{"FDP_TC_CTAS": "1"}, {"FDP_TC_RESERVE_SMS": "20"}])
+@pytest.mark.parametrize("env", [{"FDP_TC_CTAS": "1"}, {"FDP_TC_RESERVE_SMS": "20"}, {"FDP_PDL": "0"}])
 def test_noise_stream_with_single_cta_tiles_and_a_reduced_grid(env):
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
     r = subprocess.run([sys.executable, "-c", _CHILD % (root, os.path.join(root, "tests"))],

@@ -124,7 +124,8 @@ print("WORST", worst)
 
 
 @pytest.mark.parametrize("env", [{"FDP_TC_CTAS": "1"}, {"FDP_WGRAD_PRESCALE": "1"},
-                                 {"FDP_TC_CTAS": "1", "FDP_WGRAD_PRESCALE": "1"}, {"FDP_TC_RESERVE_SMS": "16"}])
+                                 {"FDP_TC_CTAS": "1", "FDP_WGRAD_PRESCALE": "1"}, {"FDP_TC_RESERVE_SMS": "16"},
+                                 {"FDP_PDL": "0"}])
 def test_kernel_variants_selected_by_environment(env):
     """Single-CTA tiles, the pre-scale path and a reduced grid are chosen once per process, so each
     is exercised in a child process and checked against the oracle at the bf16 tolerance."""
@@ -135,6 +136,48 @@ def test_kernel_variants_selected_by_environment(env):
     assert r.returncode == 0, r.stderr[-2000:]
     worst = float(r.stdout.strip().split("WORST")[-1])
     assert worst < 1e-2, worst
+
+
+_DIGEST_CHILD = r"""
+import sys, hashlib, torch
+sys.path.insert(0, %r)
+from oracle import dp_oracle as O
+from flashdp4review_b200.core import ops
+dev = torch.device("cuda:0")
+h = hashlib.sha256()
+ns = ops.NoiseSpec(0.5, 7, 3, 4, 9)
+for shape in [(4, 256, 512, 384), (8, 1024, 1024, 768), (3, 320, 264, 520), (300, 1, 136, 264), (3, 50, 72, 40)]:
+    B, T, n_in, n_out = shape
+    X, G, W = O.make_linear_inputs(B, T, n_in, n_out, 1e-3, seed=sum(shape), dtype=torch.bfloat16)
+    X, G = X.to(dev), G.to(dev)
+    for _ in range(3):      # back to back: the chains of consecutive calls overlap if anything can
+        dW, norms, _ = ops.dp_linear_weight_grad(X, G, 1e-2, 1.0, noise=ns, return_norms=True, out_dtype=torch.float32)
+        db = ops.dp_bias_grad(G, 1e-2, 1.0, noise=ns)
+        h.update(dW.cpu().numpy().tobytes()); h.update(norms.cpu().numpy().tobytes()); h.update(db.float().cpu().numpy().tobytes())
+    gamma = torch.linspace(0.5, 1.5, n_in, device=dev); beta = torch.zeros(n_in, device=dev)
+    y, buf, _ = ops.layernorm_fwd_fused(X, gamma, beta, 1e-5)
+    for _ in range(3):
+        dx, dg, dbeta = ops.dp_layernorm_backward(X, X, gamma, buf["mean"], buf["rstd"], 1e-2, 1.0, noise=ns)
+        for t in (dx, dg, dbeta):
+            h.update(t.float().cpu().numpy().tobytes())
+torch.cuda.synchronize()
+print("DIGEST", h.hexdigest())
+"""
+
+
+def test_dependent_launches_do_not_change_a_bit():
+    """The second and later kernels of a call are programmatic dependent launches unless FDP_PDL=0.
+    Weight gradient (tensor-core, short-sequence and generic paths), bias gradient and LayerNorm
+    backward, three calls in a row each, noise on: the outputs hash the same either way."""
+    import os, subprocess, sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    digests = []
+    for env in ({"FDP_PDL": "1"}, {"FDP_PDL": "0"}):
+        r = subprocess.run([sys.executable, "-c", _DIGEST_CHILD % root], env={**os.environ, **env},
+                           capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stderr[-2000:]
+        digests.append(r.stdout.strip().split("DIGEST")[-1].strip())
+    assert digests[0] == digests[1] and len(digests[0]) == 64
 
 
 # short sequences (T < 64): norms through the small Gram kernel, clipped sum as one GEMM over B*T rows
