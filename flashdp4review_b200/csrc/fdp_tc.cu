@@ -62,6 +62,8 @@ struct TcArgs {
   int* status;          // status word of the call (workspace)
   int zero_status;      // this launch is the first of its call: its first thread clears the status word
   int dependent;        // host side: launch as a programmatic dependent of the kernel before it in the stream
+  int sub_stages;       // EPI_STORE_SCALED: K stages per accumulator hand-off (<= seg_stages; chains of fp32 tensor mode)
+  int norm_mode;        // EPI_STORE_SCALED: no store; sum of squares of the unit's accumulated tile -> partials
   int* sticky;          // this device's slot of the host-visible status array, or null
   uint32_t idesc;
   // split-K (store epilogues): work units [0, units_full) are whole tiles; each later tile is cut into
@@ -380,8 +382,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     slot = v;
   };
   // EPI_STORE_SCALED: end of the sample segment that contains stage ks, cut at the unit's end
+  // (sub_stages divides seg_stages: a hand-off never spans two samples.  With fp32 inputs it is a few
+  // stages only: the tensor cores add into the TMEM accumulator by truncation, about one unit in the
+  // last place per K = 16 step and all of one sign, so a long chain drifts; short chains summed in
+  // registers with round-to-nearest do not.)
   auto segment_end = [&](int ks, int ks1) {
-    const int e = (ks / args.seg_stages + 1) * args.seg_stages;
+    const int e = (ks / args.sub_stages + 1) * args.sub_stages;
     return e < ks1 ? e : ks1;
   };
 
@@ -588,7 +594,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
         // parts stay noise-free (the fix-up kernel adds the noise once per tile).
         const bool pre_noise = slot < 0 && args.nk.std != 0.f && m < args.M;
         const uint64_t g0 = (static_cast<uint64_t>(m) * args.ld_out + n0 + chalf * 128) >> 2;
-        const int nseg = (ks1 - 1) / args.seg_stages - ks0 / args.seg_stages + 1;
+        const int nseg = (ks1 - 1) / args.sub_stages - ks0 / args.sub_stages + 1;
         int ng = 0, seg = 0;
         for (int ks = ks0; ks < ks1 && ok; ks = segment_end(ks, ks1), ++it) {
           const int acc = it % NUM_ACC;
@@ -597,7 +603,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tc_fence_after();
           const int sample = ks / args.seg_stages;
           // the divisor goes into the factor, so the noise is added as it is drawn
-          const float cbs = (args.norm_partials != nullptr ? sfac[sample] : __ldg(args.factors + sample)) * args.scale;
+          const float cbs = args.norm_mode ? 1.0f
+                          : (args.norm_partials != nullptr ? sfac[sample] : __ldg(args.factors + sample)) * args.scale;
           const uint32_t tb = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + chalf * 128;
 #pragma unroll
           for (int c4 = 0; c4 < 4; ++c4) {
@@ -624,6 +631,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
         if (!ok) break;
+        if (args.norm_mode) {
+          // the unit is one sample's product tile: its squares, without the rows and columns past the
+          // matrix (with split operands a tile that overhangs reads the other half's columns, not zeros)
+          float part = 0.f;
+          const int nb = n0 + chalf * 128;
+          if (m < args.M) {
+#pragma unroll
+            for (int i = 0; i < 128; ++i) part = fmaf((nb + i < args.N) ? accr[i] : 0.f, accr[i], part);
+          }
+          part = warp_sum(part);
+          if (lane == 0) args.partials[(static_cast<size_t>(tile) * CTAS + cta_rank) * EPI_WARPS + ew] = part;
+          continue;
+        }
         if (slot < 0) {
 #pragma unroll
           for (int c4 = 0; c4 < 4; ++c4) {
@@ -993,6 +1013,21 @@ int tc_wait_selftest(int* status, long long limit_cycles, cudaStream_t s) {
   return cudaPeekAtLastError() == cudaSuccess ? FDP_OK : (cudaGetLastError(), FDP_ERR_LAUNCH);
 }
 
+// K stages per accumulator hand-off for fp32 inputs (three bf16 products): the largest divisor of a
+// sample's stage count that is at most FDP_TC_CHAIN_STAGES (default 8: 32 steps of K = 16 per chain).
+// B=8, T=1024, 4096x4096, against float64: norms 1.1e-7 / 2.5e-7 / 4.4e-7 / 5e-6 and 2.15 / 1.48 /
+// 1.42 / 1.37 ms per call with 2 / 4 / 8 / all stages per chain (1e-5 at T=2048 with one chain).
+static int chain_stages(int seg_stages) {
+  static const int cap = [] {
+    const char* e = getenv("FDP_TC_CHAIN_STAGES");
+    const int v = e ? atoi(e) : 8;
+    return v < 1 ? 1 : v;
+  }();
+  int c = cap < seg_stages ? cap : seg_stages;
+  while (seg_stages % c != 0) --c;
+  return c;
+}
+
 // The tensor-core path needs 16-bit inputs, row pitches that are multiples of 16 bytes, and
 // matrices large enough that the 128x256 tile is not mostly padding.
 TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo) {
@@ -1002,12 +1037,12 @@ TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo) {
   const bool fp32_tensor = (norm_algo & FDP_FP32_TENSOR) != 0;
   norm_algo &= FDP_NORM_MASK;
   if (dt == FDP_F32) {
-    // fp32 on the tensor cores as three bf16 products (hi*hi + hi*lo + lo*hi, fp32 accumulation), on
-    // request only: the tensor cores add into their fp32 accumulators by truncation, a one-sided error
-    // of about 2^-24 per K=16 step that a few hundred steps carry past the fp32 tolerance of 1e-5
-    // (measured 3e-5 on the norms at 4096 columns).  Needs whole 64-column K stages per half (the Gram
-    // pass contracts over the columns), samples made of whole 64-row stages, and the per-sample
-    // epilogue (a pre-scaled copy would round c_b * G to bf16 again).
+    // fp32 on the tensor cores as three bf16 products (hi*hi + hi*lo + lo*hi, fp32 accumulation), when
+    // the caller asks for it (FDP_FP32_TENSOR).  The tensor cores add into their fp32 accumulators by
+    // truncation, a one-sided error of about 2^-24 per K=16 step, so no accumulator runs for more than
+    // a few K stages: it is handed to the epilogue warps, which add it to registers with
+    // round-to-nearest (chain_stages).  Needs whole 64-column K stages per half, samples made of whole
+    // 64-row stages, and the per-sample epilogue (a pre-scaled copy would round c_b * G to bf16 again).
     if (!fp32_tensor || n_in % BK != 0 || n_out % BK != 0 || n_in < 128 || n_out < 128 || T % BK != 0 || T < 2 * BK) return p;
     p.split3 = true;
     p.split3_g_bytes = align256(static_cast<size_t>(B) * T * n_out * 4);
@@ -1025,9 +1060,8 @@ TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo) {
     p.ws_bytes = p.split_bytes + align256(static_cast<size_t>(B) * T * n_out * 2);
     return p;
   }
-  // direct: a K stage must not run into the next sample's rows; with split operands the tile must also
-  // stay inside its half of the columns (the sum-of-squares epilogue does not mask columns)
-  const bool direct_ok = (T % BK == 0) && (!p.split3 || (n_out % BM == 0 && n_in % BN == 0));
+  // direct: a K stage must not run into the next sample's rows
+  const bool direct_ok = (T % BK == 0);
   // Cost of the two norm algorithms in K stages on the critical path: both kernels deal equal work
   // units (128x256 tiles) round-robin to one CTA per SM, so a pass takes
   // ceil(units / SMs) * (stages per unit + a fixed cost per unit of about four stages).  The SM
@@ -1042,6 +1076,10 @@ TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo) {
   int algo = norm_algo;
   if (algo == FDP_NORM_AUTO) algo = (direct_ok && direct <= gram) ? FDP_NORM_DIRECT : FDP_NORM_GRAM;
   if (algo == FDP_NORM_DIRECT && !direct_ok) algo = FDP_NORM_GRAM;
+  // split operands: always the product form, accumulated in short chains (tc_norms); the Gram form
+  // needs both T x T tiles complete in TMEM before its epilogue can multiply them, i.e. one chain of
+  // 3 * (in + out) / 16 truncating additions
+  if (p.split3) algo = FDP_NORM_DIRECT;
   p.ok = true;
   p.algo = algo;
   // clip factors applied in the GEMM epilogue (no scaled copy of G) when every 64-row K stage lies
@@ -1051,6 +1089,10 @@ TcPlan tc_plan(int B, int T, int n_in, int n_out, int dt, int norm_algo) {
   p.scaled_epilogue = p.split3 || (!force_prescale && (T % BK == 0) && T >= 256);
   // one partial per work unit and epilogue warp
   p.nparts = 4 * ((algo == FDP_NORM_DIRECT) ? ceil_div(n_out, BM) * ceil_div(n_in, BN) : gram_tiles(T));
+  if (p.split3) {   // the chained norm pass: tiles of the clipped-sum GEMM, eight epilogue warps per CTA
+    const int ctas = ctas_per_tile();
+    p.nparts = ceil_div(n_out, BM * ctas) * ceil_div(n_in, BN) * ctas * epi_warps_for(EPI_STORE_SCALED);
+  }
   // the parked accumulators of the split-K tail, then (pre-scale path only) the c_b-scaled copy of G
   p.split_bytes = split_ws_bytes();
   p.ws_bytes = p.split_bytes + (p.scaled_epilogue ? 0 : align256(static_cast<size_t>(B) * T * n_out * 2)) +
@@ -1078,6 +1120,24 @@ int tc_norms(const void* G, const void* X, float* partials, int* dev_status, int
   args.batch = B; args.batch_rows = T; args.partials = partials; args.status = dev_status; args.T = T;
   args.zero_status = 1;      // the norm pass is the first launch of a weight-gradient call
   args.terms = terms;
+  if (pl.split3) {
+    // fp32 inputs: the per-sample products G_b^T X_b themselves, on the tiles and CTA pairs of the
+    // clipped-sum GEMM, handed to the epilogue every few K stages and summed there in registers; a
+    // unit is (sample, tile) and ends with the sum of its squares instead of a store
+    if (!make_map(&a, G, rows, wo, 64, BK, dt) || !make_map(&b, X, rows, wi, 64, BK, dt)) return FDP_ERR_LAUNCH;
+    const int ctas = ctas_per_tile();
+    args.M = n_out; args.N = n_in; args.ld_out = n_in;
+    args.tiles_m = ceil_div(n_out, BM * ctas); args.tiles_n = ceil_div(n_in, BN);
+    args.tiles_per_batch = args.tiles_m * args.tiles_n;
+    args.term_stages = T / BK;
+    args.k_stages = terms * (T / BK);
+    args.plane_a = n_out; args.plane_b = n_in;
+    args.idesc = make_idesc(dt, true, true, ctas);
+    args.segs = 1; args.seg_stages = args.k_stages; args.sub_stages = chain_stages(args.seg_stages);
+    args.norm_mode = 1; args.scale = 1.0f; args.nk = NoiseKey{};
+    return ctas == 2 ? launch<true, true, EPI_STORE_SCALED, 2>(a, b, a, b, args, s)
+                     : launch<true, true, EPI_STORE_SCALED, 1>(a, b, a, b, args, s);
+  }
   if (pl.algo == FDP_NORM_DIRECT) {
     if (!make_map(&a, G, rows, wo, 64, BK, dt) || !make_map(&b, X, rows, wi, 64, BK, dt)) return FDP_ERR_LAUNCH;
     args.M = n_out; args.N = n_in;
@@ -1142,6 +1202,7 @@ int tc_clipped_wgrad(const void* Gs, const void* X, const TcFactorSource* fs, fl
   args.idesc = make_idesc(dt, true, true, ctas);
   if (scaled) {
     args.segs = B; args.seg_stages = terms * (T / BK);
+    args.sub_stages = terms == 3 ? chain_stages(args.seg_stages) : args.seg_stages;
     args.factors = fs->factors;
     if (fs->factors == nullptr) {
       if (!tc_fused_factors_ok(B) || fs->norm_partials == nullptr) return FDP_ERR_ARG;

@@ -19,12 +19,12 @@ def rand_case(B, T, n_in, n_out, g_scale, seed, dtype):
     return X, G, W
 
 
-def check_wgrad(X, G, C, clamp, dtype, layout="out_in", norm_algo="auto", out_dtype=None, tol=None):
+def check_wgrad(X, G, C, clamp, dtype, layout="out_in", norm_algo="auto", out_dtype=None, tol=None, fp32_tensor=None):
     from flashdp4review_b200.core import ops
     tol = tol or TOL[dtype]
     dW, norms, factors = ops.dp_linear_weight_grad(
         X.to(dev()), G.to(dev()), C, clamp, layout=layout, norm_algo=norm_algo,
-        out_dtype=out_dtype, return_norms=True)
+        out_dtype=out_dtype, return_norms=True, fp32_tensor=fp32_tensor)
     torch.cuda.synchronize()
     want, wn = O.linear_weight_grad(G, X, C, clamp, layout=layout)
     got = dW.float().cpu().numpy()

@@ -74,10 +74,10 @@ def test_full_size_whole_tensor_against_float64(case, sigma):
                                    (3, 320, 1024, 576, "in_out"), (2, 2048, 1024, 3072, "in_out")],
                          ids=lambda s: "x".join(map(str, s)))
 def test_fp32_inputs_on_the_tensor_cores(shape):
-    """`fp32_tensor=True`: fp32 G and X with 64-aligned shapes run as three bf16 products (hi*hi + hi*lo
-    + lo*hi) on the tensor cores.  Norms and clipped mean against float64 at 1e-4 (the tensor cores'
-    truncating accumulation keeps it from the exact path's 1e-5: observed 3e-5 at 4096 columns), both
-    norm algorithms; the default exact path on the same inputs holds 1e-5."""
+    """fp32 G and X with 64-aligned shapes run as three bf16 products (hi*hi + hi*lo + lo*hi) on the
+    tensor cores, their accumulators drained into registers every few K stages.  Norms and clipped mean
+    against float64 at the fp32 tolerance 1e-5, as the default (`fp32_tensor=None`) and on request; the
+    fp32-FMA kernels (`fp32_tensor=False`) on the same inputs hold it too."""
     from flashdp4review_b200.core import ops
     B, T, n_in, n_out, layout = shape
     gen = torch.Generator(device="cuda").manual_seed(3)
@@ -87,15 +87,15 @@ def test_fp32_inputs_on_the_tensor_cores(shape):
     G[B - 1] *= 1e-5
     C = 1.0
     want, wn = _fp64_reference(G, X, C, 1.0, layout)
-    for algo in ("auto", "gram", "direct"):
+    for algo, mode in (("auto", None), ("gram", True), ("direct", True)):
         dW, norms, factors = ops.dp_linear_weight_grad(X, G, C, 1.0, layout=layout, norm_algo=algo, return_norms=True,
-                                                       fp32_tensor=True)
+                                                       fp32_tensor=mode)
         assert dW.dtype == torch.float32
         err_n = float(((norms.double() - wn).abs() / wn).max())
         err = float((dW.double() - want).abs().max() / want.abs().max())
-        assert err_n < 1e-4 and err < 1e-4, (algo, err_n, err)
-    if B * T * n_in * n_out <= 2 ** 32:                       # the exact kernels: fp32 tolerance
-        dW, norms, _ = ops.dp_linear_weight_grad(X, G, C, 1.0, layout=layout, return_norms=True)
+        assert err_n < 1e-5 and err < 1e-5, (algo, err_n, err)
+    if B * T * n_in * n_out <= 2 ** 32:                       # the fp32-FMA kernels: same tolerance
+        dW, norms, _ = ops.dp_linear_weight_grad(X, G, C, 1.0, layout=layout, return_norms=True, fp32_tensor=False)
         assert float(((norms.double() - wn).abs() / wn).max()) < 1e-5
         assert float((dW.double() - want).abs().max() / want.abs().max()) < 1e-5
     again = ops.dp_linear_weight_grad(X, G, C, 1.0, layout=layout, fp32_tensor=True)
@@ -103,7 +103,7 @@ def test_fp32_inputs_on_the_tensor_cores(shape):
     # noise on top: the host stream, subtracted, leaves the same gradient
     noisy = ops.dp_linear_weight_grad(X, G, C, 1.0, layout=layout, noise=ops.NoiseSpec(0.01, 5, 2, 0, 9), fp32_tensor=True)
     z = O.gaussian_noise(noisy.numel(), 0.01, 5, 2, 9).reshape(noisy.shape)
-    assert float((noisy.double() - torch.from_numpy(z).to(noisy.device) - want).abs().max() / want.abs().max()) < 2e-4
+    assert float((noisy.double() - torch.from_numpy(z).to(noisy.device) - want).abs().max() / want.abs().max()) < 1e-4
 
 
 @pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
