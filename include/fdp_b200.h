@@ -62,11 +62,15 @@ enum fdp_norm_algo {
   FDP_NORM_GRAM = 2,   /* sum_{t,s} (G_b G_b^T)_{ts} (X_b X_b^T)_{ts} */
   FDP_NORM_MASK = 15,
   /* flag, OR-ed into the norm_algo argument of fdp_linear_wgrad and of its workspace query: fp32 inputs
-   * with 64-aligned shapes (n_in, n_out and T multiples of 64, T >= 128) run on the tensor cores as
-   * three bf16 products (x = hi + lo: hi*hi + hi*lo + lo*hi) instead of fp32 FMAs -- 10 to 25 times
-   * faster, but the tensor cores' truncating fp32 accumulation leaves norms and gradients within about
-   * 1e-4 of the exact result, not 1e-5.  Without the flag fp32 inputs keep exact fp32 arithmetic, the
-   * reference's own (flashdp/core/utils.py:9-12: fp32 accumulates in fp32). */
+   * with 64-aligned shapes (n_in, n_out and T multiples of 64, at least 128) run on the tensor cores as
+   * three bf16 products (x = hi + lo: hi*hi + hi*lo + lo*hi) instead of fp32 FMAs, about six times
+   * faster.  The tensor cores add into their fp32 accumulators by truncation, so no accumulator runs
+   * longer than a few K stages before it is added, with round-to-nearest, to registers; norms and
+   * gradients stay within 1e-5 of float64 like the FMA kernels (the norms then always use the product
+   * form: FDP_NORM_GRAM is ignored).  The workspace grows by the size of the inputs (their bf16 halves).
+   * Without the flag fp32 inputs keep fp32 FMA arithmetic, the reference's own
+   * (flashdp/core/utils.py:9-12: fp32 accumulates in fp32).  The Python layer sets the flag by default
+   * (runtime.set_fp32_mode). */
   FDP_FP32_TENSOR = 16
 };
 
