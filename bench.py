@@ -39,6 +39,7 @@ WORKLOADS = {
     "linear_bf16_b8_t1024_1024x3072": (8, 1024, 1024, 3072, "bf16", 1e-3),     # a GPT-2-medium c_attn call
     "linear_bf16_b4_t2048_4096x4096": (4, 2048, 4096, 4096, "bf16", 1e-3),     # a Llama-2-7B attention projection
     "linear_fp32_b4_t128_768x768": (4, 128, 768, 768, "f32", 1e-2),
+    "linear_fp32_b8_t1024_4096x4096": (8, 1024, 4096, 4096, "f32", 1e-2),      # fp32 weights at the config-2 layer size
     "small_bf16_b4_t256_512x512": (4, 256, 512, 512, "bf16", 1e-3),
 }
 DEFAULT_WORKLOAD = "linear_bf16_b32_t1024_4096x4096"
@@ -502,7 +503,9 @@ def run_native(args, wl):
             achieved = gemm_flops / (phases["clipped_gemm_ms"] * 1e-3) / 1e12
             # against the BURST cuBLAS figure: the phase events are read right after five back-to-back
             # steps that follow the mostly idle end-to-end leg, a burst-like window
-            roof = {"kernel": "clipped-sum GEMM (tcgen05)" if dtn != "f32" else "clipped-sum GEMM (fp32 FMA)",
+            roof = {"kernel": "clipped-sum GEMM (tcgen05)" if dtn != "f32" else
+                    ("clipped-sum GEMM (tcgen05, three bf16 products)" if fdp.fp32_mode() == "tensor"
+                     else "clipped-sum GEMM (fp32 FMA)"),
                     "bound": "tensor", "achieved": achieved, "peak": pk["bf16"], "unit": "TFLOP/s",
                     "frac": achieved / pk["bf16"], "frac_of_sustained_peak": achieved / pk["bf16_sustained"],
                     "frac_of_nominal": achieved / NOMINAL_BF16_TFLOPS,
