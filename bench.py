@@ -355,6 +355,15 @@ def run_native(args, wl):
     X, G, W = Xh.to(dev), Gh.to(dev), Wh.to(dev)
     step_no = [0]
 
+    # input gradient: this library's GEMM for 16-bit layers; fp32 layers keep the package default for
+    # that product, cuBLAS through torch, as the reference does (flashdp/layers/linear.py:62-64)
+    if dtn == "f32":
+        def input_grad(Gd):
+            return (Gd.reshape(-1, n_out) @ W).view(B, T, n_in)
+    else:
+        def input_grad(Gd):
+            return ops.linear_input_grad(Gd, W, "out_in")
+
     def step(Xd, Gd):
         step_no[0] += 1
         noise = ops.NoiseSpec(std=ops.noise_std(args.sigma, B * world), seed=1234, param_id=1, step=step_no[0],
@@ -362,12 +371,12 @@ def run_native(args, wl):
         dW = ops.dp_linear_weight_grad(Xd, Gd, 1.0, 1.0, batch_divisor=B * world, noise=noise,
                                        out_dtype=torch.float32, norm_algo=args.norm_algo)
         if world == 1:
-            return dW, ops.linear_input_grad(Gd, W, "out_in")
+            return dW, input_grad(Gd)
         # the all-reduce of this layer's gradient runs beside the input-gradient GEMM, which leaves a few
         # SMs free for it; the norm pass and the clipped-sum GEMM above had the whole GPU
         work = dist.all_reduce(dW, op=dist.ReduceOp.SUM, async_op=True)
         with fdp.sm_reservation(args.reserve_sms):
-            dX = ops.linear_input_grad(Gd, W, "out_in")
+            dX = input_grad(Gd)
         work.wait()
         return dW, dX
 
