@@ -971,15 +971,25 @@ int ctas_per_tile() { return forced_ctas() == 1 ? 1 : 2; }
 
 // K-split of the tail wave: `rem` tiles left after the full waves (all of them when there are fewer
 // tiles than workers) are cut into s parts of equal K-stage count, so that the last round keeps more
-// SMs busy; cost in tile-times = ceil(rem*s/workers)/s plus a fixed cost per extra part for parking
-// and re-reading the accumulators.  At most 2 * workers parked parts (workers <= MAX_SMS / CTAS).
+// SMs busy; cost in tile-times = ceil(rem*s/workers)/s plus the cost of parking and re-reading the
+// accumulators.  At most 2 * workers parked parts (workers <= MAX_SMS / CTAS).
+// That cost, in tile-times: 0.05 for the fix-up launch plus 0.15 per parked part and worker (the
+// parts are written and read again).  With 48 pair tiles of 128 K stages for 74 pairs (a GPT-2
+// layer, B=8, T=1024) three parts of 43 stages in two rounds measured no faster than the tiles
+// unsplit (100.8 against 98.6 us per call: parking, the second round's hand-over and the fix-up
+// launch eat the 42 stages saved), while 16 tiles in four parts (52 against 82 us) and the tails of
+// the larger layers do pay.
 int plan_tail_split(int total_tiles, int k_stages, int workers) {
   const int rem = total_tiles <= workers ? total_tiles : total_tiles % workers;
   if (rem == 0 || k_stages < 32) return 1;
+  // FDP_TC_SPLIT=n forces the number of parts (measurements), within the same limits
+  static const int forced = [] { const char* e = getenv("FDP_TC_SPLIT"); return e ? atoi(e) : 0; }();
+  if (forced >= 1) return (rem * forced > 2 * workers || k_stages / forced < 8) ? 1 : forced;
   int best_s = 1; double best = 1.0;
   for (int sp = 2; sp <= 16; ++sp) {
     if (rem * sp > 2 * workers || k_stages / sp < 8) break;
-    const double cost = static_cast<double>((rem * sp + workers - 1) / workers) / sp + 0.02 * sp;
+    const double cost = static_cast<double>((rem * sp + workers - 1) / workers) / sp +
+                        0.15 * (static_cast<double>(rem) * sp / workers) + 0.05;
     if (cost < best - 0.03) { best = cost; best_s = sp; }
   }
   return best_s;
