@@ -9,8 +9,9 @@ from .layers.transformers_conv1d import DPConv1D
 from .api.wrap_model import wrap_with_flashdp_layers, dp_supported_modules
 from .runtime import (manual_seed, set_data_parallel, set_input_grad_impl, set_accumulation, accumulate,
                       noise_state, set_noise_state, check_device_status, clear_device_status, sm_reservation,
-                      set_fp32_mode, fp32_mode)
+                      set_fp32_mode, fp32_mode, use_device_noise_step, advance_noise_step)
 
 __all__ = ["DPLinear", "DPLayerNorm", "DPConv1D", "wrap_with_flashdp_layers", "dp_supported_modules",
            "manual_seed", "set_data_parallel", "set_input_grad_impl", "set_accumulation", "accumulate",
-           "noise_state", "set_noise_state", "check_device_status", "clear_device_status", "sm_reservation", "set_fp32_mode", "fp32_mode"]
+           "noise_state", "set_noise_state", "check_device_status", "clear_device_status", "sm_reservation", "set_fp32_mode", "fp32_mode",
+           "use_device_noise_step", "advance_noise_step"]

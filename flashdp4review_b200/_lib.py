@@ -9,7 +9,7 @@ PKG = os.path.dirname(os.path.abspath(__file__))
 # FDP_B200_LIB points at another build of the same ABI (used to compare builds on one GPU)
 LIB_PATH = os.environ.get("FDP_B200_LIB") or os.path.join(PKG, "libfdp_b200.so")
 
-ABI_VERSION = 2
+ABI_VERSION = 3
 FDP_OK = 0
 FDP_ERR_ARG, FDP_ERR_DTYPE, FDP_ERR_SHAPE, FDP_ERR_ALIGN = -1, -2, -3, -4
 FDP_ERR_WORKSPACE, FDP_ERR_ARCH, FDP_ERR_LAUNCH, FDP_ERR_TIMEOUT = -5, -6, -7, -8
@@ -29,7 +29,7 @@ class DPParams(ctypes.Structure):
                 ("batch_divisor", ctypes.c_int32), ("seed", ctypes.c_uint64),
                 ("param_id", ctypes.c_uint32), ("param_id2", ctypes.c_uint32),
                 ("step", ctypes.c_uint32), ("noise_rank", ctypes.c_int32),
-                ("noise_world", ctypes.c_int32)]
+                ("noise_world", ctypes.c_int32), ("step_device", c_void_p)]
 
 
 # name -> (restype, argtypes); every function include/fdp_b200.h declares

@@ -69,6 +69,7 @@ class NoiseSpec:
     step: int = 0
     rank: int = 0
     world: int = 1
+    step_device: object = None    # a one-element int32 CUDA tensor the kernels add to `step` when they run
 
 
 def _params(C, clamp_value, batch_divisor, noise):
@@ -76,7 +77,8 @@ def _params(C, clamp_value, batch_divisor, noise):
     return DPParams(float(C), float(clamp_value), float(noise.std), int(batch_divisor or 0),
                     int(noise.seed) & (2 ** 64 - 1), int(noise.param_id) & 0xFFFFFFFF,
                     int(noise.param_id2) & 0xFFFFFFFF, int(noise.step) & 0xFFFFFFFF,
-                    int(noise.rank), int(noise.world))
+                    int(noise.rank), int(noise.world),
+                    noise.step_device.data_ptr() if noise.step_device is not None else None)
 
 
 # ------------------------------------------------------------------------------------------------

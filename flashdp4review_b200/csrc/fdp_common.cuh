@@ -95,6 +95,7 @@ struct NoiseKey {
   uint32_t k0, k1, param_id, step;
   float std;
   int rank, world;  // element group g is drawn by the rank with g % world == rank
+  const uint32_t* step_dev;  // null, or a device counter added to `step` when the kernel runs
 };
 
 __device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
@@ -126,7 +127,8 @@ __device__ __forceinline__ void noise_group(const NoiseKey& nk, uint64_t g, floa
     return;
   }
   uint32_t r[4];
-  philox4x32_10(static_cast<uint32_t>(g), static_cast<uint32_t>(g >> 32), nk.param_id, nk.step,
+  const uint32_t step = nk.step_dev != nullptr ? nk.step + __ldg(nk.step_dev) : nk.step;
+  philox4x32_10(static_cast<uint32_t>(g), static_cast<uint32_t>(g >> 32), nk.param_id, step,
                 nk.k0, nk.k1, r);
   box_muller(r[0], r[1], z[0], z[1]);
   box_muller(r[2], r[3], z[2], z[3]);
@@ -148,6 +150,7 @@ inline NoiseKey make_noise_key(const fdp_dp_params* p, uint32_t param_id) {
   nk.std = p->noise_std;
   nk.world = p->noise_world > 1 ? p->noise_world : 1;
   nk.rank = p->noise_world > 1 ? p->noise_rank : 0;
+  nk.step_dev = p->step_device;
   return nk;
 }
 

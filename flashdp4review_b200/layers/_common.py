@@ -39,7 +39,8 @@ def dp_scalars(local_batch, noise_multiplier, param_id, step, param_id2=0):
     # under gradient accumulation only the last micro-step carries the (single) noise draw
     std = noise_std(noise_multiplier, global_batch) if micro_index == micro_steps - 1 else 0.0
     return global_batch, NoiseSpec(std=std, seed=runtime.get_seed(),
-                                   param_id=param_id, param_id2=param_id2, step=step, rank=rank, world=world)
+                                   param_id=param_id, param_id2=param_id2, step=step, rank=rank, world=world,
+                                   step_device=runtime.device_noise_counter() if std != 0.0 else None)
 
 
 def direct_grad_target(param):

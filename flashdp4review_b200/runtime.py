@@ -28,6 +28,8 @@ class _Run:
     input_grad_impl = "library"   # "library": cuBLAS via torch (as the reference); "native": fdp_linear_dgrad
     micro_index = 0               # gradient accumulation: which micro-step of `micro_steps` runs now
     micro_steps = 1
+    device_step = False           # the noise step is read from a device counter (use_device_noise_step)
+    device_counters = None        # device index -> one-element int32 tensor
 
 
 _run = _Run()
@@ -42,9 +44,45 @@ def get_seed() -> int:
     return _run.seed
 
 
+def use_device_noise_step(on: bool = True):
+    """Read the noise step on the GPU.  By default each DP layer counts its own backward passes on the
+    host and passes the count to its kernels, which is all an eagerly executed loop needs.  A training
+    step captured in a CUDA graph replays the same kernel arguments, hence the same noise, every time.
+    With this switch on, every layer passes a fixed step plus a pointer to a per-device counter that
+    the kernels add when they run; `advance_noise_step()` -- one tiny kernel, to be called once per
+    training step, inside the captured region -- increments it, so every replay draws fresh noise."""
+    _run.device_step = bool(on)
+
+
+def device_noise_counter(device=None):
+    """The current (or given) CUDA device's noise-step counter, a one-element int32 tensor, or None
+    when `use_device_noise_step` is off."""
+    if not _run.device_step:
+        return None
+    import torch
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    if _run.device_counters is None:
+        _run.device_counters = {}
+    t = _run.device_counters.get(idx)
+    if t is None:
+        t = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+        _run.device_counters[idx] = t
+    return t
+
+
+def advance_noise_step(n: int = 1):
+    """counter += n on the current device's stream (see use_device_noise_step); a no-op when off."""
+    t = device_noise_counter()
+    if t is not None:
+        t.add_(int(n))
+
+
 def noise_step(local_count: int) -> int:
     """Philox step word of a layer's `local_count`-th backward: the run's base plus the layer's own
-    counter, so that after `set_noise_state` no (parameter, step) pair of the earlier run recurs."""
+    counter, so that after `set_noise_state` no (parameter, step) pair of the earlier run recurs.
+    With the device counter on, the host part is the constant base + 1 and the counter does the counting."""
+    if _run.device_step:
+        return (_run.step_base + 1) & 0xFFFFFFFF
     step = (_run.step_base + int(local_count)) & 0xFFFFFFFF
     if step > _run.step_high:
         _run.step_high = step
@@ -56,7 +94,10 @@ def noise_state() -> dict:
     and the highest step drawn so far.  Without it a resumed run would count its layers' steps from
     zero again and, under the same seed, repeat the noise tensors of steps 1..N exactly -- noise an
     observer of both runs could cancel."""
-    return {"seed": _run.seed, "step": _run.step_high}
+    high = _run.step_high
+    for t in (_run.device_counters or {}).values():      # reads the counters back: a synchronisation
+        high = max(high, (_run.step_base + 1 + int(t.item())) & 0xFFFFFFFF)
+    return {"seed": _run.seed, "step": high}
 
 
 def set_noise_state(state: dict):

@@ -29,7 +29,7 @@
 extern "C" {
 #endif
 
-#define FDP_ABI_VERSION 2
+#define FDP_ABI_VERSION 3
 
 typedef void* fdp_stream_t; /* a cudaStream_t */
 
@@ -88,6 +88,12 @@ typedef struct fdp_dp_params {
   uint32_t step;         /* Philox counter word 3: training step */
   int32_t noise_rank;    /* this rank draws the noise of element groups g with g % noise_world == noise_rank */
   int32_t noise_world;   /* <=1: this rank draws all of it */
+  /* NULL, or a device pointer to a 32-bit counter that the kernels read when they run: the step
+   * word is then step + *step_device.  A step captured in a CUDA graph together with a kernel that
+   * increments the counter draws fresh noise on every replay; with a host-side step a replay would
+   * repeat the captured draw.  No counterpart in the reference (torch.normal advances the device
+   * generator's offset, flashdp/layers/linear.py:74-80). */
+  const uint32_t* step_device;
 } fdp_dp_params;
 
 int fdp_abi_version(void);
