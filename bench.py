@@ -248,7 +248,51 @@ def parity_check(dev, rank, world):
     return out
 
 
-def reference_gpu_leg(X, G, W, sigma, timed, own_dw):
+def reference_gpu_leg(args):
+    """Runs `reference_gpu_child` in a process of its own and returns its JSON object: whatever the
+    reference's code or its JIT compiler does on this GPU -- a compile error (caught there), a crash, a
+    stall -- cannot take the bench with it."""
+    cmd = [sys.executable, os.path.abspath(__file__), "--workload", args.workload, "--sigma", str(args.sigma),
+           "--ref-gpu-child"]
+    try:
+        r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": "the child process that runs the reference did not finish within 600 s"}
+    lines = [l for l in r.stdout.splitlines() if l.startswith("{")]
+    if r.returncode != 0 or not lines:
+        tail = (r.stderr.strip().splitlines() or [""])[-1][:200]
+        return {"unavailable": "child process exited with %d: %s" % (r.returncode, tail)}
+    return json.loads(lines[-1])
+
+
+def reference_gpu_child(args, wl):
+    """Child of `reference_gpu_leg`: the bench's inputs (rank 0's), this library's sigma = 0 result for
+    the comparison, then the reference's code; prints one JSON object."""
+    import torch
+    from flashdp4review_b200.core import ops
+    B, T, n_in, n_out, dtn, g_scale = wl
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    dt = torch.bfloat16 if dtn == "bf16" else torch.float32
+    gen = torch.Generator().manual_seed(0)
+    X = torch.randn(B, T, n_in, generator=gen).to(dt).to(dev)
+    G = (torch.randn(B, T, n_out, generator=gen) * g_scale).to(dt).to(dev)
+    W = (torch.randn(n_out, n_in, generator=gen) * 0.02).to(dt).to(dev)
+    own = ops.dp_linear_weight_grad(X, G, 1.0, 1.0, batch_divisor=B, noise=None, out_dtype=torch.float32)
+
+    def timed(fn, steps):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1)
+    print(json.dumps(reference_gpu_run(X, G, W, args.sigma, timed, own)), flush=True)
+
+
+def reference_gpu_run(X, G, W, sigma, timed, own_dw):
     """The UNMODIFIED reference package on this GPU, where `__graft_entry__.build()` installed it
     (`baseline/_ref`, outside the history), run on the bench's own X and G.  Context for the headline
     only: none of this library's code runs inside these timings.  Three entries, each on its own:
@@ -543,10 +587,8 @@ def run_native(args, wl):
 
     ref_gpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and not args.no_ref_gpu and dtn == "bf16":
-        noise0 = ops.NoiseSpec(std=0.0, seed=1234, param_id=1, step=1, rank=0, world=1)
-        own = ops.dp_linear_weight_grad(X, G, 1.0, 1.0, batch_divisor=B, noise=noise0, out_dtype=torch.float32)
-        ref_gpu = reference_gpu_leg(X, G, W, args.sigma, timed, own)
-        del own
+        torch.cuda.synchronize()
+        ref_gpu = reference_gpu_leg(args)
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -1011,6 +1053,7 @@ def main():
     ap.add_argument("--no-check", action="store_true", help="skip the untimed N-rank == single-rank check")
     ap.add_argument("--reserve-sms", type=int, default=12,
                     help="N > 1: SMs the input-gradient GEMM leaves to the all-reduce that runs beside it")
+    ap.add_argument("--ref-gpu-child", action="store_true", help=argparse.SUPPRESS)
     ap.add_argument("--no-ref-gpu", action="store_true",
                     help="skip the context leg that runs the installed reference package on the same GPU")
     args = ap.parse_args()
@@ -1029,6 +1072,8 @@ def main():
             return
         return run_gpt2(args)
     wl = WORKLOADS[args.workload]
+    if args.ref_gpu_child:
+        return reference_gpu_child(args, wl)
     if args.impl == "reference":
         run_reference(args, wl)
     else:
