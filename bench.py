@@ -726,7 +726,11 @@ def gpt2_measure(args, steps, with_no_dp=False, no_dp=False):
     lib = _lib.load()
     fdp.manual_seed(1234)
     fdp.set_data_parallel(rank, world)
-    fdp.set_input_grad_impl(args.gemm_impl)
+    # fp32 run (--fp32: no autocast, the reference's own default, example/gpt2/train.py:34): the forward and
+    # input-gradient products stay with cuBLAS, as in the package default for fp32 layers
+    fdp.set_input_grad_impl("library" if args.fp32 else args.gemm_impl)
+    if args.fp32:
+        fdp.set_fp32_mode(args.fp32_mode)
     micro_batch, seq = args.micro_batch, 1024
     cfg = GPT2Config(n_layer=args.layers, n_embd=1024, n_head=16, n_positions=1024, vocab_size=50257,
                      resid_pdrop=0.0, embd_pdrop=0.0, attn_pdrop=0.0)
@@ -771,7 +775,7 @@ def gpt2_measure(args, steps, with_no_dp=False, no_dp=False):
                 reducer.zero_grad()
             else:
                 opt.zero_grad(set_to_none=True)
-            with torch.autocast("cuda", dtype=torch.bfloat16):
+            with torch.autocast("cuda", dtype=torch.bfloat16, enabled=not args.fp32):
                 out = model(input_ids=tok[:, :-1], labels=tok[:, :-1])
             out.loss.backward()
             if reducer is not None:
@@ -839,7 +843,8 @@ def run_gpt2(args):
         cfg = dict(g["config"], workload=args.workload)
         line = {"metric": "gpt2_medium_dp_tokens_per_s", "value": g["tokens_per_s"], "unit": "tokens/s", "n_gpus": world,
                 "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": g["ms_per_step"],
-                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                "dtype": "f32 (%s)" % args.fp32_mode if args.fp32 else "bf16",
                 "data": "synthetic", "config": cfg, "e2e": g["e2e"], "gpu_launches": g["gpu_launches"],
                 "clocks": g["clocks"], "loss": g["loss"], "peak_memory_bytes": g["peak_memory_bytes"]}
         print(json.dumps(line), flush=True)
@@ -1042,6 +1047,9 @@ def main():
     ap.add_argument("--gemm-impl", default="native", choices=["native", "library"],
                     help="gpt2_medium: forward / input-gradient GEMMs of the DP layers by this library or by cuBLAS")
     ap.add_argument("--no-dp", action="store_true", help="gpt2_medium: leave the model unwrapped (context only)")
+    ap.add_argument("--fp32", action="store_true", help="gpt2_medium: fp32 throughout, no autocast (context only)")
+    ap.add_argument("--fp32-mode", default="tensor", choices=["tensor", "exact"],
+                    help="gpt2_medium --fp32: DP weight gradients as three bf16 tensor-core products, or on fp32-FMA kernels")
     ap.add_argument("--norm-algo", default="auto", choices=["auto", "direct", "gram"])
     ap.add_argument("--sigma", type=float, default=1.0, help="noise_multiplier of the DP-Linear workloads")
     ap.add_argument("--cpu-budget", type=float, default=12.0, help="seconds of CPU work for cpu_baseline")
