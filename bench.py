@@ -726,9 +726,8 @@ def gpt2_measure(args, steps, with_no_dp=False, no_dp=False):
     lib = _lib.load()
     fdp.manual_seed(1234)
     fdp.set_data_parallel(rank, world)
-    # fp32 run (--fp32: no autocast, the reference's own default, example/gpt2/train.py:34): the forward and
-    # input-gradient products stay with cuBLAS, as in the package default for fp32 layers
-    fdp.set_input_grad_impl("library" if args.fp32 else args.gemm_impl)
+    # fp32 run (--fp32: no autocast, the reference's own default, example/gpt2/train.py:34)
+    fdp.set_input_grad_impl(args.gemm_impl)
     if args.fp32:
         fdp.set_fp32_mode(args.fp32_mode)
     micro_batch, seq = args.micro_batch, 1024

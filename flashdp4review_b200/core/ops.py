@@ -206,44 +206,71 @@ def linear_bias_grad_clip(grad_output, C, clamp_value):
 # ------------------------------------------------------------------------------------------------
 # input gradient
 # ------------------------------------------------------------------------------------------------
-def linear_input_grad(grad_output, weight, w_layout="out_in", out_dtype=None):
+def native_product_ok(dtype, rows, K, N):
+    """Whether a layer that was asked for the library's own forward / input-gradient GEMMs should use
+    them for a [rows, K] x [K, N] product: always for bf16 / fp16 (tcgen05 GEMM); for fp32 only where
+    the three-product tensor-core path applies (fp32 mode "tensor", K a multiple of 64, at least 128 of
+    everything) -- elsewhere cuBLAS through torch is the faster fp32 GEMM."""
+    if dtype in (torch.bfloat16, torch.float16):
+        return True
+    from .. import runtime
+    return (dtype == torch.float32 and runtime.fp32_mode() == "tensor" and rows >= 128 and K >= 128 and N >= 128
+            and K % 64 == 0 and N % 8 == 0)
+
+
+def _gemm_dtype_code(dtype, fp32_tensor):
+    """dtype code of the forward / input-gradient entry points, with the fp32 tensor-core flag"""
+    code = _dt(dtype)
+    if dtype == torch.float32:
+        if fp32_tensor is None:
+            from .. import runtime
+            fp32_tensor = runtime.fp32_mode() == "tensor"
+        if fp32_tensor:
+            code |= _lib.FDP_FP32_TENSOR
+    return code
+
+
+def linear_input_grad(grad_output, weight, w_layout="out_in", out_dtype=None, fp32_tensor=None):
     """grad_output @ weight (nn.Linear, weight [out,in]) or grad_output @ weight.t() (Conv1D,
     weight [in,out]) -- flashdp/layers/linear.py:62-67, transformers_conv1d.py:70-75.
-    `out_dtype` (default: grad_output's) lets the kernel write the dtype autograd wants directly."""
+    `out_dtype` (default: grad_output's) lets the kernel write the dtype autograd wants directly.
+    `fp32_tensor` as in dp_linear_weight_grad: fp32 operands as three bf16 tensor-core products."""
     lib = _lib.load()
     _require_cuda(grad_output, weight)
-    G = grad_output.contiguous()
-    W = weight.to(G.dtype).contiguous()         # AMP: weight follows the grad dtype (linear.py:66)
+    G = _aligned(grad_output.contiguous())
+    W = _aligned(weight.to(G.dtype).contiguous())         # AMP: weight follows the grad dtype (linear.py:66)
     n_out = G.shape[-1]
     n_in = W.shape[1] if w_layout == "out_in" else W.shape[0]
     rows = G.numel() // n_out
     out_dtype = out_dtype or G.dtype
     dX = torch.empty(G.shape[:-1] + (n_in,), dtype=out_dtype, device=G.device)
-    ws = _workspace(lib.fdp_linear_dgrad_workspace_bytes(rows, n_in, n_out, _dt(G.dtype)), G.device)
+    code = _gemm_dtype_code(G.dtype, fp32_tensor)
+    ws = _workspace(lib.fdp_linear_dgrad_workspace_bytes(rows, n_in, n_out, code), G.device)
     with torch.cuda.device(G.device):
-        st = lib.fdp_linear_dgrad(_ptr(G), _ptr(W), _ptr(dX), rows, n_in, n_out, _dt(G.dtype), _dt(out_dtype),
+        st = lib.fdp_linear_dgrad(_ptr(G), _ptr(W), _ptr(dX), rows, n_in, n_out, code, _dt(out_dtype),
                                   _lib.FDP_OUT_IN if w_layout == "out_in" else _lib.FDP_IN_OUT,
                                   _ptr(ws), ws.numel(), _stream(G.device))
     _lib.check(st, "fdp_linear_dgrad")
     return dX
 
 
-def linear_forward(input, weight, bias=None, w_layout="out_in", out_dtype=None):
+def linear_forward(input, weight, bias=None, w_layout="out_in", out_dtype=None, fp32_tensor=None):
     """input @ weight.t() + bias (nn.Linear, weight [out,in]) or input @ weight + bias (Conv1D, weight
     [in,out]) -- flashdp/layers/linear.py:41-46, transformers_conv1d.py:40-43."""
     lib = _lib.load()
     _require_cuda(input, weight, bias)
-    X = input.contiguous()
-    W = weight.to(X.dtype).contiguous()
-    b = None if bias is None else bias.to(X.dtype).contiguous()
+    X = _aligned(input.contiguous())
+    W = _aligned(weight.to(X.dtype).contiguous())
+    b = None if bias is None else _aligned(bias.to(X.dtype).contiguous())
     n_in = X.shape[-1]
     n_out = W.shape[0] if w_layout == "out_in" else W.shape[1]
     rows = X.numel() // n_in
     out_dtype = out_dtype or X.dtype
     Y = torch.empty(X.shape[:-1] + (n_out,), dtype=out_dtype, device=X.device)
-    ws = _workspace(lib.fdp_linear_dgrad_workspace_bytes(rows, n_out, n_in, _dt(X.dtype)), X.device)
+    code = _gemm_dtype_code(X.dtype, fp32_tensor)
+    ws = _workspace(lib.fdp_linear_dgrad_workspace_bytes(rows, n_out, n_in, code), X.device)
     with torch.cuda.device(X.device):
-        st = lib.fdp_linear_fwd(_ptr(X), _ptr(W), _ptr(b), _ptr(Y), rows, n_in, n_out, _dt(X.dtype), _dt(out_dtype),
+        st = lib.fdp_linear_fwd(_ptr(X), _ptr(W), _ptr(b), _ptr(Y), rows, n_in, n_out, code, _dt(out_dtype),
                                 _lib.FDP_OUT_IN if w_layout == "out_in" else _lib.FDP_IN_OUT,
                                 _ptr(ws), ws.numel(), _stream(X.device))
     _lib.check(st, "fdp_linear_fwd")

@@ -350,9 +350,30 @@ int fdp_bias_grad(const void* G, void* db, float* norms_out, float* factors_out,
 }
 
 // ---- input gradient ---------------------------------------------------------------------------------
+// fp32 with FDP_FP32_TENSOR in `dtype`: whether the product [rows, K] x [K, N] takes the three-product path
+static bool gemm3_wanted(int dtype, int rows, int K, int N) {
+  return dtype == (FDP_F32 | FDP_FP32_TENSOR) && tc_gemm3_ok(rows, K, N);
+}
+
 size_t fdp_linear_dgrad_workspace_bytes(int rows, int n_in, int n_out, int dtype) {
-  (void)rows; (void)n_in; (void)n_out; (void)dtype;
-  return 256;  // the status word
+  // the status word, then the split copies of the two operands when fp32 runs on the tensor cores
+  // (K = n_out, N = n_in; the forward product queries with the two exchanged)
+  return 256 + (gemm3_wanted(dtype, rows, n_out, n_in) ? tc_gemm3_ws_bytes(rows, n_out, n_in) : 0);
+}
+
+// Y[rows, N] = A[rows, K] * W (+ bias), fp32 in and out, as three bf16 products: split, then one GEMM
+static int gemm3_call(const void* A, const void* W, const void* bias, void* Y, int rows, int K, int N, int out_dtype,
+                      bool w_kn, void* workspace, size_t workspace_bytes, cudaStream_t s) {
+  if (workspace_bytes < 256 + tc_gemm3_ws_bytes(rows, K, N)) return FDP_ERR_WORKSPACE;
+  int* status = static_cast<int*>(workspace);
+  char* a3 = static_cast<char*>(workspace) + 256;
+  char* w3 = a3 + ((static_cast<size_t>(rows) * K * 4 + 255) & ~static_cast<size_t>(255));
+  FDP_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), s));
+  int st;
+  if ((st = tc_split3(A, a3, static_cast<size_t>(rows), K, s)) != FDP_OK) return st;
+  // W is [K, N] (w_kn) or [N, K]: either way its rows are split along their own columns
+  if ((st = tc_split3(W, w3, static_cast<size_t>(w_kn ? K : N), w_kn ? N : K, s)) != FDP_OK) return st;
+  return tc_gemm3(a3, w3, bias, Y, status, rows, K, N, out_dtype, w_kn, s);
 }
 
 int fdp_linear_dgrad(const void* G, const void* W, void* dX, int rows, int n_in, int n_out,
@@ -362,13 +383,19 @@ int fdp_linear_dgrad(const void* G, const void* W, void* dX, int rows, int n_in,
   if (G == nullptr || W == nullptr || dX == nullptr) return FDP_ERR_ARG;
   if (rows <= 0 || n_in <= 0 || n_out <= 0) return FDP_ERR_ARG;
   if (w_layout != FDP_OUT_IN && w_layout != FDP_IN_OUT) return FDP_ERR_ARG;
+  const bool want3 = gemm3_wanted(dtype, rows, n_out, n_in);
+  if ((dtype & FDP_FP32_TENSOR) != 0 && (dtype & ~FDP_FP32_TENSOR) == FDP_F32) dtype = FDP_F32;
   if (!valid_dtype(dtype) || !valid_dtype(out_dtype)) return FDP_ERR_DTYPE;
   int st = current_device_ok();
   if (st != FDP_OK) return st;
   if (workspace == nullptr || workspace_bytes < 256 || !aligned16(workspace)) return FDP_ERR_WORKSPACE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int* status = static_cast<int*>(workspace);
-  if (tc_dgrad_ok(rows, n_in, n_out, dtype) && aligned16(G) && aligned16(W) && aligned16(dX)) {
+  if (want3 && aligned16(G) && aligned16(W) && aligned16(dX)) {
+    // dX = G [rows, n_out] * W: W is [n_out, n_in] = [K, N] for nn.Linear, [n_in, n_out] = [N, K] for Conv1D
+    if ((st = gemm3_call(G, W, nullptr, dX, rows, n_out, n_in, out_dtype, w_layout == FDP_OUT_IN, workspace,
+                         workspace_bytes, s)) != FDP_OK) return st;
+  } else if (tc_dgrad_ok(rows, n_in, n_out, dtype) && aligned16(G) && aligned16(W) && aligned16(dX)) {
     if ((st = tc_dgrad(G, W, dX, status, rows, n_in, n_out, dtype, out_dtype, w_layout, s)) != FDP_OK) return st;
   } else {
     FDP_CUDA_OK(cudaMemsetAsync(status, 0, sizeof(int), s));
@@ -386,12 +413,19 @@ int fdp_linear_fwd(const void* X, const void* W, const void* bias, void* Y, int 
   if (X == nullptr || W == nullptr || Y == nullptr) return FDP_ERR_ARG;
   if (rows <= 0 || n_in <= 0 || n_out <= 0) return FDP_ERR_ARG;
   if (w_layout != FDP_OUT_IN && w_layout != FDP_IN_OUT) return FDP_ERR_ARG;
+  const bool want3 = gemm3_wanted(dtype, rows, n_in, n_out);
+  if ((dtype & FDP_FP32_TENSOR) != 0 && (dtype & ~FDP_FP32_TENSOR) == FDP_F32) dtype = FDP_F32;
   if (!valid_dtype(dtype) || !valid_dtype(out_dtype)) return FDP_ERR_DTYPE;
   int st = current_device_ok();
   if (st != FDP_OK) return st;
   if (workspace == nullptr || workspace_bytes < 256 || !aligned16(workspace)) return FDP_ERR_WORKSPACE;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   int* status = static_cast<int*>(workspace);
+  if (want3 && aligned16(X) && aligned16(W) && aligned16(Y) && (bias == nullptr || aligned16(bias))) {
+    // Y = X [rows, n_in] * W^T: W is [n_out, n_in] = [N, K] for nn.Linear, [n_in, n_out] = [K, N] for Conv1D
+    if ((st = gemm3_call(X, W, bias, Y, rows, n_in, n_out, out_dtype, w_layout == FDP_IN_OUT, workspace,
+                         workspace_bytes, s)) != FDP_OK) return st;
+  } else
   // same shape rules as the input gradient with the roles of n_in and n_out exchanged
   if (tc_dgrad_ok(rows, n_out, n_in, dtype) && aligned16(X) && aligned16(W) && aligned16(Y)) {
     if ((st = tc_fwd(X, W, bias, Y, status, rows, n_in, n_out, dtype, out_dtype, w_layout, s)) != FDP_OK) return st;

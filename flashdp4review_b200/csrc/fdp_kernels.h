@@ -154,6 +154,12 @@ int tc_clipped_wgrad(const void* Gs, const void* X, const TcFactorSource* fs, fl
 // test aid: one warp waits `limit_cycles` on a barrier nobody arrives on and reports the timeout
 int tc_wait_selftest(int* status, long long limit_cycles, cudaStream_t s);
 bool tc_dgrad_ok(int rows, int n_in, int n_out, int dt);
+// fp32 product Y[rows, N] = A[rows, K] * W (+ bias) as three bf16 tensor-core products over operands split
+// by tc_split3 (A3 [rows, 2K]; W3 [K, 2N] if w_kn, else [N, 2K]); workspace for the two split copies
+bool tc_gemm3_ok(int rows, int K, int N);
+size_t tc_gemm3_ws_bytes(int rows, int K, int N);
+int tc_gemm3(const void* A3, const void* W3, const void* bias, void* Y, int* dev_status, int rows, int K, int N,
+             int out_dt, bool w_kn, cudaStream_t s);
 int tc_fwd(const void* X, const void* W, const void* bias, void* Y, int* dev_status, int rows, int n_in,
            int n_out, int dt, int out_dt, int w_layout, cudaStream_t s);
 int tc_dgrad(const void* G, const void* W, void* dX, int* dev_status, int rows, int n_in, int n_out,

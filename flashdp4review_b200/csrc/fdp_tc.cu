@@ -63,7 +63,8 @@ struct TcArgs {
   int zero_status;      // this launch is the first of its call: its first thread clears the status word
   int dependent;        // host side: launch as a programmatic dependent of the kernel before it in the stream
   int sub_stages;       // EPI_STORE_SCALED: K stages per accumulator hand-off (<= seg_stages; chains of fp32 tensor mode)
-  int norm_mode;        // EPI_STORE_SCALED: no store; sum of squares of the unit's accumulated tile -> partials
+  int norm_mode;        // EPI_STORE_SCALED: 1 = no store, sum of squares of the unit's accumulated tile -> partials;
+                        // 2 = plain product (factor = scale for every segment), stored as usual
   int* sticky;          // this device's slot of the host-visible status array, or null
   uint32_t idesc;
   // split-K (store epilogues): work units [0, units_full) are whole tiles; each later tile is cut into
@@ -603,7 +604,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           tc_fence_after();
           const int sample = ks / args.seg_stages;
           // the divisor goes into the factor, so the noise is added as it is drawn
-          const float cbs = args.norm_mode ? 1.0f
+          const float cbs = args.norm_mode == 1 ? 1.0f : args.norm_mode == 2 ? args.scale
                           : (args.norm_partials != nullptr ? sfac[sample] : __ldg(args.factors + sample)) * args.scale;
           const uint32_t tb = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + chalf * 128;
 #pragma unroll
@@ -631,7 +632,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
           }
         }
         if (!ok) break;
-        if (args.norm_mode) {
+        if (args.norm_mode == 1) {
           // the unit is one sample's product tile: its squares, without the rows and columns past the
           // matrix (with split operands a tile that overhangs reads the other half's columns, not zeros)
           float part = 0.f;
@@ -1311,6 +1312,48 @@ int tc_fwd(const void* X, const void* W, const void* bias, void* Y, int* dev_sta
   args.idesc = make_idesc(dt, false, true, ctas);
   return ctas == 2 ? launch<false, true, EPI_STORE, 2>(mx, mw, mx, mw, args, s)
                    : launch<false, true, EPI_STORE, 1>(mx, mw, mx, mw, args, s);
+}
+
+// ---- fp32 products on the tensor cores: Y[rows, N] = A[rows, K] * W (+ bias) --------------------------
+// A3 is [rows, 2K] and W3 [K, 2N] (w_kn) or [N, 2K] (else): bf16 high halves then low halves (tc_split3).
+// Three bf16 products per K range into accumulators that the epilogue warps take over every few K
+// stages and sum in registers (chain_stages), then the ordinary store epilogue.
+bool tc_gemm3_ok(int rows, int K, int N) {
+  return rows >= 128 && K >= 128 && N >= 128 && K % BK == 0 && N % 8 == 0;
+}
+size_t tc_gemm3_ws_bytes(int rows, int K, int N) {
+  return align256(static_cast<size_t>(rows) * K * 4) + align256(static_cast<size_t>(K) * N * 4);
+}
+int tc_gemm3(const void* A3, const void* W3, const void* bias, void* Y, int* dev_status, int rows, int K, int N,
+             int out_dt, bool w_kn, cudaStream_t s) {
+  CUtensorMap ma, mw;
+  const int ctas = ctas_per_tile();
+  if (!make_map(&ma, A3, rows, 2 * K, BK, BM, FDP_BF16)) return FDP_ERR_LAUNCH;
+  TcArgs args{};
+  args.batch = 1; args.batch_rows = 0; args.status = dev_status;
+  args.dependent = 1;            // follows the split kernels of the same call
+  args.M = rows; args.N = N; args.ld_out = N;
+  args.tiles_m = ceil_div(rows, BM * ctas); args.tiles_n = ceil_div(N, BN);
+  args.tiles_per_batch = args.tiles_m * args.tiles_n;
+  args.terms = 3;
+  args.term_stages = K / BK;
+  args.k_stages = 3 * (K / BK);
+  args.plane_a = K; args.plane_b = w_kn ? N : K;
+  args.n_fastest = 1;
+  args.out = Y; args.out_dt = out_dt; args.scale = 1.0f; args.nk = NoiseKey{};
+  args.bias = bias; args.bias_dt = FDP_F32;
+  args.segs = 1; args.seg_stages = args.k_stages; args.sub_stages = chain_stages(args.seg_stages);
+  args.norm_mode = 2;
+  if (w_kn) {   // rows of W3 are K, N contiguous
+    if (!make_map(&mw, W3, K, 2 * N, 64, BK, FDP_BF16)) return FDP_ERR_LAUNCH;
+    args.idesc = make_idesc(FDP_BF16, false, true, ctas);
+    return ctas == 2 ? launch<false, true, EPI_STORE_SCALED, 2>(ma, mw, ma, mw, args, s)
+                     : launch<false, true, EPI_STORE_SCALED, 1>(ma, mw, ma, mw, args, s);
+  }
+  if (!make_map(&mw, W3, N, 2 * K, BK, BN / ctas, FDP_BF16)) return FDP_ERR_LAUNCH;   // K contiguous
+  args.idesc = make_idesc(FDP_BF16, false, false, ctas);
+  return ctas == 2 ? launch<false, false, EPI_STORE_SCALED, 2>(ma, mw, ma, mw, args, s)
+                   : launch<false, false, EPI_STORE_SCALED, 1>(ma, mw, ma, mw, args, s);
 }
 
 }  // namespace fdp

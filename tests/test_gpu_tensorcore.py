@@ -220,3 +220,31 @@ def test_dplinear_2d_large_batch_bf16():
     assert rel_err(lin.weight.grad.float().cpu().numpy(), want) < 1e-2
     assert rel_err(lin.bias.grad.float().cpu().numpy(), want_b) < 1e-2
     assert x.grad.shape == x.shape
+
+
+@pytest.mark.parametrize("w_layout", ["out_in", "in_out"])
+@pytest.mark.parametrize("shape", [(2048, 1024, 768), (512, 256, 520), (4096, 4096, 1024), (130, 128, 136)],
+                         ids=lambda s: "x".join(map(str, s)))
+def test_fp32_forward_and_input_gradient_on_the_tensor_cores(shape, w_layout):
+    """fp32 `linear_forward` / `linear_input_grad` as three bf16 tensor-core products with chained
+    accumulation (the package default for fp32 where K is a multiple of 64): within the fp32 tolerance
+    1e-5 of float64, bias included, output widths that are not multiples of the tile included; the
+    flag off gives the fp32-FMA kernels, also within 1e-5."""
+    from flashdp4review_b200.core import ops
+    rows, n_in, n_out = shape
+    gen = torch.Generator(device="cuda").manual_seed(rows + n_in + n_out)
+    X = torch.randn(rows, n_in, device=dev(), generator=gen)
+    G = torch.randn(rows, n_out, device=dev(), generator=gen) * 1e-2
+    W = torch.randn(n_out, n_in, device=dev(), generator=gen) * 0.02
+    bias = torch.randn(n_out, device=dev(), generator=gen)
+    Wl = W if w_layout == "out_in" else W.t().contiguous()
+    want_y = X.double() @ W.double().t() + bias.double()
+    want_dx = G.double() @ W.double()
+    assert ops.native_product_ok(torch.float32, rows, n_in, n_out) == (n_in % 64 == 0 and rows >= 128)
+    for mode in (None, True, False):
+        y = ops.linear_forward(X, Wl, bias, w_layout, fp32_tensor=mode)
+        dx = ops.linear_input_grad(G, Wl, w_layout, fp32_tensor=mode)
+        assert y.dtype == torch.float32 and dx.dtype == torch.float32
+        ey = float((y.double() - want_y).abs().max() / want_y.abs().max())
+        ex = float((dx.double() - want_dx).abs().max() / want_dx.abs().max())
+        assert ey < 1e-5 and ex < 1e-5, (mode, ey, ex)
