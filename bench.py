@@ -1043,7 +1043,7 @@ def main():
     ap.add_argument("--llama-micro-batch", type=int, default=4)
     ap.add_argument("--layers", type=int, default=24, help="gpt2_medium: number of transformer blocks")
     ap.add_argument("--micro-batch", type=int, default=8, help="gpt2_medium: samples per GPU and step")
-    ap.add_argument("--gemm-impl", default="native", choices=["native", "library"],
+    ap.add_argument("--gemm-impl", default="native", choices=["native", "library", "auto"],
                     help="gpt2_medium: forward / input-gradient GEMMs of the DP layers by this library or by cuBLAS")
     ap.add_argument("--no-dp", action="store_true", help="gpt2_medium: leave the model unwrapped (context only)")
     ap.add_argument("--fp32", action="store_true", help="gpt2_medium: fp32 throughout, no autocast (context only)")

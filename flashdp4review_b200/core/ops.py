@@ -207,15 +207,22 @@ def linear_bias_grad_clip(grad_output, C, clamp_value):
 # input gradient
 # ------------------------------------------------------------------------------------------------
 def native_product_ok(dtype, rows, K, N):
-    """Whether a layer that was asked for the library's own forward / input-gradient GEMMs should use
-    them for a [rows, K] x [K, N] product: always for bf16 / fp16 (tcgen05 GEMM); for fp32 only where
-    the three-product tensor-core path applies (fp32 mode "tensor", K a multiple of 64, at least 128 of
-    everything) -- elsewhere cuBLAS through torch is the faster fp32 GEMM."""
-    if dtype in (torch.bfloat16, torch.float16):
-        return True
+    """Whether a DP layer runs its forward / input-gradient product [rows, K] x [K, N] on this library's
+    GEMMs, under runtime.input_grad_impl(): "library" never (cuBLAS through torch, as the reference);
+    "auto" (default) where a tensor-core kernel of the library takes the shape -- bf16 / fp16 with
+    8-aligned features, at least 128 rows and output columns and 64 contracted ones; fp32 in mode "tensor"
+    with K a multiple of 64 and at least 128 of everything (three bf16 products); "native" also for every
+    other 16-bit shape (generic kernels)."""
     from .. import runtime
-    return (dtype == torch.float32 and runtime.fp32_mode() == "tensor" and rows >= 128 and K >= 128 and N >= 128
-            and K % 64 == 0 and N % 8 == 0)
+    mode = runtime.input_grad_impl()
+    if mode == "library":
+        return False
+    if dtype == torch.float32:
+        return (runtime.fp32_mode() == "tensor" and rows >= 128 and K >= 128 and N >= 128
+                and K % 64 == 0 and N % 8 == 0)
+    if dtype not in (torch.bfloat16, torch.float16):
+        return False
+    return mode == "native" or (K % 8 == 0 and N % 8 == 0 and N >= 128 and K >= 64 and rows >= 128)
 
 
 def _gemm_dtype_code(dtype, fp32_tensor):

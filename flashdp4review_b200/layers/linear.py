@@ -27,7 +27,7 @@ class _DPLinearFunc(Function):
         ctx.save_for_backward(x, weight, bias, w if dt is not None else None)
         ctx.layer = layer
         ctx.input_dtype = input.dtype
-        if runtime.input_grad_impl() == "native" and x.is_cuda and ops.native_product_ok(
+        if x.is_cuda and ops.native_product_ok(
                 x.dtype, x.numel() // x.shape[-1], w.shape[1], w.shape[0]):
             return ops.linear_forward(x, w, bias, "out_in")     # library GEMM, bias added in its epilogue
         output = x @ w.t()
@@ -46,7 +46,7 @@ class _DPLinearFunc(Function):
         grad_input = grad_weight = grad_bias = None
 
         if ctx.needs_input_grad[0]:
-            if runtime.input_grad_impl() == "native" and ops.native_product_ok(
+            if ops.native_product_ok(
                     g3.dtype, g3.numel() // g3.shape[-1], w_for_dx.shape[0], w_for_dx.shape[1]):
                 grad_input = ops.linear_input_grad(g3, w_for_dx, "out_in", out_dtype=ctx.input_dtype)
             else:

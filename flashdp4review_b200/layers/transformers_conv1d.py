@@ -44,7 +44,7 @@ class _DPConv1DFunc(Function):
         ctx.save_for_backward(bias, x, weight, w if dt is not None else None)
         ctx.layer = layer
         ctx.input_dtype = input.dtype
-        if runtime.input_grad_impl() == "native" and x.is_cuda and ops.native_product_ok(
+        if x.is_cuda and ops.native_product_ok(
                 x.dtype, x.numel() // x.shape[-1], w.shape[0], w.shape[1]):
             return ops.linear_forward(x, w, bias, "in_out")     # library GEMM, bias added in its epilogue
         return x @ w + (bias if dt is None else bias.to(dt))
@@ -71,7 +71,7 @@ class _DPConv1DFunc(Function):
                 grad_bias = None
 
         if ctx.needs_input_grad[1]:
-            if runtime.input_grad_impl() == "native" and ops.native_product_ok(
+            if ops.native_product_ok(
                     g3.dtype, g3.numel() // g3.shape[-1], w_for_dx.shape[1], w_for_dx.shape[0]):
                 grad_input = ops.linear_input_grad(g3, w_for_dx, "in_out", out_dtype=ctx.input_dtype)
             else:

@@ -25,7 +25,7 @@ class _Run:
     # kernels (GPT-2-medium on two GPUs: 95.1 ms per step without a reservation, 97.1 ms with 12 SMs)
     reserve_sms = int(os.environ.get("FDP_DP_RESERVE_SMS", "0"))
     fp32_mode = "tensor"          # "tensor": three bf16 tensor-core products where the shape allows; "exact": fp32 FMA kernels
-    input_grad_impl = "library"   # "library": cuBLAS via torch (as the reference); "native": fdp_linear_dgrad
+    input_grad_impl = "auto"      # forward / input-gradient products of the DP layers: see set_input_grad_impl
     micro_index = 0               # gradient accumulation: which micro-step of `micro_steps` runs now
     micro_steps = 1
     device_step = False           # the noise step is read from a device counter (use_device_noise_step)
@@ -210,12 +210,14 @@ def fp32_mode():
 
 
 def set_input_grad_impl(name: str):
-    """Which GEMMs the DP layers use beside the DP kernels: "library" = cuBLAS through torch, as the
-    reference does (flashdp/layers/linear.py:43, :62-67); "native" = this package's own tcgen05 GEMMs
-    for the input gradient (any dtype) and, for bf16/fp16, the forward product with the bias added in
-    the epilogue."""
-    if name not in ("library", "native"):
-        raise ValueError("input_grad_impl must be 'library' or 'native'")
+    """Which GEMMs the DP layers use beside the DP kernels, i.e. for the forward product and the input
+    gradient.  "library": cuBLAS through torch, as the reference does (flashdp/layers/linear.py:43,
+    :62-67).  "auto" (default): this package's own tcgen05 GEMMs (bias added in the epilogue) wherever one
+    of them takes the shape -- for fp32 layers that is three bf16 products within 1e-5, about five times
+    cuBLAS's fp32 GEMM -- and cuBLAS elsewhere.  "native": the package's kernels for every 16-bit shape,
+    the generic ones included."""
+    if name not in ("library", "native", "auto"):
+        raise ValueError("input_grad_impl must be 'library', 'native' or 'auto'")
     _run.input_grad_impl = name
 
 

@@ -32,7 +32,7 @@ def test_dplinear_matches_reference_function(golden):
     assert lin.dp and lin.weight.requires_dp and type(lin.weight).__name__ == "DPParameter"
 
 
-@pytest.mark.parametrize("impl", ["library", "native"])
+@pytest.mark.parametrize("impl", ["library", "native", "auto"])
 def test_dplinear_2d_and_4d_inputs(impl):
     import flashdp4review_b200 as fdp
     fdp.set_input_grad_impl(impl)
@@ -50,7 +50,7 @@ def test_dplinear_2d_and_4d_inputs(impl):
             assert rel_err(lin.weight.grad.cpu().numpy(), want) < 1e-5
             assert rel_err(x.grad.cpu().numpy(), (gy.double().cpu() @ lin.weight.double().cpu()).detach().numpy()) < 1e-5
     finally:
-        fdp.set_input_grad_impl("library")
+        fdp.set_input_grad_impl("auto")
 
 
 def test_dpconv1d_rectangular_and_compat(golden):
@@ -170,7 +170,7 @@ def test_native_gemms_bf16_layer_matches_oracle():
             want, _ = O.linear_weight_grad(G, X, 0.1, 1.0, layout="out_in" if kind == "linear" else "in_out")
             assert rel_err(layer.weight.grad.float().cpu().numpy(), want) < 1e-2
     finally:
-        fdp.set_input_grad_impl("library")
+        fdp.set_input_grad_impl("auto")
 
 
 def test_wrapped_model_trains_one_step():

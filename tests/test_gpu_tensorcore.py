@@ -240,7 +240,14 @@ def test_fp32_forward_and_input_gradient_on_the_tensor_cores(shape, w_layout):
     Wl = W if w_layout == "out_in" else W.t().contiguous()
     want_y = X.double() @ W.double().t() + bias.double()
     want_dx = G.double() @ W.double()
-    assert ops.native_product_ok(torch.float32, rows, n_in, n_out) == (n_in % 64 == 0 and rows >= 128)
+    from flashdp4review_b200 import runtime
+    before = runtime.input_grad_impl()
+    try:
+        for impl, want in (("auto", n_in % 64 == 0 and rows >= 128), ("library", False)):
+            runtime.set_input_grad_impl(impl)
+            assert ops.native_product_ok(torch.float32, rows, n_in, n_out) == want
+    finally:
+        runtime.set_input_grad_impl(before)
     for mode in (None, True, False):
         y = ops.linear_forward(X, Wl, bias, w_layout, fp32_tensor=mode)
         dx = ops.linear_input_grad(G, Wl, w_layout, fp32_tensor=mode)
