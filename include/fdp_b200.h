@@ -198,6 +198,11 @@ int fdp_bias_grad_static(const void* G, void* db, float* norms_out, float* facto
  * `grad_output @ weight.t()` of flashdp/layers/transformers_conv1d.py:70-75 (FDP_IN_OUT, W [n_in,n_out]).
  *   G [rows,n_out] and W in `dtype`; dX [rows,n_in] in `out_dtype` (e.g. fp32 when the layer input was
  *   fp32 under bf16 autocast, which saves the cast pass autograd would otherwise add).
+ *   fp32 on the tensor cores: pass FDP_F32 | FDP_FP32_TENSOR as `dtype`, to the workspace query and to
+ *   the call (also of fdp_linear_fwd).  Where the contracted dimension is a multiple of 64 and rows,
+ *   n_in and n_out are at least 128 the product runs as three bf16 products with chained accumulation,
+ *   within 1e-5 of float64 and about five times cuBLAS's fp32 GEMM; the workspace then also holds the
+ *   bf16 halves of both operands.  Other shapes ignore the flag.
  */
 size_t fdp_linear_dgrad_workspace_bytes(int rows, int n_in, int n_out, int dtype);
 int fdp_linear_dgrad(const void* G, const void* W, void* dX, int rows, int n_in, int n_out,
