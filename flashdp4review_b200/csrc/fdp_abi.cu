@@ -83,6 +83,15 @@ int device_cc_major(int dev) {
 int current_device_ok() {
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return FDP_ERR_LAUNCH; }
+  // A host thread that has not made a CUDA call yet (an autograd worker thread running its first
+  // backward node, say) has a device ordinal but no context bound to it.  The runtime binds one on
+  // demand, the driver entry point that encodes the tensor maps does not and fails.  cudaSetDevice
+  // binds the device's primary context to the calling thread; once per thread and device.
+  thread_local int bound_dev = -1;
+  if (bound_dev != dev) {
+    if (cudaSetDevice(dev) != cudaSuccess) { cudaGetLastError(); return FDP_ERR_LAUNCH; }
+    bound_dev = dev;
+  }
   if (device_cc_major(dev) != 10) return FDP_ERR_ARCH;
   volatile int* arr = sticky_array();
   if (arr != nullptr && dev < 64 && arr[dev] != 0) return FDP_ERR_TIMEOUT;

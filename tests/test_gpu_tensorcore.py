@@ -255,3 +255,30 @@ def test_fp32_forward_and_input_gradient_on_the_tensor_cores(shape, w_layout):
         ey = float((y.double() - want_y).abs().max() / want_y.abs().max())
         ex = float((dx.double() - want_dx).abs().max() / want_dx.abs().max())
         assert ey < 1e-5 and ex < 1e-5, (mode, ey, ex)
+
+
+def test_first_cuda_call_of_a_thread_may_be_a_library_call():
+    """A host thread that has made no CUDA call yet has no context bound (an autograd worker thread
+    running a DP layer's backward as its first node is such a thread).  The tensor-map encoder is a
+    driver entry point and does not bind one on demand, so every entry point binds the device's
+    primary context itself: a tensor-core GEMM called first thing in a new thread works."""
+    import threading
+    from flashdp4review_b200.core import ops
+    X, G, W = O.make_linear_inputs(4, 256, 512, 384, 1e-3, seed=2, dtype=torch.bfloat16)
+    g, w = G.to(dev()), W.to(dev())
+    want = (G.double().reshape(-1, 384) @ W.double()).numpy()
+    torch.cuda.synchronize()
+    box = {}
+
+    def work():
+        try:
+            box["dx"] = ops.linear_input_grad(g, w, "out_in")
+        except Exception as e:      # surfaces in the main thread below
+            box["err"] = e
+    t = threading.Thread(target=work)
+    t.start()
+    t.join()
+    assert "err" not in box, box.get("err")
+    torch.cuda.synchronize()
+    got = box["dx"].float().cpu().numpy().reshape(-1, 512)
+    assert np.abs(got - want).max() / np.abs(want).max() < 1e-2
