@@ -162,3 +162,37 @@ int main() {
     subprocess.run([gxx, "-O1", "-std=c++17", "-o", str(exe), str(src)], check=True)
     out = subprocess.run([str(exe)], capture_output=True, text=True)
     assert out.returncode == 0 and out.stdout.strip() == "ok", out.stdout
+
+
+def test_forward_and_input_gradient_gemm_selection():
+    """`set_input_grad_impl`: "library" never uses the package's GEMMs, "auto" (default) only where a
+    tensor-core kernel takes the shape, "native" also the generic 16-bit kernels; fp32 only in fp32 mode
+    "tensor" and with the contracted dimension a multiple of 64."""
+    import torch
+    from flashdp4review_b200 import runtime
+    from flashdp4review_b200.core import ops
+    before, before32 = runtime.input_grad_impl(), runtime.fp32_mode()
+    try:
+        assert before == "auto" and before32 == "tensor"
+        bf, f32 = torch.bfloat16, torch.float32
+        cases = {  # (dtype, rows, K, N): (library, auto, native)
+            (bf, 8192, 1024, 3072): (False, True, True),
+            (bf, 8192, 100, 3072): (False, False, True),      # K not a multiple of 8: generic kernel
+            (bf, 64, 1024, 1024): (False, False, True),       # too few rows for a tile
+            (f32, 8192, 1024, 3072): (False, True, True),
+            (f32, 8192, 1000, 3072): (False, False, False),   # K not a multiple of 64: cuBLAS
+            (f32, 96, 1024, 1024): (False, False, False),
+            (torch.float64, 8192, 1024, 1024): (False, False, False),
+        }
+        for i, impl in enumerate(("library", "auto", "native")):
+            runtime.set_input_grad_impl(impl)
+            for (dt, rows, K, N), want in cases.items():
+                assert ops.native_product_ok(dt, rows, K, N) == want[i], (impl, dt, rows, K, N)
+        runtime.set_input_grad_impl("auto")
+        runtime.set_fp32_mode("exact")
+        assert not ops.native_product_ok(f32, 8192, 1024, 3072)
+        with pytest.raises(ValueError):
+            runtime.set_input_grad_impl("cublas")
+    finally:
+        runtime.set_input_grad_impl(before)
+        runtime.set_fp32_mode(before32)
