@@ -29,6 +29,9 @@
 extern "C" {
 #endif
 
+/* 2: asynchronous status word, SM reservation, saturating LayerNorm mode, FDP_FP32_TENSOR.
+ * 3: fdp_dp_params.step_device (appended; earlier fields keep their offsets); FDP_FP32_TENSOR also
+ *    accepted in the dtype of fdp_linear_dgrad / fdp_linear_fwd. */
 #define FDP_ABI_VERSION 3
 
 typedef void* fdp_stream_t; /* a cudaStream_t */
