@@ -119,6 +119,19 @@ def test_workspace_queries_are_pure_host_functions():
     assert ln(0, 1, 1) == 0
     assert 0 < ln(4, 9, 40) <= ln(16, 1024, 1024) <= ln(32, 1024, 4096)
     assert lib.fdp_linear_dgrad_workspace_bytes(4096, 256, 384, _lib.FDP_BF16) >= 0
+    # fp32 on the tensor cores: the flag adds room for the bf16 halves of the operands where the shape
+    # qualifies (64-aligned contracted dimension, at least 128 of everything) and nothing elsewhere
+    t3 = _lib.FDP_F32 | _lib.FDP_FP32_TENSOR
+    d = lib.fdp_linear_dgrad_workspace_bytes
+    rows, n_in, n_out = 8192, 1024, 3072
+    assert d(rows, n_in, n_out, _lib.FDP_F32) == 256
+    assert d(rows, n_in, n_out, t3) >= 256 + 4 * (rows * n_out + n_out * n_in)
+    assert d(rows, n_in, 1000, t3) == 256 and d(64, n_in, n_out, t3) == 256     # K % 64, too few rows
+    w = lib.fdp_linear_wgrad_workspace_bytes
+    plain, flagged = w(8, 1024, 4096, 4096, _lib.FDP_F32, 0), w(8, 1024, 4096, 4096, _lib.FDP_F32, _lib.FDP_FP32_TENSOR)
+    assert flagged >= plain + 4 * 8 * 1024 * (4096 + 4096) - (1 << 20)
+    assert w(8, 1000, 4096, 4096, _lib.FDP_F32, _lib.FDP_FP32_TENSOR) == w(8, 1000, 4096, 4096, _lib.FDP_F32, 0)
+    assert w(8, 1024, 4096, 4096, _lib.FDP_BF16, _lib.FDP_FP32_TENSOR) == w(8, 1024, 4096, 4096, _lib.FDP_BF16, 0)
 
 
 def test_gram_work_units_cover_the_block_triangle_once(tmp_path):
